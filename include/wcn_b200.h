@@ -1,0 +1,215 @@
+/*
+ * wcn_b200.h — C ABI of libwcn_b200.so: the sm_100a kernels behind the sparse-convolution
+ * hot path (coordinate hash table, kernel-map generation, stride-2 coordinate
+ * down-sampling, Morton code, gather-GEMM-scatter convolution with a fused
+ * BatchNorm/ReLU/residual epilogue).
+ *
+ * Conventions
+ *  - plain C: device pointers, 64-bit sizes, enum codes; no C++ or torch types.
+ *  - every entry point returns an int status (WCN_OK or a negative wcn_status code) and
+ *    never throws, exits or allocates device memory: outputs and scratch are passed in,
+ *    with a *_bytes query where the size is not obvious.
+ *  - `stream` is a cudaStream_t passed as void*; work is enqueued on it and the call
+ *    returns without synchronising.
+ *  - conditions that can only be detected on the device (hash-table overflow, a bounded
+ *    wait that ran out) are reported through `dev_status`, a device int32 the caller
+ *    zeroes beforehand and reads back when it wants to check; kernels only ever store a
+ *    negative wcn_status code into it.
+ *  - coordinates are int32 rows (batch, x, y, z).  The batch value INT32_MIN is reserved
+ *    (it marks an empty hash slot).
+ *
+ * Each declaration names the reference interface it replaces (paths relative to the
+ * reference project root).
+ */
+#ifndef WCN_B200_H_
+#define WCN_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Status codes.  -1..-5 mirror the reference's GemmStatus
+ * (warpconvnet/csrc/include/gemm_error_codes.h:5-13); the rest are new. */
+enum wcn_status {
+  WCN_OK = 0,
+  WCN_ERR_PROBLEM_NOT_SUPPORTED = -1,
+  WCN_ERR_INITIALIZATION = -2,
+  WCN_ERR_EXECUTION = -3,
+  WCN_ERR_UNSUPPORTED_CONFIG = -4,
+  WCN_ERR_INVALID_PARAMETERS = -5,
+  WCN_ERR_HASH_OVERFLOW = -6,
+  WCN_ERR_WAIT_EXPIRED = -7,
+  WCN_ERR_BOUNDS = -8
+};
+
+/* Element types of feature / weight tensors. */
+enum wcn_dtype { WCN_F32 = 0, WCN_F16 = 1, WCN_BF16 = 2 };
+
+/* Hash functions, in the order of HashMethod
+ * (warpconvnet/geometry/coords/search/torch_hashmap.py:17-32). */
+enum wcn_hash_method { WCN_HASH_FNV1A = 0, WCN_HASH_CITY = 1, WCN_HASH_MURMUR = 2 };
+
+/* Convolution kernels selectable through wcn_conv_fwd's `algo`. */
+enum wcn_conv_algo { WCN_CONV_AUTO = 0, WCN_CONV_SIMT = 1, WCN_CONV_TCGEN05 = 2 };
+
+/* Library version (major*10000 + minor*100 + patch). No reference counterpart. */
+int wcn_version(void);
+
+/* Human-readable text of a status code.
+ * Replaces gemm_status_to_string (warpconvnet/csrc/warpconvnet_pybind.cpp:1220-1226). */
+const char* wcn_status_string(int status);
+
+/* ------------------------------------------------------------------ hash table */
+
+/* Bytes of the table buffer for `capacity` slots (16-byte key + 4-byte value per slot).
+ * Replaces the `[capacity, 2] int32` allocation in TorchHashTable.insert
+ * (warpconvnet/geometry/coords/search/torch_hashmap.py:142). */
+int wcn_hash_table_bytes(int64_t capacity, int64_t* bytes);
+
+/* Clear the table and insert keys[n,4]; the value of a key is its row index (the smallest
+ * one when a key occurs more than once).  stride = {sx,sy,sz} floor-divides x,y,z before
+ * insertion ({1,1,1} or NULL: keys as given).  Needs n <= capacity.
+ * Replaces prepare_key_value_pairs_kernel + insert_kernel_{fnv1a,city,murmur}
+ * (warpconvnet/csrc/hashmap_kernels.cu:182-234, 258-270). */
+int wcn_hash_build(const int32_t* keys, int64_t n, const int32_t* stride, void* table,
+                   int64_t capacity, int hash_method, int32_t* dev_status, void* stream);
+
+/* results[i] = value of queries[i] in the table, or -1.
+ * Replaces search_kernel_{fnv1a,city,murmur} (warpconvnet/csrc/hashmap_kernels.cu:237-301). */
+int wcn_hash_search(const void* table, int64_t capacity, int hash_method, const int32_t* queries,
+                    int64_t num_queries, int32_t* results, void* stream);
+
+/* ------------------------------------------------------------------ distinct / strided coordinates */
+
+/* Scratch bytes for wcn_unique_mark / wcn_unique_emit over n rows. */
+int wcn_unique_workspace_bytes(int64_t n, int64_t* bytes);
+
+/* Phase 1: with the table built by wcn_hash_build over the same (coords, stride), mark the
+ * first occurrence of every distinct row of floor(coords / [1,sx,sy,sz]) and count them
+ * into num_unique (device int64).
+ * Replaces TorchHashTable.unique_index (torch_hashmap.py:303-322: search of all keys
+ * followed by torch.unique) as used by stride_coords
+ * (warpconvnet/geometry/coords/ops/stride.py:41-43). */
+int wcn_unique_mark(const int32_t* coords, int64_t n, const int32_t* stride, const void* table,
+                    int64_t capacity, int hash_method, void* workspace, int64_t* num_unique,
+                    void* stream);
+
+/* Phase 2 (after the caller has read num_unique and sized the outputs): write the distinct
+ * rows in first-occurrence order to out_coords[num_unique,4], their source rows to
+ * unique_index[num_unique], and for every input row the output row it collapsed into to
+ * parent[n].  unique_index / parent may be NULL.
+ * Replaces the gather `discretized_coords[unique_indices]` and the batch argsort of
+ * stride_coords (stride.py:43-48); the order produced here is deterministic. */
+int wcn_unique_emit(const int32_t* coords, int64_t n, const int32_t* stride, void* workspace,
+                    int32_t* out_coords, int32_t* unique_index, int32_t* parent, void* stream);
+
+/* ------------------------------------------------------------------ kernel map */
+
+/* Scratch bytes for the three kernel-map calls (per-block hit counts). */
+int wcn_kmap_workspace_bytes(int64_t num_queries, int32_t num_offsets, int64_t* bytes);
+
+/* nbr[k*M + m] = row of (b, x*sx + i - cx, y*sy + j - cy, z*sz + l - cz) in the table or
+ * -1, for k = (i*ky + j)*kz + l and c = size/2 for odd sizes, 0 for even sizes; also the
+ * per-block hit counts in `workspace`.  num_offsets limits k to the first num_offsets
+ * positions (the reference's skip_symmetric mode passes K/2).
+ * Replaces kernel_map_size_4d_{fnv1a,city,murmur}
+ * (warpconvnet/csrc/discrete_kernels.cu:264-334, 339-370). */
+int wcn_kmap_search(const void* table, int64_t capacity, int hash_method, const int32_t* queries,
+                    int64_t num_queries, const int32_t* stride, const int32_t* kernel_size,
+                    int32_t num_offsets, int32_t* nbr, void* workspace, void* stream);
+
+/* offsets[k] = number of hits of all offsets < k (device int32 [num_offsets+1]); turns the
+ * per-block counts in `workspace` into write positions.
+ * Replaces the cumsum/max/cumsum chain of _kernel_map_search_to_result
+ * (warpconvnet/geometry/coords/search/torch_discrete.py:103-119). */
+int wcn_kmap_scan(void* workspace, int64_t num_queries, int32_t num_offsets, int32_t* offsets,
+                  void* stream);
+
+/* Compact nbr into in_maps / out_maps (length offsets[num_offsets]); within one offset the
+ * pairs are in ascending output row.
+ * Replaces map_found_indices_to_maps_cuda (warpconvnet/csrc/discrete_kernels.cu:183-213, 250-259). */
+int wcn_kmap_compact(const int32_t* nbr, int64_t num_queries, int32_t num_offsets,
+                     const void* workspace, const int32_t* offsets, int32_t* in_maps,
+                     int32_t* out_maps, void* stream);
+
+/* Dense neighbour table from a compact map: nbr[k*M + out_maps[p]] = in_maps[p] for
+ * offsets[k] <= p < offsets[k+1], -1 elsewhere.  Requires out_maps to be distinct within
+ * one offset (true of every map the reference builds).
+ * Replaces nothing directly: the reference's kernels consume the compact lists
+ * (warpconvnet/nn/functional/sparse_conv.py:300-310); this is the layout the
+ * output-stationary convolution reads. */
+int wcn_nbr_from_maps(const int32_t* in_maps, const int32_t* out_maps, const int32_t* offsets,
+                      int32_t num_offsets, int64_t num_pairs, int64_t num_out, int32_t* nbr,
+                      void* stream);
+
+/* Neighbour table of the transposed map: nbr_t[k*num_in + i] = m wherever
+ * nbr_fwd[k*num_out + m] = i, -1 elsewhere.  Requires each input row to occur at most once
+ * per offset (true of every map the reference builds).
+ * Replaces the in/out swap `IntSearchResult(in_maps=fwd.out_maps, out_maps=fwd.in_maps, ...)`
+ * of transposed convolutions (warpconvnet/nn/functional/sparse_conv.py:1934-1938, 1953-1957). */
+int wcn_nbr_transpose(const int32_t* nbr_fwd, int32_t num_offsets, int64_t num_out, int64_t num_in,
+                      int32_t* nbr_t, void* stream);
+
+/* ------------------------------------------------------------------ Morton code */
+
+/* codes[i] = 3-D Morton code of (x - min_xyz[0], y - min_xyz[1], z - min_xyz[2]), x in bit
+ * 0, y in bit 1, z in bit 2, up to 21 bits per axis.  coords has `row_ints` int32 per row
+ * and the x column at `col0` (3,0 for xyz rows; 4,1 for batch-indexed rows).
+ * Replaces assign_order_discrete_20bit_kernel_4points (warpconvnet/csrc/morton_code.cu:71-94)
+ * and the min subtraction of morton_code (coords/ops/serialization.py:224-225). */
+int wcn_morton20(const int32_t* coords, int64_t n, int32_t row_ints, int32_t col0,
+                 const int32_t* min_xyz, int64_t* codes, void* stream);
+
+/* ------------------------------------------------------------------ convolution */
+
+/* dst[r, :] = src[idx[r], :]  (rows of `channels` elements).
+ * Replaces the `comp_in_feats[in_map]` gather of _explicit_gemm_forward_logic
+ * (warpconvnet/nn/functional/sparse_conv.py:309). */
+int wcn_gather_rows(const void* src, const int32_t* idx, void* dst, int64_t num_rows,
+                    int32_t channels, int dtype, void* stream);
+
+/* dst[idx[r], :] += src[r, :]; idx must hold distinct rows (one kernel offset).
+ * Replaces `output_feature_tensor[out_map] += ...` (sparse_conv.py:310). */
+int wcn_scatter_add_rows(const void* src, const int32_t* idx, void* dst, int64_t num_rows,
+                         int32_t channels, int dtype, void* stream);
+
+/* Bytes of the packed-weight buffer wcn_conv_fwd needs for (algo, shape, dtype); 0 when
+ * the chosen kernel reads the weights as given. */
+int wcn_conv_packed_weight_bytes(int algo, int32_t num_offsets, int32_t c_in, int32_t c_out,
+                                 int dtype, int64_t* bytes);
+
+/* Re-layout weight[K, c_in, c_out] into the buffer above (K-major tiles for the tensor-core
+ * kernel).  No reference counterpart (its kernels read the weights as stored). */
+int wcn_conv_pack_weight(int algo, const void* weight, int32_t num_offsets, int32_t c_in,
+                         int32_t c_out, int dtype, void* packed, void* stream);
+
+/* Output-stationary sparse convolution with a fused epilogue:
+ *   acc[m, :] = sum_k feats[nbr[k*M + m], :] @ weight[k]      (rows with nbr < 0 skipped, fp32 accumulation)
+ *   y = acc * scale + shift   (scale NULL: y = acc + shift; both NULL: y = acc)
+ *   y += residual[m, :]       (residual NULL: skipped; residual has the output dtype)
+ *   y = max(y, 0)             (relu != 0)
+ *   out[m, :] = (out dtype) y
+ * feats / weight share `dtype`; scale / shift are fp32 [c_out].  Each output row is written
+ * once by the block that owns it: no atomics, bit-reproducible.
+ * algo WCN_CONV_TCGEN05 needs dtype f16/bf16, c_in % 32 == 0, c_out % 16 == 0, 16 <= c_out <= 256
+ * and `packed_weight` from wcn_conv_pack_weight; WCN_CONV_AUTO picks it when those hold and
+ * packed_weight is not NULL, else the SIMT kernel.
+ * Replaces implicit_gemm (warpconvnet/csrc/warpconvnet_pybind.cpp:732-837,
+ * warpconvnet/csrc/implicit_gemm.cu:44-267) and cutlass_gemm_AD_gather_scatter
+ * (warpconvnet_pybind.cpp:396-509, warpconvnet/csrc/cutlass_gemm_gather_scatter.cu:207-464),
+ * the per-offset loop around them (warpconvnet/nn/functional/sparse_conv.py:396-413, 516-544),
+ * the bias add (sparse_conv.py:1794-1795) and the BatchNorm1d / ReLU / residual-add chain of
+ * the model blocks (examples/mink_unet.py:36-47, 129-141). */
+int wcn_conv_fwd(int algo, const void* feats, int64_t num_in, const void* weight,
+                 const void* packed_weight, const int32_t* nbr, int64_t num_out,
+                 int32_t num_offsets, int32_t c_in, int32_t c_out, int dtype, const float* scale,
+                 const float* shift, const void* residual, int relu, void* out, int out_dtype,
+                 int32_t* dev_status, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* WCN_B200_H_ */

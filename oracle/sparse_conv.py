@@ -1,0 +1,158 @@
+"""torch-CPU restatement of the reference's explicit-GEMM sparse convolution,
+the BatchNorm / ReLU / residual chain and the MinkUNet forward built on them.
+
+TEST INFRASTRUCTURE ONLY (checker and timed CPU baseline); the product package
+never imports this file.  Kernel maps come from ``oracle/kernel_map.py``.
+
+Parity: pinned — :func:`explicit_gemm_forward` is compared with the reference's
+``_explicit_gemm_forward_logic`` run on the same CPU tensors when the golden
+fixtures are generated (``tests/golden/make_golden.py``) and the fixtures are
+replayed in ``tests/test_oracle_pins.py``.
+"""
+from __future__ import annotations
+
+from typing import Dict, Optional, Sequence
+
+import numpy as np
+import torch
+
+from . import kernel_map as km
+
+
+def explicit_gemm_forward(feats: torch.Tensor, weight: torch.Tensor, in_maps, out_maps, offsets,
+                          identity_index: Optional[int], num_out: int,
+                          compute_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """``out = X @ W[c]`` for the identity offset (else zeros), then for every
+    other offset ``out[out_map_k] += X[in_map_k] @ W[k]``; result cast back to
+    the input dtype.  Restates ``_explicit_gemm_forward_logic``
+    (warpconvnet/nn/functional/sparse_conv.py:281-311)."""
+    x = feats if compute_dtype is None else feats.to(compute_dtype)
+    w = weight if compute_dtype is None else weight.to(compute_dtype)
+    in_maps = torch.as_tensor(np.asarray(in_maps), dtype=torch.long)
+    out_maps = torch.as_tensor(np.asarray(out_maps), dtype=torch.long)
+    offsets = np.asarray(offsets)
+    if identity_index is not None:
+        out = x @ w[identity_index]
+    else:
+        out = torch.zeros(num_out, w.shape[-1], dtype=x.dtype)
+    for k in range(len(offsets) - 1):
+        if k == identity_index:
+            continue
+        s, e = int(offsets[k]), int(offsets[k + 1])
+        if e == s:
+            continue
+        out[out_maps[s:e]] += x[in_maps[s:e]] @ w[k]
+    return out.to(feats.dtype)
+
+
+def batchnorm_eval(x: torch.Tensor, weight, bias, running_mean, running_var, eps: float = 1e-5):
+    """``nn.BatchNorm1d`` in eval mode (the reference's BatchNorm wrapper,
+    warpconvnet/nn/modules/normalizations.py:49-63, applies it to the feature
+    tensor): per-channel affine from the running statistics."""
+    return torch.nn.functional.batch_norm(x, running_mean, running_var, weight, bias, False, 0.0, eps)
+
+
+# --------------------------------------------------------------------------- network
+
+
+class _Geom:
+    """Coordinates [N,4] (NumPy) + features (torch) + a per-network map cache
+    keyed like the reference's IntSearchCacheKey (kernel, transposed, in/out
+    per-batch counts; warpconvnet/geometry/coords/search/cache.py:84-142)."""
+
+    def __init__(self, coords, feats, cache):
+        self.coords, self.feats, self.cache = coords, feats, cache
+
+    def counts(self):
+        return tuple(np.bincount(self.coords[:, 0]).tolist())
+
+
+def _conv(g: _Geom, weight: torch.Tensor, kernel: int, stride: int = 1, transposed: bool = False,
+          out_geom: Optional[_Geom] = None) -> _Geom:
+    """``spatially_sparse_conv`` (warpconvnet/nn/functional/sparse_conv.py:1662-1805),
+    explicit-GEMM algorithm, STRIDE_ONLY mode."""
+    if kernel == 1 and stride == 1:
+        return _Geom(g.coords, g.feats @ weight[0], g.cache)  # :1714-1721
+    ks, st = (kernel,) * 3, (stride,) * 3
+    if transposed:
+        out_coords = out_geom.coords
+        key = ("T", ks, g.counts(), out_geom.counts())
+        if key not in g.cache:
+            fkey = ("F", ks, out_geom.counts(), g.counts())
+            if fkey in g.cache:  # :1916-1939: forward map with in/out swapped
+                fi, fo, fofs, _ = g.cache[fkey]
+                g.cache[key] = (fo, fi, fofs, None)
+            else:
+                g.cache[key] = km.transposed_kernel_map(g.coords, out_coords, st, ks)
+    else:
+        out_coords = g.coords if stride == 1 else km.stride_coords(g.coords, st)[0]
+        key = ("F", ks, g.counts(), tuple(np.bincount(out_coords[:, 0]).tolist()))
+        if key not in g.cache:
+            g.cache[key] = km.generate_kernel_map(g.coords, out_coords, st, ks)
+    im, om, ofs, iden = g.cache[key]
+    out = explicit_gemm_forward(g.feats, weight, im, om, ofs, iden, len(out_coords))
+    return _Geom(out_coords, out, g.cache)
+
+
+def _bn(sd, prefix, x):
+    return batchnorm_eval(x, sd[prefix + ".weight"], sd[prefix + ".bias"], sd[prefix + ".running_mean"],
+                          sd[prefix + ".running_var"])
+
+
+def _conv_block(sd, prefix, g, kernel, stride=1, act=True):
+    # ConvBlock = SparseConv3d(bias=False) -> BatchNorm1d -> ReLU|Identity (examples/mink_unet.py:25-47)
+    g = _conv(g, sd[prefix + ".0.weight"], kernel, stride)
+    x = _bn(sd, prefix + ".1", g.feats)
+    return _Geom(g.coords, torch.relu(x) if act else x, g.cache)
+
+
+def _basic_block(sd, prefix, g):
+    # BasicBlock (examples/mink_unet.py:86-141)
+    out = _conv_block(sd, prefix + ".conv1", g, 3)
+    out = _conv_block(sd, prefix + ".conv2", out, 3, act=False)
+    identity = g
+    if (prefix + ".downsample.0.weight") in sd:
+        identity = _conv_block(sd, prefix + ".downsample", g, 1, act=False)
+    return _Geom(out.coords, torch.relu(out.feats + identity.feats), g.cache)
+
+
+def _conv_tr_block(sd, prefix, g, skip):
+    # ConvTrBlock (examples/mink_unet.py:50-83)
+    out = _conv(g, sd[prefix + ".conv_tr.weight"], 2, 2, transposed=True, out_geom=skip)
+    return _Geom(out.coords, torch.relu(_bn(sd, prefix + ".norm_act.0", out.feats)), g.cache)
+
+
+def minkunet_forward(state_dict: Dict[str, torch.Tensor], coords: np.ndarray, feats: torch.Tensor,
+                     layers: Sequence[int] = (2, 3, 4, 6, 2, 2, 2, 2)) -> torch.Tensor:
+    """MinkUNet forward (examples/mink_unet.py:324-361) on CPU tensors from a
+    ``state_dict`` whose parameter names follow the reference model."""
+    sd = {k: v.detach().to("cpu") for k, v in state_dict.items()}
+    dtype = feats.dtype
+    sd = {k: (v.to(dtype) if v.is_floating_point() else v) for k, v in sd.items()}
+    g = _Geom(np.ascontiguousarray(coords, dtype=np.int32), feats, {})
+
+    def blocks(name, g, n):
+        for i in range(n):
+            g = _basic_block(sd, f"{name}.{i}", g)
+        return g
+
+    out_p1 = _conv_block(sd, "conv0", g, 1)
+    out = _conv_block(sd, "conv1", out_p1, 2, 2)
+    out_b1p2 = blocks("block1", out, layers[0])
+    out = _conv_block(sd, "conv2", out_b1p2, 2, 2)
+    out_b2p4 = blocks("block2", out, layers[1])
+    out = _conv_block(sd, "conv3", out_b2p4, 2, 2)
+    out_b3p8 = blocks("block3", out, layers[2])
+    out = _conv_block(sd, "conv4", out_b3p8, 2, 2)
+    out = blocks("block4", out, layers[3])
+
+    def up(name, block, out, skip, n):
+        out = _conv_tr_block(sd, name, out, skip)
+        out = _Geom(out.coords, torch.cat([out.feats, skip.feats], dim=-1), out.cache)
+        return blocks(block, out, n)
+
+    out = up("convtr4", "block5", out, out_b3p8, layers[4])
+    out = up("convtr5", "block6", out, out_b2p4, layers[5])
+    out = up("convtr6", "block7", out, out_b1p2, layers[6])
+    out = up("convtr7", "block8", out, out_p1, layers[7])
+    return out.feats @ sd["final.weight"][0] + sd["final.bias"]

@@ -1,0 +1,131 @@
+"""ctypes binding of ``csrc/libwcn_b200.so`` (declared in ``include/wcn_b200.h``).
+
+The library is the only compute back-end of this package: when it is missing
+or cannot be loaded, every operation raises; there is no CPU or eager fallback.
+PyTorch is used for device memory and streams only.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from typing import Optional
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "csrc", "libwcn_b200.so")
+
+WCN_F32, WCN_F16, WCN_BF16 = 0, 1, 2
+CONV_AUTO, CONV_SIMT, CONV_TCGEN05 = 0, 1, 2
+_DTYPE_CODE = {torch.float32: WCN_F32, torch.float16: WCN_F16, torch.bfloat16: WCN_BF16}
+
+_c_i32, _c_i64, _c_vp = ctypes.c_int32, ctypes.c_int64, ctypes.c_void_p
+_p_i64 = ctypes.POINTER(ctypes.c_int64)
+
+# name -> argument types, exactly the prototypes of include/wcn_b200.h
+SIGNATURES = {
+    "wcn_version": [],
+    "wcn_hash_table_bytes": [_c_i64, _p_i64],
+    "wcn_hash_build": [_c_vp, _c_i64, _c_vp, _c_vp, _c_i64, _c_i32, _c_vp, _c_vp],
+    "wcn_hash_search": [_c_vp, _c_i64, _c_i32, _c_vp, _c_i64, _c_vp, _c_vp],
+    "wcn_unique_workspace_bytes": [_c_i64, _p_i64],
+    "wcn_unique_mark": [_c_vp, _c_i64, _c_vp, _c_vp, _c_i64, _c_i32, _c_vp, _c_vp, _c_vp],
+    "wcn_unique_emit": [_c_vp, _c_i64, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp],
+    "wcn_kmap_workspace_bytes": [_c_i64, _c_i32, _p_i64],
+    "wcn_kmap_search": [_c_vp, _c_i64, _c_i32, _c_vp, _c_i64, _c_vp, _c_vp, _c_i32, _c_vp, _c_vp, _c_vp],
+    "wcn_kmap_scan": [_c_vp, _c_i64, _c_i32, _c_vp, _c_vp],
+    "wcn_kmap_compact": [_c_vp, _c_i64, _c_i32, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp],
+    "wcn_nbr_from_maps": [_c_vp, _c_vp, _c_vp, _c_i32, _c_i64, _c_i64, _c_vp, _c_vp],
+    "wcn_nbr_transpose": [_c_vp, _c_i32, _c_i64, _c_i64, _c_vp, _c_vp],
+    "wcn_morton20": [_c_vp, _c_i64, _c_i32, _c_i32, _c_vp, _c_vp, _c_vp],
+    "wcn_gather_rows": [_c_vp, _c_vp, _c_vp, _c_i64, _c_i32, _c_i32, _c_vp],
+    "wcn_scatter_add_rows": [_c_vp, _c_vp, _c_vp, _c_i64, _c_i32, _c_i32, _c_vp],
+    "wcn_conv_packed_weight_bytes": [_c_i32, _c_i32, _c_i32, _c_i32, _c_i32, _p_i64],
+    "wcn_conv_pack_weight": [_c_i32, _c_vp, _c_i32, _c_i32, _c_i32, _c_i32, _c_vp, _c_vp],
+    "wcn_conv_fwd": [_c_i32, _c_vp, _c_i64, _c_vp, _c_vp, _c_vp, _c_i64, _c_i32, _c_i32, _c_i32, _c_i32,
+                     _c_vp, _c_vp, _c_vp, _c_i32, _c_vp, _c_i32, _c_vp, _c_vp],
+}
+
+_lib: Optional[ctypes.CDLL] = None
+
+
+class NativeLibraryError(RuntimeError):
+    pass
+
+
+def lib() -> ctypes.CDLL:
+    """The loaded library; raises NativeLibraryError when it is not built."""
+    global _lib
+    if _lib is None:
+        if not os.path.isfile(LIB_PATH):
+            raise NativeLibraryError(
+                f"{LIB_PATH} is missing: build it with `python -m warpconvnet_b200.csrc.build` "
+                "(nvcc, sm_100a). This package has no fallback path.")
+        try:
+            handle = ctypes.CDLL(LIB_PATH)
+        except OSError as e:  # pragma: no cover
+            raise NativeLibraryError(f"cannot load {LIB_PATH}: {e}") from e
+        for name, argtypes in SIGNATURES.items():
+            fn = getattr(handle, name)
+            fn.argtypes = argtypes
+            fn.restype = ctypes.c_int
+        handle.wcn_status_string.argtypes = [ctypes.c_int]
+        handle.wcn_status_string.restype = ctypes.c_char_p
+        _lib = handle
+    return _lib
+
+
+def status_string(status: int) -> str:
+    return lib().wcn_status_string(int(status)).decode()
+
+
+def check(status: int, what: str = "") -> None:
+    if status != 0:
+        raise RuntimeError(f"libwcn_b200 {what} failed: {status_string(status)} ({status})")
+
+
+def ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def stream_ptr(device: torch.device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def dtype_code(dtype: torch.dtype) -> int:
+    try:
+        return _DTYPE_CODE[dtype]
+    except KeyError:
+        raise TypeError(f"unsupported feature dtype {dtype}; expected float32, float16 or bfloat16")
+
+
+def require_cuda(t: torch.Tensor, name: str) -> None:
+    if not t.is_cuda:
+        raise ValueError(f"{name} must be on a CUDA device, got {t.device}")
+
+
+_status_words = {}
+
+
+def device_status(device: torch.device) -> torch.Tensor:
+    """Per-device int32 status word shared by all kernels that can fail on the device."""
+    device = torch.device(device)
+    key = (device.type, device.index if device.index is not None else torch.cuda.current_device())
+    if key not in _status_words:
+        _status_words[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _status_words[key]
+
+
+def check_device_status(device: torch.device) -> None:
+    """Read the status word (synchronises) and raise if a kernel recorded a failure."""
+    word = device_status(device)
+    code = int(word.item())
+    if code != 0:
+        word.zero_()
+        raise RuntimeError(f"libwcn_b200 kernel reported: {status_string(code)} ({code})")
+
+
+def query_bytes(fn_name: str, *args) -> int:
+    out = ctypes.c_int64(0)
+    check(getattr(lib(), fn_name)(*args, ctypes.byref(out)), fn_name)
+    return int(out.value)

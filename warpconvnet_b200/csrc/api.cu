@@ -1,0 +1,74 @@
+// Entry points that do not belong to one kernel family: version, status text and
+// the convolution dispatcher.
+#include "wcn_common.cuh"
+
+// conv_simt.cu
+int wcn_conv_simt_fwd(const void* feats, const void* weight, const int32_t* nbr, int64_t M, int K, int c_in,
+                      int c_out, int dtype, const float* scale, const float* shift, const void* residual,
+                      int relu, void* out, int out_dtype, cudaStream_t st);
+// conv_tcgen05.cu
+bool wcn_conv_tcgen05_supported(int K, int c_in, int c_out, int dtype, int out_dtype);
+int64_t wcn_conv_tcgen05_packed_bytes(int K, int c_in, int c_out);
+int wcn_conv_tcgen05_pack(const void* weight, int K, int c_in, int c_out, void* packed, cudaStream_t st);
+int wcn_conv_tcgen05_fwd(const void* feats, const void* packed, const int32_t* nbr, int64_t M, int K, int c_in,
+                         int c_out, int dtype, const float* scale, const float* shift, const void* residual,
+                         int relu, void* out, int out_dtype, int32_t* dev_status, cudaStream_t st);
+
+extern "C" int wcn_version(void) { return 100; }
+
+extern "C" const char* wcn_status_string(int status) {
+  switch (status) {
+    case WCN_OK: return "success";
+    case WCN_ERR_PROBLEM_NOT_SUPPORTED: return "problem not supported";
+    case WCN_ERR_INITIALIZATION: return "kernel initialization failed";
+    case WCN_ERR_EXECUTION: return "kernel launch or execution failed";
+    case WCN_ERR_UNSUPPORTED_CONFIG: return "unsupported configuration";
+    case WCN_ERR_INVALID_PARAMETERS: return "invalid parameters";
+    case WCN_ERR_HASH_OVERFLOW: return "hash table overflow";
+    case WCN_ERR_WAIT_EXPIRED: return "a bounded device-side wait expired";
+    case WCN_ERR_BOUNDS: return "index out of bounds";
+    default: return "unknown status";
+  }
+}
+
+extern "C" int wcn_conv_packed_weight_bytes(int algo, int32_t num_offsets, int32_t c_in, int32_t c_out,
+                                            int dtype, int64_t* bytes) {
+  if (!bytes || num_offsets <= 0 || c_in <= 0 || c_out <= 0) return WCN_ERR_INVALID_PARAMETERS;
+  *bytes = 0;
+  if (algo == WCN_CONV_SIMT) return WCN_OK;
+  const bool ok = wcn_conv_tcgen05_supported(num_offsets, c_in, c_out, dtype, dtype);
+  if (!ok) return algo == WCN_CONV_TCGEN05 ? WCN_ERR_UNSUPPORTED_CONFIG : WCN_OK;
+  *bytes = wcn_conv_tcgen05_packed_bytes(num_offsets, c_in, c_out);
+  return WCN_OK;
+}
+
+extern "C" int wcn_conv_pack_weight(int algo, const void* weight, int32_t num_offsets, int32_t c_in,
+                                    int32_t c_out, int dtype, void* packed, void* stream) {
+  if (!weight || !packed) return WCN_ERR_INVALID_PARAMETERS;
+  if (algo == WCN_CONV_SIMT || !wcn_conv_tcgen05_supported(num_offsets, c_in, c_out, dtype, dtype))
+    return WCN_ERR_UNSUPPORTED_CONFIG;
+  return wcn_conv_tcgen05_pack(weight, num_offsets, c_in, c_out, packed, wcn_stream(stream));
+}
+
+extern "C" int wcn_conv_fwd(int algo, const void* feats, int64_t num_in, const void* weight,
+                            const void* packed_weight, const int32_t* nbr, int64_t num_out,
+                            int32_t num_offsets, int32_t c_in, int32_t c_out, int dtype, const float* scale,
+                            const float* shift, const void* residual, int relu, void* out, int out_dtype,
+                            int32_t* dev_status, void* stream) {
+  if (num_in < 0 || num_out < 0 || num_offsets <= 0 || c_in <= 0 || c_out <= 0) return WCN_ERR_INVALID_PARAMETERS;
+  if (dtype < WCN_F32 || dtype > WCN_BF16 || out_dtype < WCN_F32 || out_dtype > WCN_BF16)
+    return WCN_ERR_INVALID_PARAMETERS;
+  if (num_out == 0) return WCN_OK;
+  if (!nbr || !out || (num_in > 0 && !feats)) return WCN_ERR_INVALID_PARAMETERS;
+  cudaStream_t st = wcn_stream(stream);
+  const bool tc_ok = wcn_conv_tcgen05_supported(num_offsets, c_in, c_out, dtype, out_dtype);
+  if (algo == WCN_CONV_TCGEN05 || (algo == WCN_CONV_AUTO && tc_ok && packed_weight && dev_status)) {
+    if (!tc_ok) return WCN_ERR_UNSUPPORTED_CONFIG;
+    return wcn_conv_tcgen05_fwd(feats, packed_weight, nbr, num_out, num_offsets, c_in, c_out, dtype, scale, shift,
+                                residual, relu, out, out_dtype, dev_status, st);
+  }
+  if (algo != WCN_CONV_SIMT && algo != WCN_CONV_AUTO) return WCN_ERR_INVALID_PARAMETERS;
+  if (!weight) return WCN_ERR_INVALID_PARAMETERS;
+  return wcn_conv_simt_fwd(feats, weight, nbr, num_out, num_offsets, c_in, c_out, dtype, scale, shift, residual,
+                           relu, out, out_dtype, st);
+}

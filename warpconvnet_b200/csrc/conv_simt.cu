@@ -1,0 +1,121 @@
+// Output-stationary sparse convolution on the FP32 pipes.  This is the kernel
+// for fp32 tensors (where tensor-core formats would lose the 1e-4 accuracy
+// bound) and for shapes the tcgen05 kernel does not take.  One block owns a
+// 64-row x 64-column output tile, walks the kernel offsets that have at least
+// one neighbour in the tile, gathers the neighbour rows into shared memory and
+// accumulates in fp32 registers; every output element is written once.
+#include "wcn_common.cuh"
+
+namespace {
+
+constexpr int TM = 64;   // output rows per block
+constexpr int TN = 64;   // output columns per block
+constexpr int TK = 16;   // input channels per step
+constexpr int NT = 256;  // threads: 16 x 16, each a 4 x 4 micro-tile
+
+template <typename T, typename TO>
+__global__ void __launch_bounds__(NT)
+conv_simt_kernel(const T* __restrict__ feats, const T* __restrict__ weight, const int32_t* __restrict__ nbr,
+                 int64_t M, int K, int c_in, int c_out, const float* __restrict__ scale,
+                 const float* __restrict__ shift, const TO* __restrict__ residual, int relu,
+                 TO* __restrict__ out) {
+  __shared__ float As[TK][TM + 4];
+  __shared__ float Ws[TK][TN + 4];
+  __shared__ int rows[TM];
+
+  const int64_t m0 = (int64_t)blockIdx.x * TM;
+  const int n0 = blockIdx.y * TN;
+  const int tx = threadIdx.x & 15;  // column group
+  const int ty = threadIdx.x >> 4;  // row group
+  float acc[4][4] = {};
+
+  for (int k = 0; k < K; ++k) {
+    int r = -1;
+    if (threadIdx.x < TM) {
+      const int64_t m = m0 + threadIdx.x;
+      r = m < M ? __ldg(&nbr[(int64_t)k * M + m]) : -1;
+      rows[threadIdx.x] = r;
+    }
+    if (!__syncthreads_or(r >= 0)) continue;  // no neighbour at this offset in the tile
+    const T* wk = weight + (int64_t)k * c_in * c_out;
+    for (int c0 = 0; c0 < c_in; c0 += TK) {
+      // A: TM x TK gathered rows (zero where the neighbour is absent)
+#pragma unroll
+      for (int e = threadIdx.x; e < TM * TK; e += NT) {
+        const int rr = e / TK, cc = e % TK;
+        const int src = rows[rr];
+        float v = 0.f;
+        if (src >= 0 && c0 + cc < c_in) v = wcn_to_float<T>(feats[(int64_t)src * c_in + c0 + cc]);
+        As[cc][rr] = v;
+      }
+      // W: TK x TN slice of weight[k]
+#pragma unroll
+      for (int e = threadIdx.x; e < TK * TN; e += NT) {
+        const int cc = e / TN, nn = e % TN;
+        float v = 0.f;
+        if (c0 + cc < c_in && n0 + nn < c_out) v = wcn_to_float<T>(wk[(int64_t)(c0 + cc) * c_out + n0 + nn]);
+        Ws[cc][nn] = v;
+      }
+      __syncthreads();
+#pragma unroll
+      for (int cc = 0; cc < TK; ++cc) {
+        float a[4], b[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) a[i] = As[cc][ty * 4 + i];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) b[j] = Ws[cc][tx * 4 + j];
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+      }
+      __syncthreads();
+    }
+  }
+
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int64_t m = m0 + ty * 4 + i;
+    if (m >= M) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = n0 + tx * 4 + j;
+      if (n >= c_out) continue;
+      float y = acc[i][j];
+      if (scale) y *= scale[n];
+      if (shift) y += shift[n];
+      if (residual) y += wcn_to_float<TO>(residual[m * c_out + n]);
+      if (relu) y = fmaxf(y, 0.f);
+      out[m * c_out + n] = wcn_from_float<TO>(y);
+    }
+  }
+}
+
+template <typename T, typename TO>
+int launch_simt(const void* feats, const void* weight, const int32_t* nbr, int64_t M, int K, int c_in,
+                int c_out, const float* scale, const float* shift, const void* residual, int relu, void* out,
+                cudaStream_t st) {
+  dim3 grid((unsigned)((M + TM - 1) / TM), (unsigned)((c_out + TN - 1) / TN));
+  conv_simt_kernel<T, TO><<<grid, NT, 0, st>>>((const T*)feats, (const T*)weight, nbr, M, K, c_in, c_out, scale,
+                                              shift, (const TO*)residual, relu, (TO*)out);
+  return cudaGetLastError() == cudaSuccess ? WCN_OK : WCN_ERR_EXECUTION;
+}
+
+}  // namespace
+
+int wcn_conv_simt_fwd(const void* feats, const void* weight, const int32_t* nbr, int64_t M, int K, int c_in,
+                      int c_out, int dtype, const float* scale, const float* shift, const void* residual,
+                      int relu, void* out, int out_dtype, cudaStream_t st) {
+#define WCN_SIMT_CASE(DT, T, ODT, TO) \
+  if (dtype == DT && out_dtype == ODT) \
+    return launch_simt<T, TO>(feats, weight, nbr, M, K, c_in, c_out, scale, shift, residual, relu, out, st);
+  WCN_SIMT_CASE(WCN_F32, float, WCN_F32, float)
+  WCN_SIMT_CASE(WCN_F16, __half, WCN_F16, __half)
+  WCN_SIMT_CASE(WCN_BF16, __nv_bfloat16, WCN_BF16, __nv_bfloat16)
+  WCN_SIMT_CASE(WCN_F16, __half, WCN_F32, float)
+  WCN_SIMT_CASE(WCN_BF16, __nv_bfloat16, WCN_F32, float)
+  WCN_SIMT_CASE(WCN_F32, float, WCN_F16, __half)
+  WCN_SIMT_CASE(WCN_F32, float, WCN_BF16, __nv_bfloat16)
+#undef WCN_SIMT_CASE
+  return WCN_ERR_UNSUPPORTED_CONFIG;
+}

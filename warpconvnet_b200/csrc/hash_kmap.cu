@@ -1,0 +1,523 @@
+// Coordinate hash table, distinct/strided coordinates, kernel-map generation and
+// Morton code.  All of it is integer, bandwidth-bound work: one 16-byte key per
+// slot so a probe is one 32-byte sector, coalesced int4 query loads, warp-ballot
+// compaction, no host synchronisation inside the library.
+#include "wcn_common.cuh"
+
+namespace {
+
+constexpr int kThreads = 256;
+
+// ------------------------------------------------------------------ 128-bit CAS
+
+__device__ __forceinline__ int4 cas128(int4* addr, int4 cmp, int4 val) {
+  unsigned long long clo = ((unsigned long long)(uint32_t)cmp.y << 32) | (uint32_t)cmp.x;
+  unsigned long long chi = ((unsigned long long)(uint32_t)cmp.w << 32) | (uint32_t)cmp.z;
+  unsigned long long vlo = ((unsigned long long)(uint32_t)val.y << 32) | (uint32_t)val.x;
+  unsigned long long vhi = ((unsigned long long)(uint32_t)val.w << 32) | (uint32_t)val.z;
+  unsigned long long olo, ohi;
+  asm volatile(
+      "{\n\t"
+      ".reg .b128 c, v, o;\n\t"
+      "mov.b128 c, {%2, %3};\n\t"
+      "mov.b128 v, {%4, %5};\n\t"
+      "atom.global.relaxed.gpu.cas.b128 o, [%6], c, v;\n\t"
+      "mov.b128 {%0, %1}, o;\n\t"
+      "}"
+      : "=l"(olo), "=l"(ohi)
+      : "l"(clo), "l"(chi), "l"(vlo), "l"(vhi), "l"(addr)
+      : "memory");
+  int4 old;
+  old.x = (int)(uint32_t)olo;
+  old.y = (int)(uint32_t)(olo >> 32);
+  old.z = (int)(uint32_t)ohi;
+  old.w = (int)(uint32_t)(ohi >> 32);
+  return old;
+}
+
+__device__ __forceinline__ int4 load_key(const int32_t* __restrict__ keys, int64_t i, int sx, int sy,
+                                         int sz) {
+  int4 k = __ldg(reinterpret_cast<const int4*>(keys) + i);
+  if (sx != 1) k.y = wcn_floordiv(k.y, sx);
+  if (sy != 1) k.z = wcn_floordiv(k.z, sy);
+  if (sz != 1) k.w = wcn_floordiv(k.w, sz);
+  return k;
+}
+
+// ------------------------------------------------------------------ table build / search
+
+__global__ void hash_clear_kernel(int4* tkeys, int* tvals, int64_t cap) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < cap) {
+    tkeys[i] = make_int4(WCN_EMPTY_BATCH, 0, 0, 0);
+    tvals[i] = INT_MAX;
+  }
+}
+
+template <int METHOD>
+__global__ void hash_insert_kernel(const int32_t* __restrict__ keys, int64_t n, int sx, int sy, int sz,
+                                   int4* tkeys, int* tvals, uint32_t cap, int32_t* dev_status) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int4 key = load_key(keys, i, sx, sy, sz);
+  const int4 empty = make_int4(WCN_EMPTY_BATCH, 0, 0, 0);
+  uint32_t slot = wcn_slot(wcn_hash4<METHOD>(key), cap);
+  for (uint32_t p = 0; p < cap; ++p) {
+    int4 cur = __ldcg(&tkeys[slot]);
+    if (cur.x == WCN_EMPTY_BATCH) cur = cas128(&tkeys[slot], empty, key);
+    if (cur.x == WCN_EMPTY_BATCH || wcn_key_eq(cur, key)) {
+      atomicMin(&tvals[slot], (int)i);  // smallest row index wins: deterministic
+      return;
+    }
+    slot = (slot + 1 == cap) ? 0u : slot + 1;
+  }
+  if (dev_status) atomicMin(dev_status, (int)WCN_ERR_HASH_OVERFLOW);
+}
+
+template <int METHOD>
+__global__ void hash_search_kernel(const int4* __restrict__ tkeys, const int* __restrict__ tvals,
+                                   uint32_t cap, const int32_t* __restrict__ queries, int64_t nq,
+                                   int32_t* __restrict__ results) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= nq) return;
+  const int4 q = __ldg(reinterpret_cast<const int4*>(queries) + i);
+  results[i] = wcn_lookup<METHOD>(tkeys, tvals, cap, q);
+}
+
+// ------------------------------------------------------------------ block scan helpers
+
+// Exclusive prefix of `v` over the block (blockDim.x <= 1024, multiple of 32);
+// the block total is returned through `total` (valid in every thread).
+__device__ __forceinline__ int block_exclusive_scan(int v, int* total) {
+  __shared__ int warp_sums[32];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  int incl = v;
+#pragma unroll
+  for (int d = 1; d < 32; d <<= 1) {
+    int t = __shfl_up_sync(0xFFFFFFFFu, incl, d);
+    if (lane >= d) incl += t;
+  }
+  if (lane == 31) warp_sums[warp] = incl;
+  __syncthreads();
+  if (warp == 0) {
+    int w = lane < nwarps ? warp_sums[lane] : 0;
+    int wi = w;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      int t = __shfl_up_sync(0xFFFFFFFFu, wi, d);
+      if (lane >= d) wi += t;
+    }
+    warp_sums[lane] = wi - w;  // exclusive prefix of warp sums
+  }
+  __syncthreads();
+  int result = incl - v + warp_sums[warp];
+  __shared__ int block_total;  // = exclusive prefix of the last thread + its value
+  if (threadIdx.x == blockDim.x - 1) block_total = result + v;
+  __syncthreads();
+  *total = block_total;
+  return result;
+}
+
+// In-place exclusive scan of each row of data[rows, len]; totals[row] = row sum.
+__global__ void scan_rows_kernel(int* data, int64_t len, int* totals) {
+  int* row = data + (int64_t)blockIdx.x * len;
+  int carry = 0;
+  for (int64_t base = 0; base < len; base += blockDim.x) {
+    int64_t i = base + threadIdx.x;
+    int v = i < len ? row[i] : 0;
+    int total;
+    int ex = block_exclusive_scan(v, &total);
+    if (i < len) row[i] = carry + ex;
+    carry += total;
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) totals[blockIdx.x] = carry;
+}
+
+__global__ void offsets_from_totals_kernel(const int* totals, int rows, int32_t* offsets) {
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    int acc = 0;
+    offsets[0] = 0;
+    for (int k = 0; k < rows; ++k) {
+      acc += totals[k];
+      offsets[k + 1] = acc;
+    }
+  }
+}
+
+// ------------------------------------------------------------------ distinct rows
+
+struct UniqueWs {
+  int* rep;           // [n] row index of the first occurrence of each row's key
+  int* rank_of;       // [n] output position of a first-occurrence row
+  int* block_counts;  // [nblk] then scanned in place
+  int* total;         // [1]
+  int64_t nblk;
+};
+
+__host__ __device__ inline int64_t unique_nblk(int64_t n) { return (n + kThreads - 1) / kThreads; }
+
+inline UniqueWs unique_ws(void* ws, int64_t n) {
+  UniqueWs w;
+  w.nblk = unique_nblk(n);
+  w.rep = reinterpret_cast<int*>(ws);
+  w.rank_of = w.rep + n;
+  w.block_counts = w.rank_of + n;
+  w.total = w.block_counts + w.nblk;
+  return w;
+}
+
+template <int METHOD>
+__global__ void unique_mark_kernel(const int32_t* __restrict__ coords, int64_t n, int sx, int sy, int sz,
+                                   const int4* __restrict__ tkeys, const int* __restrict__ tvals,
+                                   uint32_t cap, int* __restrict__ rep, int* __restrict__ block_counts) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  int first = 0;
+  if (i < n) {
+    const int4 key = load_key(coords, i, sx, sy, sz);
+    const int r = wcn_lookup<METHOD>(tkeys, tvals, cap, key);
+    rep[i] = r;
+    first = (r == (int)i);
+  }
+  int c = __syncthreads_count(first);
+  if (threadIdx.x == 0) block_counts[blockIdx.x] = c;
+}
+
+__global__ void store_total_kernel(const int* total, int64_t* out) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) *out = (int64_t)(*total);
+}
+
+__global__ void unique_emit_kernel(const int32_t* __restrict__ coords, int64_t n, int sx, int sy, int sz,
+                                   const int* __restrict__ rep, const int* __restrict__ block_prefix,
+                                   int* __restrict__ rank_of, int32_t* __restrict__ out_coords,
+                                   int32_t* __restrict__ unique_index) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const bool first = (i < n) && (rep[i] == (int)i);
+  int total;
+  const int ex = block_exclusive_scan(first ? 1 : 0, &total);
+  if (first) {
+    const int pos = block_prefix[blockIdx.x] + ex;
+    rank_of[i] = pos;
+    reinterpret_cast<int4*>(out_coords)[pos] = load_key(coords, i, sx, sy, sz);
+    if (unique_index) unique_index[pos] = (int)i;
+  }
+}
+
+__global__ void unique_parent_kernel(int64_t n, const int* __restrict__ rep, const int* __restrict__ rank_of,
+                                     int32_t* __restrict__ parent) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) {
+    const int r = rep[i];
+    parent[i] = r >= 0 ? rank_of[r] : -1;
+  }
+}
+
+// ------------------------------------------------------------------ kernel map
+
+struct KernelGeom {
+  int sx, sy, sz;  // multiply output coordinates by this
+  int kx, ky, kz;
+  int cx, cy, cz;  // centre: size/2 for odd sizes, 0 for even
+};
+
+// One thread per (query m, offset k); m runs along the warp so the query load
+// and the nbr store are coalesced.  grid = (ceil(M/256), K).
+template <int METHOD>
+__global__ void kmap_search_kernel(const int4* __restrict__ tkeys, const int* __restrict__ tvals,
+                                   uint32_t cap, const int32_t* __restrict__ queries, int64_t M,
+                                   KernelGeom g, int32_t* __restrict__ nbr,
+                                   int* __restrict__ block_counts) {
+  const int k = blockIdx.y;
+  const int64_t m = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  int found = -1;
+  if (m < M) {
+    int4 q = __ldg(reinterpret_cast<const int4*>(queries) + m);
+    const int l = k % g.kz, j = (k / g.kz) % g.ky, i = k / (g.kz * g.ky);
+    q.y = q.y * g.sx + i - g.cx;
+    q.z = q.z * g.sy + j - g.cy;
+    q.w = q.w * g.sz + l - g.cz;
+    found = wcn_lookup<METHOD>(tkeys, tvals, cap, q);
+    nbr[(int64_t)k * M + m] = found;
+  }
+  const int c = __syncthreads_count(found >= 0);
+  if (threadIdx.x == 0) block_counts[(int64_t)k * gridDim.x + blockIdx.x] = c;
+}
+
+__global__ void kmap_compact_kernel(const int32_t* __restrict__ nbr, int64_t M,
+                                    const int* __restrict__ block_prefix,
+                                    const int32_t* __restrict__ offsets, int32_t* __restrict__ in_maps,
+                                    int32_t* __restrict__ out_maps) {
+  const int k = blockIdx.y;
+  const int64_t m = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int v = m < M ? __ldg(&nbr[(int64_t)k * M + m]) : -1;
+  int total;
+  const int ex = block_exclusive_scan(v >= 0 ? 1 : 0, &total);
+  if (v >= 0) {
+    const int64_t pos = (int64_t)offsets[k] + block_prefix[(int64_t)k * gridDim.x + blockIdx.x] + ex;
+    in_maps[pos] = v;
+    out_maps[pos] = (int32_t)m;
+  }
+}
+
+__global__ void nbr_from_maps_kernel(const int32_t* __restrict__ in_maps,
+                                     const int32_t* __restrict__ out_maps,
+                                     const int32_t* __restrict__ offsets, int K, int64_t L, int64_t M,
+                                     int32_t* __restrict__ nbr) {
+  const int64_t p = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (p >= L) return;
+  int lo = 0, hi = K;  // largest k with offsets[k] <= p
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if ((int64_t)__ldg(&offsets[mid]) <= p) lo = mid; else hi = mid;
+  }
+  const int32_t o = out_maps[p];
+  if (o >= 0 && o < M) nbr[(int64_t)lo * M + o] = in_maps[p];
+}
+
+__global__ void nbr_transpose_kernel(const int32_t* __restrict__ nbr_fwd, int64_t M, int64_t N,
+                                     int32_t* __restrict__ nbr_t) {
+  const int k = blockIdx.y;
+  const int64_t m = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (m >= M) return;
+  const int v = __ldg(&nbr_fwd[(int64_t)k * M + m]);
+  if (v >= 0 && v < N) nbr_t[(int64_t)k * N + v] = (int32_t)m;
+}
+
+// ------------------------------------------------------------------ Morton
+
+__device__ __forceinline__ unsigned long long spread3(unsigned long long n) {
+  n &= 0x1FFFFFull;
+  n = (n | (n << 32)) & 0x001F00000000FFFFull;
+  n = (n | (n << 16)) & 0x001F0000FF0000FFull;
+  n = (n | (n << 8)) & 0x100F00F00F00F00Full;
+  n = (n | (n << 4)) & 0x10C30C30C30C30C3ull;
+  n = (n | (n << 2)) & 0x1249249249249249ull;
+  return n;
+}
+
+__global__ void morton20_kernel(const int32_t* __restrict__ coords, int64_t n, int row_ints, int col0,
+                                int mx, int my, int mz, int64_t* __restrict__ codes) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int32_t* r = coords + i * row_ints + col0;
+  const unsigned long long x = (unsigned long long)(uint32_t)(r[0] - mx);
+  const unsigned long long y = (unsigned long long)(uint32_t)(r[1] - my);
+  const unsigned long long z = (unsigned long long)(uint32_t)(r[2] - mz);
+  codes[i] = (int64_t)(spread3(x) | (spread3(y) << 1) | (spread3(z) << 2));
+}
+
+inline unsigned grid_for(int64_t n) { return (unsigned)((n + kThreads - 1) / kThreads); }
+
+}  // namespace
+
+// ====================================================================== C ABI
+
+extern "C" int wcn_hash_table_bytes(int64_t capacity, int64_t* bytes) {
+  if (capacity <= 0 || !bytes) return WCN_ERR_INVALID_PARAMETERS;
+  *bytes = capacity * 20;
+  return WCN_OK;
+}
+
+#define WCN_DISPATCH_HASH(method, CALL)                         \
+  switch (method) {                                             \
+    case WCN_HASH_FNV1A: { constexpr int HM = WCN_HASH_FNV1A; CALL; } break;  \
+    case WCN_HASH_CITY: { constexpr int HM = WCN_HASH_CITY; CALL; } break;    \
+    case WCN_HASH_MURMUR: { constexpr int HM = WCN_HASH_MURMUR; CALL; } break; \
+    default: return WCN_ERR_INVALID_PARAMETERS;                 \
+  }
+
+static inline bool parse_stride(const int32_t* stride, int* sx, int* sy, int* sz) {
+  *sx = *sy = *sz = 1;
+  if (stride) {
+    *sx = stride[0]; *sy = stride[1]; *sz = stride[2];
+  }
+  return *sx > 0 && *sy > 0 && *sz > 0;
+}
+
+extern "C" int wcn_hash_build(const int32_t* keys, int64_t n, const int32_t* stride, void* table,
+                              int64_t capacity, int hash_method, int32_t* dev_status, void* stream) {
+  int sx, sy, sz;
+  if (!table || capacity <= 0 || capacity > 0x7FFFFFFFll || n < 0 || n > capacity || (n > 0 && !keys) ||
+      !parse_stride(stride, &sx, &sy, &sz))
+    return WCN_ERR_INVALID_PARAMETERS;
+  if ((reinterpret_cast<uintptr_t>(table) & 15) || (reinterpret_cast<uintptr_t>(keys) & 15))
+    return WCN_ERR_INVALID_PARAMETERS;
+  cudaStream_t st = wcn_stream(stream);
+  int4* tkeys = reinterpret_cast<int4*>(table);
+  int* tvals = reinterpret_cast<int*>(tkeys + capacity);
+  hash_clear_kernel<<<grid_for(capacity), kThreads, 0, st>>>(tkeys, tvals, capacity);
+  if (n > 0) {
+    WCN_DISPATCH_HASH(hash_method, (hash_insert_kernel<HM><<<grid_for(n), kThreads, 0, st>>>(
+                                       keys, n, sx, sy, sz, tkeys, tvals, (uint32_t)capacity, dev_status)));
+  }
+  WCN_CHECK_LAUNCH();
+  return WCN_OK;
+}
+
+extern "C" int wcn_hash_search(const void* table, int64_t capacity, int hash_method,
+                               const int32_t* queries, int64_t num_queries, int32_t* results,
+                               void* stream) {
+  if (!table || capacity <= 0 || capacity > 0x7FFFFFFFll || num_queries < 0) return WCN_ERR_INVALID_PARAMETERS;
+  if (num_queries == 0) return WCN_OK;
+  if (!queries || !results || (reinterpret_cast<uintptr_t>(queries) & 15)) return WCN_ERR_INVALID_PARAMETERS;
+  const int4* tkeys = reinterpret_cast<const int4*>(table);
+  const int* tvals = reinterpret_cast<const int*>(tkeys + capacity);
+  WCN_DISPATCH_HASH(hash_method, (hash_search_kernel<HM><<<grid_for(num_queries), kThreads, 0, wcn_stream(stream)>>>(
+                                     tkeys, tvals, (uint32_t)capacity, queries, num_queries, results)));
+  WCN_CHECK_LAUNCH();
+  return WCN_OK;
+}
+
+extern "C" int wcn_unique_workspace_bytes(int64_t n, int64_t* bytes) {
+  if (n < 0 || !bytes) return WCN_ERR_INVALID_PARAMETERS;
+  *bytes = ((2 * n + unique_nblk(n) + 16) * 4 + 255) / 256 * 256;
+  return WCN_OK;
+}
+
+extern "C" int wcn_unique_mark(const int32_t* coords, int64_t n, const int32_t* stride, const void* table,
+                               int64_t capacity, int hash_method, void* workspace, int64_t* num_unique,
+                               void* stream) {
+  int sx, sy, sz;
+  if (!table || !workspace || !num_unique || n < 0 || capacity <= 0 || capacity > 0x7FFFFFFFll ||
+      !parse_stride(stride, &sx, &sy, &sz))
+    return WCN_ERR_INVALID_PARAMETERS;
+  cudaStream_t st = wcn_stream(stream);
+  UniqueWs w = unique_ws(workspace, n);
+  if (n == 0) {
+    cudaMemsetAsync(num_unique, 0, sizeof(int64_t), st);
+    return WCN_OK;
+  }
+  if (!coords || (reinterpret_cast<uintptr_t>(coords) & 15)) return WCN_ERR_INVALID_PARAMETERS;
+  const int4* tkeys = reinterpret_cast<const int4*>(table);
+  const int* tvals = reinterpret_cast<const int*>(tkeys + capacity);
+  WCN_DISPATCH_HASH(hash_method, (unique_mark_kernel<HM><<<(unsigned)w.nblk, kThreads, 0, st>>>(
+                                     coords, n, sx, sy, sz, tkeys, tvals, (uint32_t)capacity, w.rep, w.block_counts)));
+  scan_rows_kernel<<<1, 1024, 0, st>>>(w.block_counts, w.nblk, w.total);
+  store_total_kernel<<<1, 32, 0, st>>>(w.total, num_unique);
+  WCN_CHECK_LAUNCH();
+  return WCN_OK;
+}
+
+extern "C" int wcn_unique_emit(const int32_t* coords, int64_t n, const int32_t* stride, void* workspace,
+                               int32_t* out_coords, int32_t* unique_index, int32_t* parent, void* stream) {
+  int sx, sy, sz;
+  if (!workspace || n < 0 || !parse_stride(stride, &sx, &sy, &sz)) return WCN_ERR_INVALID_PARAMETERS;
+  if (n == 0) return WCN_OK;
+  if (!coords || !out_coords || (reinterpret_cast<uintptr_t>(out_coords) & 15)) return WCN_ERR_INVALID_PARAMETERS;
+  cudaStream_t st = wcn_stream(stream);
+  UniqueWs w = unique_ws(workspace, n);
+  unique_emit_kernel<<<(unsigned)w.nblk, kThreads, 0, st>>>(coords, n, sx, sy, sz, w.rep, w.block_counts,
+                                                          w.rank_of, out_coords, unique_index);
+  if (parent) unique_parent_kernel<<<(unsigned)w.nblk, kThreads, 0, st>>>(n, w.rep, w.rank_of, parent);
+  WCN_CHECK_LAUNCH();
+  return WCN_OK;
+}
+
+extern "C" int wcn_kmap_workspace_bytes(int64_t num_queries, int32_t num_offsets, int64_t* bytes) {
+  if (num_queries < 0 || num_offsets <= 0 || !bytes) return WCN_ERR_INVALID_PARAMETERS;
+  const int64_t nblk = (num_queries + kThreads - 1) / kThreads;
+  *bytes = (((int64_t)num_offsets * nblk + num_offsets + 16) * 4 + 255) / 256 * 256;
+  return WCN_OK;
+}
+
+extern "C" int wcn_kmap_search(const void* table, int64_t capacity, int hash_method, const int32_t* queries,
+                               int64_t num_queries, const int32_t* stride, const int32_t* kernel_size,
+                               int32_t num_offsets, int32_t* nbr, void* workspace, void* stream) {
+  KernelGeom g;
+  if (!table || !kernel_size || !workspace || capacity <= 0 || capacity > 0x7FFFFFFFll || num_queries < 0 ||
+      !parse_stride(stride, &g.sx, &g.sy, &g.sz))
+    return WCN_ERR_INVALID_PARAMETERS;
+  g.kx = kernel_size[0]; g.ky = kernel_size[1]; g.kz = kernel_size[2];
+  if (g.kx <= 0 || g.ky <= 0 || g.kz <= 0) return WCN_ERR_INVALID_PARAMETERS;
+  const int K = g.kx * g.ky * g.kz;
+  if (num_offsets <= 0 || num_offsets > K || num_offsets > 65535) return WCN_ERR_INVALID_PARAMETERS;
+  g.cx = (g.kx & 1) ? g.kx / 2 : 0;
+  g.cy = (g.ky & 1) ? g.ky / 2 : 0;
+  g.cz = (g.kz & 1) ? g.kz / 2 : 0;
+  if (num_queries == 0) return WCN_OK;
+  if (!queries || !nbr || (reinterpret_cast<uintptr_t>(queries) & 15)) return WCN_ERR_INVALID_PARAMETERS;
+  const int4* tkeys = reinterpret_cast<const int4*>(table);
+  const int* tvals = reinterpret_cast<const int*>(tkeys + capacity);
+  dim3 grid(grid_for(num_queries), (unsigned)num_offsets);
+  WCN_DISPATCH_HASH(hash_method, (kmap_search_kernel<HM><<<grid, kThreads, 0, wcn_stream(stream)>>>(
+                                     tkeys, tvals, (uint32_t)capacity, queries, num_queries, g, nbr,
+                                     reinterpret_cast<int*>(workspace))));
+  WCN_CHECK_LAUNCH();
+  return WCN_OK;
+}
+
+extern "C" int wcn_kmap_scan(void* workspace, int64_t num_queries, int32_t num_offsets, int32_t* offsets,
+                             void* stream) {
+  if (!workspace || !offsets || num_queries < 0 || num_offsets <= 0) return WCN_ERR_INVALID_PARAMETERS;
+  cudaStream_t st = wcn_stream(stream);
+  const int64_t nblk = (num_queries + kThreads - 1) / kThreads;
+  int* counts = reinterpret_cast<int*>(workspace);
+  int* totals = counts + (int64_t)num_offsets * nblk;
+  if (nblk == 0) {
+    cudaMemsetAsync(offsets, 0, sizeof(int32_t) * (num_offsets + 1), st);
+    return WCN_OK;
+  }
+  scan_rows_kernel<<<(unsigned)num_offsets, 1024, 0, st>>>(counts, nblk, totals);
+  offsets_from_totals_kernel<<<1, 32, 0, st>>>(totals, num_offsets, offsets);
+  WCN_CHECK_LAUNCH();
+  return WCN_OK;
+}
+
+extern "C" int wcn_kmap_compact(const int32_t* nbr, int64_t num_queries, int32_t num_offsets,
+                                const void* workspace, const int32_t* offsets, int32_t* in_maps,
+                                int32_t* out_maps, void* stream) {
+  if (!workspace || !offsets || num_queries < 0 || num_offsets <= 0 || num_offsets > 65535)
+    return WCN_ERR_INVALID_PARAMETERS;
+  if (num_queries == 0) return WCN_OK;
+  if (!nbr || !in_maps || !out_maps) return WCN_ERR_INVALID_PARAMETERS;
+  dim3 grid(grid_for(num_queries), (unsigned)num_offsets);
+  kmap_compact_kernel<<<grid, kThreads, 0, wcn_stream(stream)>>>(nbr, num_queries,
+                                                               reinterpret_cast<const int*>(workspace), offsets,
+                                                               in_maps, out_maps);
+  WCN_CHECK_LAUNCH();
+  return WCN_OK;
+}
+
+extern "C" int wcn_nbr_from_maps(const int32_t* in_maps, const int32_t* out_maps, const int32_t* offsets,
+                                 int32_t num_offsets, int64_t num_pairs, int64_t num_out, int32_t* nbr,
+                                 void* stream) {
+  if (num_offsets <= 0 || num_pairs < 0 || num_out < 0 || !offsets) return WCN_ERR_INVALID_PARAMETERS;
+  if (num_out == 0) return WCN_OK;
+  if (!nbr) return WCN_ERR_INVALID_PARAMETERS;
+  cudaStream_t st = wcn_stream(stream);
+  cudaMemsetAsync(nbr, 0xFF, sizeof(int32_t) * (size_t)num_offsets * (size_t)num_out, st);
+  if (num_pairs > 0) {
+    if (!in_maps || !out_maps) return WCN_ERR_INVALID_PARAMETERS;
+    nbr_from_maps_kernel<<<grid_for(num_pairs), kThreads, 0, st>>>(in_maps, out_maps, offsets, num_offsets,
+                                                                  num_pairs, num_out, nbr);
+  }
+  WCN_CHECK_LAUNCH();
+  return WCN_OK;
+}
+
+extern "C" int wcn_nbr_transpose(const int32_t* nbr_fwd, int32_t num_offsets, int64_t num_out, int64_t num_in,
+                                 int32_t* nbr_t, void* stream) {
+  if (num_offsets <= 0 || num_offsets > 65535 || num_out < 0 || num_in < 0) return WCN_ERR_INVALID_PARAMETERS;
+  if (num_in == 0) return WCN_OK;
+  if (!nbr_t) return WCN_ERR_INVALID_PARAMETERS;
+  cudaStream_t st = wcn_stream(stream);
+  cudaMemsetAsync(nbr_t, 0xFF, sizeof(int32_t) * (size_t)num_offsets * (size_t)num_in, st);
+  if (num_out > 0) {
+    if (!nbr_fwd) return WCN_ERR_INVALID_PARAMETERS;
+    dim3 grid(grid_for(num_out), (unsigned)num_offsets);
+    nbr_transpose_kernel<<<grid, kThreads, 0, st>>>(nbr_fwd, num_out, num_in, nbr_t);
+  }
+  WCN_CHECK_LAUNCH();
+  return WCN_OK;
+}
+
+extern "C" int wcn_morton20(const int32_t* coords, int64_t n, int32_t row_ints, int32_t col0,
+                            const int32_t* min_xyz, int64_t* codes, void* stream) {
+  if (n < 0 || row_ints < 3 || col0 < 0 || col0 + 3 > row_ints) return WCN_ERR_INVALID_PARAMETERS;
+  if (n == 0) return WCN_OK;
+  if (!coords || !codes) return WCN_ERR_INVALID_PARAMETERS;
+  const int mx = min_xyz ? min_xyz[0] : 0, my = min_xyz ? min_xyz[1] : 0, mz = min_xyz ? min_xyz[2] : 0;
+  morton20_kernel<<<grid_for(n), kThreads, 0, wcn_stream(stream)>>>(coords, n, row_ints, col0, mx, my, mz, codes);
+  WCN_CHECK_LAUNCH();
+  return WCN_OK;
+}

@@ -1,0 +1,146 @@
+"""MinkUNet family on the sparse-convolution stack, with the layer structure and
+parameter names of the reference model (examples/mink_unet.py:25-141, 212-413):
+``ConvBlock`` = SparseConv3d(bias=False) -> BatchNorm1d -> ReLU, ``BasicBlock`` =
+two 3x3x3 ConvBlocks + (projected) identity + ReLU, ``ConvTrBlock`` = transposed
+2x2x2 stride-2 SparseConv3d -> BatchNorm1d -> ReLU, U-shaped encoder/decoder with
+skip concatenation and a biased 1x1x1 head.  A reference ``state_dict`` loads
+unchanged.  In eval mode every conv -> BN -> (+identity) -> ReLU run executes as
+one fused kernel.
+"""
+from __future__ import annotations
+
+from typing import Optional, Union
+
+import torch
+import torch.nn as nn
+
+from ..geometry.types.voxels import Voxels
+from ..nn.functional.sparse_conv import ConvEpilogue
+from ..nn.functional.transforms import cat
+from ..nn.modules.activations import ReLU
+from ..nn.modules.sequential import Sequential, fold_batchnorm
+from ..nn.modules.sparse_conv import SparseConv3d
+
+
+class ConvBlock(Sequential):
+    def __init__(self, in_channels: int, out_channels: int, kernel_size: int = 3, stride: int = 1,
+                 activation: Optional[nn.Module] = "relu", bias: bool = False,
+                 compute_dtype: Optional[torch.dtype] = None):
+        act = nn.ReLU(inplace=True) if activation == "relu" else (nn.Identity() if activation is None else activation)
+        super().__init__(
+            SparseConv3d(in_channels, out_channels, kernel_size, stride, bias=bias, compute_dtype=compute_dtype),
+            nn.BatchNorm1d(out_channels),
+            act,
+        )
+
+
+class ConvTrBlock(nn.Module):
+    def __init__(self, in_channels: int, out_channels: int, kernel_size: int = 3, stride: int = 1,
+                 activation: Optional[nn.Module] = "relu", bias: bool = False,
+                 compute_dtype: Optional[torch.dtype] = None):
+        super().__init__()
+        self.conv_tr = SparseConv3d(in_channels, out_channels, kernel_size, stride, transposed=True, bias=bias,
+                                    compute_dtype=compute_dtype)
+        act = nn.ReLU(inplace=True) if activation == "relu" else (nn.Identity() if activation is None else activation)
+        self.norm_act = Sequential(nn.BatchNorm1d(out_channels), act)
+
+    def forward(self, x: Voxels, out_spatial_sparsity: Voxels) -> Voxels:
+        bn = self.norm_act[0]
+        if not bn.training and not (torch.is_grad_enabled() and self.conv_tr.weight.requires_grad):
+            scale, shift = fold_batchnorm(bn)
+            ep = ConvEpilogue(scale=scale, shift=shift, relu=isinstance(self.norm_act[1], nn.ReLU))
+            return self.conv_tr(x, out_spatial_sparsity, epilogue=ep)
+        return self.norm_act(self.conv_tr(x, out_spatial_sparsity))
+
+
+class BasicBlock(nn.Module):
+    expansion = 1
+
+    def __init__(self, in_channels: int, out_channels: int, stride: int = 1, bias: bool = False,
+                 compute_dtype: Optional[torch.dtype] = None):
+        super().__init__()
+        self.conv1 = ConvBlock(in_channels, out_channels, kernel_size=3, stride=stride, bias=bias,
+                               compute_dtype=compute_dtype)
+        self.conv2 = ConvBlock(out_channels, out_channels, kernel_size=3, activation=None, bias=bias,
+                               compute_dtype=compute_dtype)
+        self.downsample = None
+        if stride != 1 or in_channels != out_channels:
+            self.downsample = ConvBlock(in_channels, out_channels, kernel_size=1, stride=stride, activation=None,
+                                        bias=bias, compute_dtype=compute_dtype)
+        self.relu = ReLU(inplace=True)
+
+    def forward(self, x: Voxels) -> Voxels:
+        identity = x if self.downsample is None else self.downsample(x)
+        out = self.conv1(x)
+        # out = relu(conv2(out) + identity): residual add and ReLU ride in conv2's epilogue
+        return self.conv2(out, residual=identity.feature_tensor, final_relu=True)
+
+
+class MinkUNetBase(nn.Module):
+    def __init__(self, in_channels: int, out_channels: int, planes, layers, init_dim: int = 32,
+                 BLOCK: Union[str, nn.Module] = BasicBlock, init_kernel_size: int = 1, **kwargs):
+        super().__init__()
+        assert len(planes) == len(layers)
+        self.PLANES, self.LAYERS, self.INIT_DIM = planes, layers, init_dim
+        self.conv0 = ConvBlock(in_channels, init_dim, kernel_size=init_kernel_size, bias=False)
+        self.conv1 = ConvBlock(init_dim, init_dim, kernel_size=2, stride=2)
+        self.block1 = self._make_layer(BLOCK, init_dim, planes[0], layers[0])
+        self.conv2 = ConvBlock(planes[0], planes[0], kernel_size=2, stride=2)
+        self.block2 = self._make_layer(BLOCK, planes[0], planes[1], layers[1])
+        self.conv3 = ConvBlock(planes[1], planes[1], kernel_size=2, stride=2)
+        self.block3 = self._make_layer(BLOCK, planes[1], planes[2], layers[2])
+        self.conv4 = ConvBlock(planes[2], planes[2], kernel_size=2, stride=2)
+        self.block4 = self._make_layer(BLOCK, planes[2], planes[3], layers[3])
+        self.convtr4 = ConvTrBlock(planes[3], planes[4], kernel_size=2, stride=2)
+        self.block5 = self._make_layer(BLOCK, planes[4] + planes[2], planes[4], layers[4])
+        self.convtr5 = ConvTrBlock(planes[4], planes[5], kernel_size=2, stride=2)
+        self.block6 = self._make_layer(BLOCK, planes[5] + planes[1], planes[5], layers[5])
+        self.convtr6 = ConvTrBlock(planes[5], planes[6], kernel_size=2, stride=2)
+        self.block7 = self._make_layer(BLOCK, planes[6] + planes[0], planes[6], layers[6])
+        self.convtr7 = ConvTrBlock(planes[6], planes[7], kernel_size=2, stride=2)
+        self.block8 = self._make_layer(BLOCK, planes[7] + planes[0], planes[7], layers[7])
+        self.final = SparseConv3d(planes[7], out_channels, kernel_size=1, bias=True)
+
+    @staticmethod
+    def _make_layer(BLOCK, in_channels: int, out_channels: int, blocks: int) -> nn.Sequential:
+        layers = [BLOCK(in_channels, out_channels)]
+        layers += [BLOCK(out_channels, out_channels) for _ in range(1, blocks)]
+        return nn.Sequential(*layers)
+
+    def forward(self, x: Voxels) -> Voxels:
+        out_p1 = self.conv0(x)
+        out_b1p2 = self.block1(self.conv1(out_p1))
+        out_b2p4 = self.block2(self.conv2(out_b1p2))
+        out_b3p8 = self.block3(self.conv3(out_b2p4))
+        out = self.block4(self.conv4(out_b3p8))
+        out = self.block5(cat(self.convtr4(out, out_b3p8), out_b3p8))
+        out = self.block6(cat(self.convtr5(out, out_b2p4), out_b2p4))
+        out = self.block7(cat(self.convtr6(out, out_b1p2), out_b1p2))
+        out = self.block8(cat(self.convtr7(out, out_p1), out_p1))
+        return self.final(out)
+
+
+class MinkUNet18(MinkUNetBase):
+    def __init__(self, in_channels: int, out_channels: int, **kwargs):
+        super().__init__(in_channels, out_channels, planes=(32, 64, 128, 256, 256, 128, 96, 96),
+                         layers=(2, 2, 2, 2, 2, 2, 2, 2), init_dim=32, BLOCK=BasicBlock, **kwargs)
+
+
+class MinkUNet34(MinkUNetBase):
+    def __init__(self, in_channels: int, out_channels: int, **kwargs):
+        super().__init__(in_channels, out_channels, planes=(32, 64, 128, 256, 256, 128, 96, 96),
+                         layers=(2, 3, 4, 6, 2, 2, 2, 2), init_dim=32, BLOCK=BasicBlock, **kwargs)
+
+
+@torch.no_grad()
+def randomize_batchnorm_(model: nn.Module, seed: int = 0) -> None:
+    """Seeded, non-trivial BatchNorm parameters and running statistics, so that an
+    eval-mode comparison exercises the folded scale/shift instead of an identity."""
+    g = torch.Generator().manual_seed(seed)
+    for m in model.modules():
+        if isinstance(m, nn.BatchNorm1d):
+            c = m.num_features
+            m.weight.copy_(torch.rand(c, generator=g) + 0.5)
+            m.bias.copy_(torch.randn(c, generator=g) * 0.1)
+            m.running_mean.copy_(torch.randn(c, generator=g) * 0.1)
+            m.running_var.copy_(torch.rand(c, generator=g) * 0.5 + 0.75)

@@ -1,0 +1,72 @@
+"""Strided (down-sampled) output coordinates (warpconvnet/geometry/coords/ops/stride.py:17-54).
+
+``floor(coords / stride)`` rows are made distinct through the hash table; the rows
+come out in first-occurrence order, which keeps a batch-sorted input batch-sorted
+and is the same on every run (the reference's order depends on insertion races
+and an unstable argsort; only the set of rows is comparable with it).
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional, Tuple
+
+import torch
+from torch import Tensor
+
+from ...._native import check, device_status, lib, ptr, query_bytes, stream_ptr
+from ....utils.ntuple import ntuple
+from ..search.torch_hashmap import HashMethod
+from .batch_index import offsets_from_batch_index
+
+
+@torch.no_grad()
+def unique_strided_rows(bcoords: Tensor, stride: Tuple[int, int, int] = (1, 1, 1),
+                        hash_method: HashMethod = HashMethod.CITY, return_parent: bool = False):
+    """Distinct rows of ``floor(bcoords / [1, *stride])``.
+
+    Returns ``(rows [M,4] int32, unique_index [M] int32, parent [N] int32 | None)``:
+    ``unique_index`` are the (ascending) source rows of the first occurrences and
+    ``parent[i]`` the output row input i collapsed into.
+    """
+    assert bcoords.is_cuda, f"Batched coordinates must be on cuda device, got {bcoords.device}"
+    assert bcoords.dtype == torch.int32 and bcoords.ndim == 2 and bcoords.shape[1] == 4
+    dev = bcoords.device
+    c = bcoords.contiguous()
+    n = c.shape[0]
+    if n == 0:
+        e = torch.empty(0, dtype=torch.int32, device=dev)
+        return c.clone(), e, (e.clone() if return_parent else None)
+    cap = max(16, 2 * n)
+    table = torch.empty(query_bytes("wcn_hash_table_bytes", cap), dtype=torch.uint8, device=dev)
+    strd = (ctypes.c_int32 * 3)(*[int(s) for s in stride])
+    sp = ctypes.addressof(strd)
+    st = stream_ptr(dev)
+    check(lib().wcn_hash_build(ptr(c), n, sp, ptr(table), cap, hash_method.value, ptr(device_status(dev)), st),
+          "wcn_hash_build")
+    ws = torch.empty(query_bytes("wcn_unique_workspace_bytes", n), dtype=torch.uint8, device=dev)
+    count = torch.empty(1, dtype=torch.int64, device=dev)
+    check(lib().wcn_unique_mark(ptr(c), n, sp, ptr(table), cap, hash_method.value, ptr(ws), ptr(count), st),
+          "wcn_unique_mark")
+    m = int(count.item())  # output size is needed on the host to allocate
+    rows = torch.empty((m, 4), dtype=torch.int32, device=dev)
+    uidx = torch.empty(m, dtype=torch.int32, device=dev)
+    parent = torch.empty(n, dtype=torch.int32, device=dev) if return_parent else None
+    check(lib().wcn_unique_emit(ptr(c), n, sp, ptr(ws), ptr(rows), ptr(uidx), ptr(parent), st), "wcn_unique_emit")
+    return rows, uidx, parent
+
+
+@torch.no_grad()
+def stride_coords(batch_indexed_coords: Tensor, stride: Tuple[int, ...], order=None):
+    """Down-sample coordinates by ``stride``; returns (coords [M,4], CPU offsets [B+1])."""
+    nd = batch_indexed_coords.shape[1] - 1
+    assert len(stride) == nd, (f"Stride must match the number of spatial dimensions. Got {len(stride)} spatial "
+                               f"dimensions for but coordinates with {nd} spatial dimensions.")
+    if all(s == 1 for s in stride):
+        return batch_indexed_coords, offsets_from_batch_index(batch_indexed_coords[:, 0])
+    rows, _, _ = unique_strided_rows(batch_indexed_coords, ntuple(stride, ndim=nd))
+    from .serialization import POINT_ORDERING, encode
+    if order is not None and order != POINT_ORDERING.RANDOM:
+        offsets = offsets_from_batch_index(rows[:, 0])
+        perm = encode(rows[:, 1:], batch_offsets=offsets, order=order, return_perm=True).perm
+        rows = rows[perm]
+    return rows, offsets_from_batch_index(rows[:, 0])

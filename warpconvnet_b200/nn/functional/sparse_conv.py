@@ -1,0 +1,443 @@
+"""Functional sparse convolution (warpconvnet/nn/functional/sparse_conv.py).
+
+``spatially_sparse_conv`` keeps the reference's signature and semantics
+(:1662-1805): the 1x1x1 shortcut, tensor-stride bookkeeping, output-coordinate
+selection, the shared kernel-map cache with transposed maps taken from the
+forward map (:1808-1996), the explicit / implicit algorithm switch and the bias
+add.  Behind it:
+
+* ``explicit_gemm``: per kernel offset, a row-gather kernel, a dense cuBLAS GEMM
+  and an owner scatter-add kernel (the reference's algorithm, :281-311);
+* ``implicit_gemm`` / ``cutlass_implicit_gemm`` / ``auto``: ONE output-stationary
+  kernel over the dense neighbour table — tcgen05 tensor cores for fp16/bf16
+  with channel counts it supports, an FP32-pipe kernel otherwise — with bias,
+  folded BatchNorm, residual add and ReLU fused into its epilogue when the
+  caller passes a :class:`ConvEpilogue`.
+
+There is no auto-tuner and no CPU path.
+"""
+from __future__ import annotations
+
+import enum
+from dataclasses import dataclass
+from typing import List, Optional, Tuple, Union
+
+import numpy as np
+import torch
+from torch import Tensor
+
+from ..._native import (CONV_AUTO, CONV_SIMT, CONV_TCGEN05, check, device_status, dtype_code, lib, ptr,
+                        query_bytes, require_cuda, stream_ptr)
+from ...geometry.coords.integer import IntCoords
+from ...geometry.coords.ops.serialization import POINT_ORDERING, encode
+from ...geometry.coords.ops.stride import stride_coords
+from ...geometry.coords.search.cache import IntSearchCache, IntSearchCacheKey
+from ...geometry.coords.search.search_results import IntSearchResult
+from ...geometry.coords.search.torch_discrete import generate_kernel_map
+from ...geometry.types.voxels import Voxels
+from ...utils.ntuple import ntuple
+from ...utils.type_cast import _maybe_cast, _min_dtype
+
+
+class STRIDED_CONV_MODE(enum.Enum):
+    REDUCE_AND_STRIDE = "reduce_and_stride"
+    STRIDE_ONLY = "stride_only"
+
+
+class SPARSE_CONV_FWD_ALGO_MODE(enum.Enum):
+    EXPLICIT_GEMM = "explicit_gemm"
+    IMPLICIT_GEMM = "implicit_gemm"
+    CUTLASS_IMPLICIT_GEMM = "cutlass_implicit_gemm"
+    AUTO = "auto"
+
+
+class SPARSE_CONV_BWD_ALGO_MODE(enum.Enum):
+    EXPLICIT_GEMM = "explicit_gemm"
+    IMPLICIT_GEMM = "implicit_gemm"
+    CUTLASS_IMPLICIT_GEMM = "cutlass_implicit_gemm"
+    AUTO = "auto"
+
+
+@dataclass
+class ConvEpilogue:
+    """Element-wise tail fused into the convolution kernel:
+    ``y = conv * scale + shift; y += residual; y = relu(y)`` (each part optional).
+    ``scale``/``shift`` are fp32 ``[C_out]`` (an eval-mode BatchNorm folds to
+    exactly this; a bias is a shift); ``residual`` is ``[M, C_out]`` in the
+    output dtype."""
+
+    scale: Optional[Tensor] = None
+    shift: Optional[Tensor] = None
+    residual: Optional[Tensor] = None
+    relu: bool = False
+
+
+def _normalize_fwd_algo(algo) -> SPARSE_CONV_FWD_ALGO_MODE:
+    """Enum | str | list of either -> one algorithm.  A list means "pick the
+    best of these" in the reference (:1338-1363); without a tuner the first
+    native-kernel entry wins, else the first entry."""
+    if isinstance(algo, (list, tuple)):
+        items = [_normalize_fwd_algo(a) for a in algo]
+        if not items:
+            raise ValueError("empty algorithm list")
+        for a in items:
+            if a != SPARSE_CONV_FWD_ALGO_MODE.EXPLICIT_GEMM:
+                return a
+        return items[0]
+    if isinstance(algo, SPARSE_CONV_FWD_ALGO_MODE):
+        return algo
+    if isinstance(algo, str):
+        try:
+            return SPARSE_CONV_FWD_ALGO_MODE(algo.lower())
+        except ValueError:
+            raise ValueError(f"Unsupported forward algorithm: {algo}")
+    if isinstance(algo, enum.Enum) and isinstance(algo.value, str):
+        return _normalize_fwd_algo(algo.value)
+    raise ValueError(f"Unsupported forward algorithm: {algo}")
+
+
+# --------------------------------------------------------------------------- kernels
+
+
+def _gather_rows(src: Tensor, idx: Tensor) -> Tensor:
+    dst = torch.empty((idx.shape[0], src.shape[1]), dtype=src.dtype, device=src.device)
+    check(lib().wcn_gather_rows(ptr(src), ptr(idx), ptr(dst), idx.shape[0], src.shape[1], dtype_code(src.dtype),
+                                stream_ptr(src.device)), "wcn_gather_rows")
+    return dst
+
+
+def _scatter_add_rows(src: Tensor, idx: Tensor, dst: Tensor) -> None:
+    check(lib().wcn_scatter_add_rows(ptr(src), ptr(idx), ptr(dst), idx.shape[0], src.shape[1],
+                                     dtype_code(src.dtype), stream_ptr(src.device)), "wcn_scatter_add_rows")
+
+
+def _explicit_gemm_forward_logic(in_features: Tensor, weight: Tensor, kernel_map: IntSearchResult,
+                                 num_out_coords: int, compute_dtype: Optional[torch.dtype] = None) -> Tensor:
+    """gather -> GEMM -> scatter-add per kernel offset; the identity offset is one
+    dense GEMM (reference :281-311)."""
+    require_cuda(in_features, "in_features")
+    x = _maybe_cast(in_features, compute_dtype).contiguous()
+    w = _maybe_cast(weight, compute_dtype).contiguous()
+    iden = kernel_map.identity_map_index
+    if iden is not None:
+        out = torch.matmul(x, w[iden])
+    else:
+        out = torch.zeros(num_out_coords, w.shape[-1], device=x.device, dtype=x.dtype)
+    offsets = kernel_map.offsets
+    in_maps, out_maps = kernel_map.in_maps, kernel_map.out_maps
+    for k in range(len(kernel_map)):
+        if k == iden:
+            continue
+        s, e = int(offsets[k]), int(offsets[k + 1])
+        if e == s:
+            continue
+        cur = torch.matmul(_gather_rows(x, in_maps[s:e]), w[k])
+        _scatter_add_rows(cur, out_maps[s:e], out)
+    return out.to(dtype=in_features.dtype)
+
+
+def _prepared_weight(weight: Tensor, dtype: torch.dtype, algo: int = CONV_AUTO):
+    """(weight in ``dtype``, its re-tiled copy for the tensor-core kernel or None).
+
+    Both are cached ON the weight tensor object, tagged with its version counter,
+    so an inference loop casts and re-tiles a parameter once and a parameter
+    update invalidates the copy."""
+    store = weight.__dict__.setdefault("_wcn_prepared", {})
+    hit = store.get((dtype, algo))
+    if hit is not None and hit[0] == weight._version and hit[1].device == weight.device:
+        return hit[1], hit[2]
+    w = weight.detach().to(dtype=dtype).contiguous()
+    K, c_in, c_out = w.shape
+    packed = None
+    if algo != CONV_SIMT and w.is_cuda:
+        nbytes = query_bytes("wcn_conv_packed_weight_bytes", algo, K, c_in, c_out, dtype_code(dtype))
+        if nbytes > 0:
+            packed = torch.empty(nbytes, dtype=torch.uint8, device=w.device)
+            check(lib().wcn_conv_pack_weight(algo, ptr(w), K, c_in, c_out, dtype_code(dtype), ptr(packed),
+                                             stream_ptr(w.device)), "wcn_conv_pack_weight")
+    store[(dtype, algo)] = (weight._version, w, packed)
+    return w, packed
+
+
+def sparse_conv_fused(in_features: Tensor, weight: Tensor, kernel_map: IntSearchResult, num_out_coords: int,
+                      epilogue: Optional[ConvEpilogue] = None, out_dtype: Optional[torch.dtype] = None,
+                      algo: int = CONV_AUTO) -> Tensor:
+    """One launch: all kernel offsets + epilogue.  The weight is used in the
+    feature dtype (fp32, fp16 or bf16); accumulation is fp32."""
+    require_cuda(in_features, "in_features")
+    x = in_features.contiguous()
+    w, packed = _prepared_weight(weight, x.dtype, algo)
+    K, c_in, c_out = w.shape
+    assert x.shape[1] == c_in, f"features have {x.shape[1]} channels, weight expects {c_in}"
+    dev = x.device
+    out_dtype = out_dtype or x.dtype
+    out = torch.empty((num_out_coords, c_out), dtype=out_dtype, device=dev)
+    if num_out_coords == 0:
+        return out
+    nbr = kernel_map.neighbor_table(num_out_coords)
+    assert nbr.shape[0] == K, f"kernel map has {nbr.shape[0]} offsets, weight has {K}"
+    ep = epilogue or ConvEpilogue()
+    scale = ep.scale.to(device=dev, dtype=torch.float32).contiguous() if ep.scale is not None else None
+    shift = ep.shift.to(device=dev, dtype=torch.float32).contiguous() if ep.shift is not None else None
+    residual = None
+    if ep.residual is not None:
+        residual = ep.residual.to(dtype=out_dtype).contiguous()
+        assert residual.shape == out.shape, f"residual {tuple(residual.shape)} != output {tuple(out.shape)}"
+    check(lib().wcn_conv_fwd(algo, ptr(x), x.shape[0], ptr(w), ptr(packed), ptr(nbr), num_out_coords, K, c_in,
+                             c_out, dtype_code(x.dtype), ptr(scale), ptr(shift), ptr(residual), int(ep.relu),
+                             ptr(out), dtype_code(out_dtype), ptr(device_status(dev)), stream_ptr(dev)),
+          "wcn_conv_fwd")
+    return out
+
+
+def _implicit_gemm_forward_logic(in_features: Tensor, weight: Tensor, kernel_map: IntSearchResult,
+                                 num_out_coords: int, compute_dtype: Optional[torch.dtype],
+                                 fwd_block_size: Optional[int] = None,
+                                 epilogue: Optional[ConvEpilogue] = None) -> Tensor:
+    """Both operands are cast to the lower-ranked of (feature/compute dtype,
+    weight dtype); the result returns in the feature dtype (reference :358-415,
+    :495-544).  ``fwd_block_size`` is accepted and ignored (no tunables)."""
+    feature_dtype = compute_dtype if compute_dtype is not None else in_features.dtype
+    min_dtype = _min_dtype(feature_dtype, weight.dtype)
+    if min_dtype == torch.float64:
+        raise ValueError("float64 is not supported by the native kernels; use explicit_gemm")
+    x = in_features.detach().to(dtype=min_dtype)
+    return sparse_conv_fused(x, weight, kernel_map, num_out_coords, epilogue, out_dtype=in_features.dtype
+                             if in_features.dtype in (torch.float32, torch.float16, torch.bfloat16) else None)
+
+
+_cutlass_implicit_gemm_forward_logic = _implicit_gemm_forward_logic
+
+
+# --------------------------------------------------------------------------- output coordinates + kernel map
+
+
+def generate_output_coords_and_kernel_map(input_sparse_tensor: Voxels, kernel_size: Tuple[int, ...],
+                                          kernel_dilation: Tuple[int, ...], stride: Tuple[int, ...],
+                                          generative: bool, transposed: bool,
+                                          output_spatially_sparse_tensor: Optional[Voxels],
+                                          stride_mode: STRIDED_CONV_MODE = STRIDED_CONV_MODE.STRIDE_ONLY,
+                                          order: POINT_ORDERING = POINT_ORDERING.RANDOM):
+    """(batch-indexed output coords, output offsets, kernel map); maps are cached on
+    the input's shared cache and a transposed map reuses the forward one."""
+    if generative:
+        raise NotImplementedError("generative convolution is outside the supported path")
+    if stride_mode != STRIDED_CONV_MODE.STRIDE_ONLY and any(s != 1 for s in stride):
+        raise NotImplementedError("stride_mode=reduce_and_stride is outside the supported path")
+    in_coords = input_sparse_tensor.batch_indexed_coordinates
+    if in_coords.dtype != torch.int32:
+        in_coords = in_coords.to(torch.int32)
+
+    if output_spatially_sparse_tensor is not None:
+        out_coords = output_spatially_sparse_tensor.batch_indexed_coordinates
+        if out_coords.dtype != torch.int32:
+            out_coords = out_coords.to(torch.int32)
+        out_offsets = output_spatially_sparse_tensor.offsets
+    elif any(s != 1 for s in stride):
+        out_coords, out_offsets = stride_coords(in_coords, stride)
+    else:
+        out_coords, out_offsets = in_coords, input_sparse_tensor.offsets
+
+    if order != POINT_ORDERING.RANDOM:
+        perm = encode(out_coords[:, 1:], batch_offsets=out_offsets, order=order, return_perm=True).perm
+        out_coords = out_coords[perm]
+
+    def key_for(transposed_, in_off, out_off):
+        return IntSearchCacheKey(kernel_size=kernel_size, kernel_dilation=kernel_dilation, transposed=transposed_,
+                                 generative=generative, stride_mode=str(stride_mode),
+                                 skip_symmetric_kernel_map=False, in_offsets=in_off, out_offsets=out_off)
+
+    key = key_for(transposed, input_sparse_tensor.offsets, out_offsets)
+    cache = input_sparse_tensor.cache
+    if cache is not None:
+        hit = cache.get(key)
+        if hit is not None:
+            return out_coords, out_offsets, hit
+
+    if transposed:
+        fwd = None
+        if cache is not None:
+            fwd = cache.get(key_for(False, out_offsets, input_sparse_tensor.offsets))
+        if fwd is None:
+            # forward map: table on the (fine) output coordinates, (coarse) inputs * stride as queries
+            fwd = generate_kernel_map(out_coords, in_coords, stride, kernel_size, None)
+        kernel_map = fwd.swapped(num_in=out_coords.shape[0])
+    else:
+        kernel_map = generate_kernel_map(in_coords, out_coords, stride, kernel_size, None)
+
+    if input_sparse_tensor.cache is None:
+        input_sparse_tensor._extra_attributes["_cache"] = IntSearchCache()
+    input_sparse_tensor.cache.put(key, kernel_map)
+    return out_coords, out_offsets, kernel_map
+
+
+# --------------------------------------------------------------------------- autograd
+
+
+class _SparseConvFunction(torch.autograd.Function):
+    """Forward through the native kernels; backward with the explicit-GEMM
+    formulas (reference :314-355) on the compact map: dX[in_k] += dY[out_k] @ W_k^T,
+    dW_k = X[in_k]^T @ dY[out_k]."""
+
+    @staticmethod
+    def forward(ctx, in_features, weight, kernel_map, num_out_coords, algo, compute_dtype, epilogue):
+        ctx.kernel_map = kernel_map
+        ctx.compute_dtype = compute_dtype
+        ctx.save_for_backward(in_features, weight)
+        if algo == SPARSE_CONV_FWD_ALGO_MODE.EXPLICIT_GEMM:
+            return _explicit_gemm_forward_logic(in_features, weight, kernel_map, num_out_coords, compute_dtype)
+        return _implicit_gemm_forward_logic(in_features, weight, kernel_map, num_out_coords, compute_dtype,
+                                            epilogue=epilogue)
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        x, w = ctx.saved_tensors
+        km = ctx.kernel_map
+        dt = ctx.compute_dtype if ctx.compute_dtype is not None else x.dtype
+        xc, wc, gc = x.to(dt), w.to(dt), grad_output.contiguous().to(dt)
+        gx = torch.zeros_like(xc)
+        gw = torch.zeros_like(wc)
+        offsets, in_maps, out_maps = km.offsets, km.in_maps, km.out_maps
+        for k in range(len(km)):
+            s, e = int(offsets[k]), int(offsets[k + 1])
+            if e == s:
+                continue
+            go = _gather_rows(gc, out_maps[s:e])
+            xi = _gather_rows(xc, in_maps[s:e])
+            _scatter_add_rows(torch.matmul(go, wc[k].T), in_maps[s:e], gx)
+            gw[k] = torch.matmul(xi.T, go)
+        return gx.to(x.dtype), gw.to(w.dtype), None, None, None, None, None
+
+
+# --------------------------------------------------------------------------- entry point
+
+
+def spatially_sparse_conv(
+    input_sparse_tensor: Voxels,
+    weight: Tensor,
+    kernel_size: Union[int, List[int], Tuple[int, ...]],
+    stride: Union[int, List[int], Tuple[int, ...]] = 1,
+    kernel_dilation: Union[int, List[int], Tuple[int, ...]] = 1,
+    bias: Optional[Tensor] = None,
+    kernel_matmul_batch_size: int = 2,
+    generative: bool = False,
+    output_spatially_sparse_tensor: Optional[Voxels] = None,
+    transposed: bool = False,
+    fwd_algo: Union[SPARSE_CONV_FWD_ALGO_MODE, List[SPARSE_CONV_FWD_ALGO_MODE]] = SPARSE_CONV_FWD_ALGO_MODE.EXPLICIT_GEMM,
+    bwd_algo: Union[SPARSE_CONV_BWD_ALGO_MODE, List[SPARSE_CONV_BWD_ALGO_MODE]] = SPARSE_CONV_BWD_ALGO_MODE.EXPLICIT_GEMM,
+    stride_mode: STRIDED_CONV_MODE = STRIDED_CONV_MODE.STRIDE_ONLY,
+    stride_reduce: str = "max",
+    order: POINT_ORDERING = POINT_ORDERING.RANDOM,
+    compute_dtype: Optional[torch.dtype] = None,
+    implicit_matmul_fwd_block_size: Optional[int] = 16,
+    implicit_matmul_bwd_block_size: Optional[int] = 16,
+    epilogue: Optional[ConvEpilogue] = None,
+) -> Voxels:
+    """Sparse convolution of a ``Voxels`` tensor with ``weight [K, C_in, C_out]``.
+
+    ``epilogue`` (an addition to the reference signature) fuses scale/shift,
+    residual add and ReLU into the kernel; it forces the native implicit kernel.
+    """
+    if not isinstance(input_sparse_tensor, Voxels):
+        raise TypeError("Native spatially_sparse_conv expects input_sparse_tensor of type Voxels, got "
+                        f"{type(input_sparse_tensor)}")
+    if output_spatially_sparse_tensor is not None and not isinstance(output_spatially_sparse_tensor, Voxels):
+        raise TypeError("Native spatially_sparse_conv expects output_spatially_sparse_tensor of type Voxels or "
+                        f"None, got {type(output_spatially_sparse_tensor)}")
+    nd = input_sparse_tensor.num_spatial_dims
+    _kernel_size = ntuple(kernel_size, ndim=nd)
+    _kernel_dilation = ntuple(kernel_dilation, ndim=nd)
+    _stride = ntuple(stride, ndim=nd)
+    algo = _normalize_fwd_algo(fwd_algo)
+    feats = input_sparse_tensor.feature_tensor
+    needs_grad = torch.is_grad_enabled() and (feats.requires_grad or weight.requires_grad)
+
+    if np.prod(_kernel_size) == 1 and np.prod(_stride) == 1:
+        if epilogue is None:
+            out = feats @ weight[0].to(feats.dtype) if weight.dtype != feats.dtype else feats @ weight[0]
+            if bias is not None:
+                out = out + bias.to(out.dtype)
+            return input_sparse_tensor.replace(batched_features=out)
+        # 1x1x1 with a fused tail: the same kernel over the identity neighbour table
+        n = feats.shape[0]
+        ident = _identity_map(n, feats.device)
+        ep = _merge_bias(epilogue, bias)
+        out = _implicit_gemm_forward_logic(feats, weight, ident, n, compute_dtype, epilogue=ep)
+        return input_sparse_tensor.replace(batched_features=out)
+
+    in_tensor_stride = input_sparse_tensor.tensor_stride
+    if in_tensor_stride is None:
+        in_tensor_stride = ntuple(1, ndim=nd)
+    if transposed and not generative:
+        assert output_spatially_sparse_tensor is not None, \
+            "Output spatially sparse tensor is required for transposed convolution"
+    if not transposed:
+        out_tensor_stride = tuple(o * s for o, s in zip(_stride, in_tensor_stride))
+    else:
+        if output_spatially_sparse_tensor is not None and output_spatially_sparse_tensor.tensor_stride is not None:
+            out_tensor_stride = output_spatially_sparse_tensor.tensor_stride
+        else:
+            out_tensor_stride = ntuple(1, ndim=nd)
+        assert any(o < i for o, i in zip(out_tensor_stride, in_tensor_stride)), \
+            "Output stride is larger than input stride"
+
+    effective_compute_dtype = compute_dtype if compute_dtype is not None else feats.dtype
+
+    out_coords, out_offsets, kernel_map = generate_output_coords_and_kernel_map(
+        input_sparse_tensor=input_sparse_tensor, kernel_size=_kernel_size, kernel_dilation=_kernel_dilation,
+        stride=_stride, generative=generative, transposed=transposed,
+        output_spatially_sparse_tensor=output_spatially_sparse_tensor, stride_mode=stride_mode, order=order)
+    num_out = out_coords.shape[0]
+
+    if algo == SPARSE_CONV_FWD_ALGO_MODE.EXPLICIT_GEMM and epilogue is None:
+        if needs_grad:
+            out = _SparseConvFunction.apply(feats, weight, kernel_map, num_out, algo, effective_compute_dtype, None)
+        else:
+            out = _explicit_gemm_forward_logic(feats, weight, kernel_map, num_out, effective_compute_dtype)
+        if bias is not None:
+            out = out + bias.to(out.dtype)
+    else:
+        ep = _merge_bias(epilogue, bias)
+        if needs_grad:
+            if epilogue is not None:
+                raise RuntimeError("a fused epilogue is an inference feature; run under torch.no_grad()")
+            out = _SparseConvFunction.apply(feats, weight, kernel_map, num_out,
+                                            SPARSE_CONV_FWD_ALGO_MODE.IMPLICIT_GEMM, effective_compute_dtype, ep)
+        else:
+            out = _implicit_gemm_forward_logic(feats, weight, kernel_map, num_out, effective_compute_dtype,
+                                               epilogue=ep)
+
+    return input_sparse_tensor.replace(
+        batched_coordinates=IntCoords(out_coords[:, 1:], offsets=out_offsets.cpu().int()),
+        batched_features=out, tensor_stride=out_tensor_stride)
+
+
+def _merge_bias(epilogue: Optional[ConvEpilogue], bias: Optional[Tensor]) -> Optional[ConvEpilogue]:
+    """The reference adds the bias right after the convolution (:1794-1795), i.e.
+    before any BatchNorm that follows: (conv + b) * scale + shift
+    = conv * scale + (shift + b * scale)."""
+    if bias is None:
+        return epilogue
+    b = bias.detach().float()
+    if epilogue is None:
+        return ConvEpilogue(shift=b)
+    if epilogue.scale is not None:
+        b = b * epilogue.scale.to(b.device).float()
+    shift = b if epilogue.shift is None else epilogue.shift.to(b.device).float() + b
+    return ConvEpilogue(scale=epilogue.scale, shift=shift, residual=epilogue.residual, relu=epilogue.relu)
+
+
+_identity_maps: dict = {}
+
+
+def _identity_map(n: int, device: torch.device) -> IntSearchResult:
+    """Neighbour table of a 1x1x1 convolution: row m reads row m."""
+    key = (n, str(device))
+    hit = _identity_maps.get(key)
+    if hit is None:
+        nbr = torch.arange(n, dtype=torch.int32, device=device).unsqueeze(0).contiguous()
+        hit = IntSearchResult.from_neighbor_table(nbr, n, None, 0)
+        if len(_identity_maps) > 64:
+            _identity_maps.clear()
+        _identity_maps[key] = hit
+    return hit
