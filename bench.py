@@ -1,0 +1,375 @@
+#!/usr/bin/env python
+"""Benchmark of the sparse-convolution hot path: MinkUNet-34 inference forward
+(fp16, random-init weights) over batches of synthetic indoor rooms.
+
+    python bench.py --gpus N --steps K --warmup W          # this library
+    python bench.py --impl reference --steps K --warmup W  # the reference's CPU path
+
+One step = one pass of the whole path over one batch held by a rank: Morton
+ordering of the voxels, coordinate hashing, kernel-map generation for every
+resolution level, the 46 3x3x3 / 4 down / 4 up / 1x1x1 convolutions with their
+fused BatchNorm/ReLU/residual epilogues, un-permutation of the logits.  Every
+step sees a fresh ``Voxels`` object, so nothing (maps, orderings) is carried
+over between steps.  ``value`` times the step with the batch already in HBM;
+``e2e`` times the same step from pinned host buffers, with the host-to-device
+copy of coordinates and features and the device-to-host copy of the logits
+inside the timed region.
+
+Ranks hold independent scene groups (no data-path collective): weak scaling.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "sparse-conv voxels/sec (MinkUNet fwd)"
+UNIT = "voxels/s"
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", choices=["b200", "reference"], default="b200")
+    ap.add_argument("--scenes", type=int, default=8, help="rooms per rank")
+    ap.add_argument("--voxels", type=int, default=150000, help="voxels per room")
+    ap.add_argument("--voxel-size", type=float, default=0.02)
+    ap.add_argument("--mode", choices=["raster_crop", "sample"], default="raster_crop")
+    ap.add_argument("--cpu-sample-voxels", type=int, default=150000)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    return ap.parse_args()
+
+
+# --------------------------------------------------------------------------- workload
+
+
+def make_batch(args, rank):
+    from warpconvnet_b200.datasets import synthetic
+    scenes = [synthetic.room_scene(args.voxels, args.voxel_size, 200 + rank * args.scenes + s, args.mode)
+              for s in range(args.scenes)]
+    coords, offsets = synthetic.batch_scenes(scenes)
+    feats = np.random.default_rng(1000 + rank).random((len(coords), 3), dtype=np.float32)
+    return coords, offsets, feats
+
+
+def make_model():
+    from warpconvnet_b200.examples.mink_unet import MinkUNet34, randomize_batchnorm_
+    torch.manual_seed(0)
+    model = MinkUNet34(3, 20)
+    randomize_batchnorm_(model, 1)
+    return model.eval()
+
+
+# --------------------------------------------------------------------------- clocks
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples of one GPU while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, smax, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            parts = [p.strip() for p in ln.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                smax = float(parts[1])
+            except ValueError:
+                continue
+            for nm, v in zip(names, parts[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(nm)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": smax, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# --------------------------------------------------------------------------- CPU arm (the reference's own path restated)
+
+
+def cpu_forward_timed(args, repeats):
+    """The reference's CPU-runnable path — explicit-GEMM convolutions on torch CPU
+    tensors + the kernel-map restatement — over one room; returns (voxels/s, info)."""
+    from oracle import sparse_conv as osc
+    from warpconvnet_b200.datasets import synthetic
+    torch.set_num_threads(os.cpu_count() or 1)
+    model = make_model()
+    sd = model.state_dict()
+    n = args.cpu_sample_voxels
+    xyz = synthetic.room_scene(n, args.voxel_size, 200, args.mode)
+    coords = np.concatenate([np.zeros((len(xyz), 1), np.int32), xyz], 1)
+    feats = torch.rand(n, 3, generator=torch.Generator().manual_seed(0))
+    times = []
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        osc.minkunet_forward(sd, coords, feats)
+        times.append(time.perf_counter() - t0)
+    return n, times
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    n, _ = cpu_forward_timed(args, max(args.warmup, 1))
+    n, times = cpu_forward_timed(args, args.steps)
+    total = sum(times)
+    value = n * len(times) / total
+    cores = torch.get_num_threads()
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": 1e3 * total / len(times), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic", "impl": "reference",
+        "config": workload_config(args, note="CPU arm: each step is one room of the workload"),
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port",
+                         "sample": f"one {args.mode} room of {n} voxels per step, fp32, MinkUNet-34 forward"},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(args, note=None):
+    cfg = {"workload": f"MinkUNet-34 inference forward, fp16, batch of {args.scenes} synthetic rooms x "
+                       f"{args.voxels} voxels at {args.voxel_size} m ({args.mode}), 3 input channels, 20 classes; "
+                       "one scene group per GPU, no communication",
+           "scenes_per_gpu": args.scenes, "voxels_per_scene": args.voxels, "generator": args.mode,
+           "l2": "flushed between steps (256 MiB write); per-step working set is also far larger than L2",
+           "step": "morton sort + hash/kernel maps (rebuilt every step) + all convolutions + unpermute"}
+    if note:
+        cfg["note"] = note
+    return cfg
+
+
+# --------------------------------------------------------------------------- GPU arm
+
+
+class ConvProfile:
+    """CUDA-event durations and useful FLOPs of the convolution launches of one step."""
+
+    def __init__(self):
+        self.records = []  # (start, end, nbr tensor, c_in, c_out, kind)
+
+    def summarise(self):
+        pair_counts = {}
+        tot_ms, tot_flop, n = 0.0, 0.0, 0
+        tc_ms, tc_flop, tc_n = 0.0, 0.0, 0
+        for s, e, nbr, c_in, c_out, kind in self.records:
+            key = nbr.data_ptr()
+            if key not in pair_counts:
+                pair_counts[key] = int((nbr >= 0).sum().item())
+            ms = s.elapsed_time(e)
+            fl = 2.0 * pair_counts[key] * c_in * c_out
+            tot_ms += ms; tot_flop += fl; n += 1
+            if kind == "tcgen05":
+                tc_ms += ms; tc_flop += fl; tc_n += 1
+        return {"launches": n, "ms": tot_ms, "flop": tot_flop, "tc_launches": tc_n, "tc_ms": tc_ms, "tc_flop": tc_flop}
+
+
+def install_conv_profiler(profile):
+    """Wrap the fused-convolution entry so each launch is bracketed by events on the launching stream."""
+    import warpconvnet_b200.nn.functional.sparse_conv as F
+    from warpconvnet_b200._native import query_bytes, dtype_code
+    orig = F.sparse_conv_fused
+
+    def wrapped(in_features, weight, kernel_map, num_out_coords, epilogue=None, out_dtype=None, algo=0):
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        out = orig(in_features, weight, kernel_map, num_out_coords, epilogue, out_dtype, algo)
+        e.record()
+        K, c_in, c_out = weight.shape
+        tc = in_features.dtype != torch.float32 and query_bytes(
+            "wcn_conv_packed_weight_bytes", 0, K, c_in, c_out, dtype_code(in_features.dtype)) > 0
+        profile.records.append((s, e, kernel_map.neighbor_table(num_out_coords), c_in, c_out,
+                                "tcgen05" if tc else "simt"))
+        return out
+
+    F.sparse_conv_fused = wrapped
+    return lambda: setattr(F, "sparse_conv_fused", orig)
+
+
+def run_gpu_arm(args):
+    import torch.distributed as dist
+    from warpconvnet_b200 import POINT_ORDERING, Voxels
+    from warpconvnet_b200 import _native
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: this library has no CPU path")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    _native.lib()  # fail loudly now if the library is missing
+
+    coords_np, offsets_np, feats_np = make_batch(args, rank)
+    n_vox = len(coords_np)
+    model = make_model().to(dev).half()
+    xyz_host = torch.from_numpy(np.ascontiguousarray(coords_np[:, 1:])).pin_memory()
+    feats_host = torch.from_numpy(feats_np).half().pin_memory()
+    offsets = torch.from_numpy(offsets_np)
+    logits_host = torch.empty((n_vox, 20), dtype=torch.float16).pin_memory()
+    xyz_dev, feats_dev = xyz_host.to(dev), feats_host.to(dev)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    def forward(xyz, feats):
+        vox = Voxels(xyz, feats, offsets=offsets)
+        ordered = vox.sort(POINT_ORDERING.MORTON_XYZ)
+        out = model(ordered)
+        inv = torch.empty_like(ordered.extra_attributes["perm"])
+        inv[ordered.extra_attributes["perm"]] = torch.arange(n_vox, device=dev)
+        return out.feature_tensor[inv]
+
+    def step_resident():
+        flush.zero_()
+        return forward(xyz_dev, feats_dev)
+
+    def step_e2e():
+        flush.zero_()
+        xyz = xyz_host.to(dev, non_blocking=True)
+        feats = feats_host.to(dev, non_blocking=True)
+        logits_host.copy_(forward(xyz, feats), non_blocking=True)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        barrier()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        for _ in range(steps):
+            fn()
+        e.record()
+        barrier()
+        ms = torch.tensor([s.elapsed_time(e)], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    with torch.no_grad():
+        for _ in range(max(args.warmup, 3)):
+            step_resident()
+        _native.check_device_status(dev)
+        sampler = ClockSampler(local_rank)
+        sampler.start()
+        before = _native.launches_total()
+        ms = timed(step_resident, args.steps)
+        launches = _native.launches_total() - before
+        clocks = sampler.stop()
+        for _ in range(2):
+            step_e2e()
+        ms_e2e = timed(step_e2e, args.steps)
+        _native.check_device_status(dev)
+
+        # roofline of the dominant kernel: per-launch CUDA events over a timed region of its own
+        profile = ConvProfile()
+        restore = install_conv_profiler(profile)
+        barrier()
+        prof_steps = min(args.steps, 5)
+        for _ in range(prof_steps):
+            step_resident()
+        barrier()
+        restore()
+        prof = profile.summarise()
+
+    total_vox = n_vox * world  # every rank holds a batch of the same size
+    if world > 1:
+        t = torch.tensor([n_vox], device=dev, dtype=torch.int64)
+        dist.all_reduce(t)
+        total_vox = int(t.item())
+    value = total_vox * args.steps / (ms * 1e-3)
+    e2e_value = total_vox * args.steps / (ms_e2e * 1e-3)
+
+    if rank == 0:
+        peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+        if os.path.isfile(peaks_path):
+            peaks = json.load(open(peaks_path))
+            peak_tf, peak_src = float(peaks["bf16_tflops_sustained"]), "measured sustained bf16 (MEASURED_PEAKS.json)"
+        else:
+            peak_tf, peak_src = 1400.0, "fallback sustained figure"
+        achieved_tf = prof["tc_flop"] / (prof["tc_ms"] * 1e-3) / 1e12 if prof["tc_ms"] > 0 else 0.0
+        roofline = {
+            "bound": "tensor", "achieved": achieved_tf, "peak": peak_tf, "unit": "TFLOP/s",
+            "frac": achieved_tf / peak_tf, "traffic": None, "peak_source": peak_src,
+            "kernel": "conv_tcgen05_kernel (all tensor-core convolution launches of a step)",
+            "useful_flop_per_step": prof["tc_flop"] / prof_steps, "launches_per_step": prof["tc_launches"] / prof_steps,
+            "avg_launch_ms": prof["tc_ms"] / max(prof["tc_launches"], 1),
+            "conv_share_of_step": (prof["ms"] / prof_steps) / (ms / args.steps),
+        }
+        cpu = None
+        if not args.no_cpu_baseline:
+            n, _ = cpu_forward_timed(args, 1)
+            n, times = cpu_forward_timed(args, 3)
+            cpu = {"value": n * len(times) / sum(times), "unit": UNIT, "cores": torch.get_num_threads(),
+                   "kind": "port", "sample": f"3 forwards of one {args.mode} room of {n} voxels, fp32, all host threads"}
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": workload_config(args),
+            "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": ms_e2e / args.steps,
+                    "h2d_bytes_per_step": int(xyz_host.numel() * 4 + feats_host.numel() * 2),
+                    "d2h_bytes_per_step": int(logits_host.numel() * 2)},
+            "gpu_launches": int(launches), "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu,
+            "voxels_per_gpu": n_vox,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_gpu_arm(args)
+
+
+if __name__ == "__main__":
+    main()

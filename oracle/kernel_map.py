@@ -53,19 +53,34 @@ def kernel_offsets_from_size(
 
 
 def _pack_rows(rows_list):
-    """Map int32 [*, D] row arrays to int64 scalars with one shared mixed radix."""
-    mins = np.min([r.min(axis=0) for r in rows_list if len(r)], axis=0).astype(np.int64)
-    maxs = np.max([r.max(axis=0) for r in rows_list if len(r)], axis=0).astype(np.int64)
+    """Map int32 [*, D] row arrays to int64 scalars with one shared mixed radix.
+    Columns whose raw range would overflow are first replaced by their dense rank."""
+    nonempty = [r for r in rows_list if len(r)]
+    mins = np.min([r.min(axis=0) for r in nonempty], axis=0).astype(np.int64)
+    maxs = np.max([r.max(axis=0) for r in nonempty], axis=0).astype(np.int64)
     span = maxs - mins + 1
     total = 1
     for s in span:
         total *= int(s)
-    assert total < 2**62, "coordinate range too wide for the int64 packing used by the oracle"
+    cols = [[r[:, d].astype(np.int64) - mins[d] for d in range(r.shape[1])] for r in rows_list]
+    if total >= 2**62:
+        for d in range(len(span)):
+            allv = np.concatenate([c[d] for c in cols])
+            uniq, inv = np.unique(allv, return_inverse=True)
+            span[d] = len(uniq)
+            pos = 0
+            for c in cols:
+                c[d] = inv[pos:pos + len(c[d])].astype(np.int64)
+                pos += len(c[d])
+        total = 1
+        for s in span:
+            total *= int(s)
+        assert total < 2**62, "too many distinct coordinate values for the oracle's int64 packing"
     packed = []
-    for r in rows_list:
+    for c, r in zip(cols, rows_list):
         acc = np.zeros(len(r), dtype=np.int64)
         for d in range(r.shape[1]):
-            acc = acc * span[d] + (r[:, d].astype(np.int64) - mins[d])
+            acc = acc * span[d] + c[d]
         packed.append(acc)
     return packed
 

@@ -1,0 +1,208 @@
+"""GPU parity of the sparse convolution through the public surface: fp32 within 1e-4
+relative L2 of the reference's explicit-GEMM path, fp16/bf16 within 1e-2."""
+import numpy as np
+import pytest
+import torch
+import torch.nn as nn
+
+from oracle import kernel_map as km
+from oracle import sparse_conv as osc
+from warpconvnet_b200 import (SPARSE_CONV_FWD_ALGO_MODE as ALGO, ConvEpilogue, IntSearchResult, Sequential,
+                              SparseConv3d, Voxels, generate_kernel_map, spatially_sparse_conv)
+from warpconvnet_b200._native import CONV_SIMT, CONV_TCGEN05, check_device_status
+from warpconvnet_b200.datasets import synthetic
+from warpconvnet_b200.examples.mink_unet import MinkUNet18, randomize_batchnorm_
+from warpconvnet_b200.nn.functional.sparse_conv import sparse_conv_fused
+
+from conftest import rel_l2
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+TOL = {torch.float32: 1e-4, torch.float16: 1e-2, torch.bfloat16: 1e-2}
+
+
+def make_voxels(coords_b, feats, **kw):
+    offsets = np.concatenate([[0], np.cumsum(np.bincount(coords_b[:, 0]))])
+    return Voxels(torch.from_numpy(coords_b[:, 1:].copy()).to(DEV), feats.to(DEV), offsets=torch.from_numpy(offsets), **kw)
+
+
+@pytest.mark.parametrize("algo", [ALGO.EXPLICIT_GEMM, ALGO.IMPLICIT_GEMM, ALGO.CUTLASS_IMPLICIT_GEMM, ALGO.AUTO])
+def test_small_golden_fp32(golden, algo):
+    g, c = golden("kmap_small.npz"), golden("conv_small.npz")
+    x = make_voxels(g["coords"], torch.from_numpy(c["x"]))
+    y = spatially_sparse_conv(x, torch.from_numpy(c["w333"]).to(DEV), 3, fwd_algo=algo)
+    assert rel_l2(y.feature_tensor.cpu().numpy(), c["y333"]) < 1e-4
+    assert y.tensor_stride == (1, 1, 1) and torch.equal(y.coordinate_tensor, x.coordinate_tensor)
+    down = spatially_sparse_conv(x, torch.from_numpy(c["w222"]).to(DEV), 2, stride=2, fwd_algo=algo)
+    assert down.tensor_stride == (2, 2, 2)
+    assert np.array_equal(down.batch_indexed_coordinates.cpu().numpy(), g["out_coords"])
+    assert rel_l2(down.feature_tensor.cpu().numpy(), c["y222"]) < 1e-4
+    up = spatially_sparse_conv(down, torch.from_numpy(c["wtr"]).to(DEV), 2, stride=2, transposed=True,
+                               output_spatially_sparse_tensor=x, fwd_algo=algo)
+    assert up.tensor_stride == (1, 1, 1) and len(up) == len(x)
+    assert rel_l2(up.feature_tensor.cpu().numpy(), c["ytr"]) < 1e-4
+    assert len(x.cache) == 3  # 3x3x3 map, down map, transposed map share one cache
+    check_device_status(DEV)
+
+
+@pytest.mark.parametrize("algo", [ALGO.EXPLICIT_GEMM, ALGO.IMPLICIT_GEMM])
+def test_config1_golden_fp32(golden, algo):
+    """Single SparseConv3d layer: 20 000 voxels of [0,64)^3, C_in = C_out = 32, 3x3x3, fp32, no bias."""
+    g = golden("conv_config1.npz")
+    xyz = synthetic.random_cells(20000, 64, seed=0)
+    coords = np.concatenate([np.zeros((len(xyz), 1), np.int32), xyz], 1)
+    feats = torch.from_numpy(np.random.default_rng(0).standard_normal((20000, 32)).astype(np.float32))
+    x = make_voxels(coords, feats)
+    conv = SparseConv3d(32, 32, 3, bias=False, fwd_algo=algo).to(DEV)
+    assert float(conv.weight.abs().max()) <= float(g["weight_bound"]) * 1.05  # same init bound as the reference
+    with torch.no_grad():
+        conv.weight.copy_(torch.from_numpy(g["weight"]))
+        y = conv(x).feature_tensor.cpu().numpy()
+    assert rel_l2(y[g["rows"]], g["y_rows"]) < 1e-4
+    assert np.allclose(y.astype(np.float64).sum(0), g["y_colsum"], rtol=1e-4, atol=1e-3)
+    kmap = next(iter(x.cache.values()))
+    assert np.array_equal(kmap.offsets.numpy(), g["offsets"])
+    assert int(kmap.in_maps.long().sum()) == int(g["in_maps_sum"])
+
+
+def _layer_case(n, c_in, c_out, seed, mode="raster_crop"):
+    xyz = synthetic.room_scene(n, 0.02, seed, mode)
+    coords = np.concatenate([np.zeros((len(xyz), 1), np.int32), xyz], 1)
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(n, c_in, generator=g)
+    w = (torch.rand(27, c_in, c_out, generator=g) * 2 - 1) * (3.0 / (27 * c_in)) ** 0.5 * 1.73
+    return coords, x, w
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("c_in,c_out", [(32, 32), (64, 64), (96, 96), (128, 96), (128, 128), (256, 256), (384, 256),
+                                        (192, 128), (32, 64), (64, 16)])
+def test_tcgen05_matches_oracle(dtype, c_in, c_out):
+    n = 6000 if c_in * c_out > 20000 else 12000
+    coords, x, w = _layer_case(n, c_in, c_out, 400 + c_in + c_out)
+    xq, wq = x.to(dtype), w.to(dtype)
+    i, o, f, iden = km.generate_kernel_map(coords, coords, (1, 1, 1), (3, 3, 3))
+    ref = osc.explicit_gemm_forward(xq.float(), wq.float(), i, o, f, iden, n).numpy()  # fp32 on the quantised inputs
+    c = torch.from_numpy(coords).to(DEV)
+    kmap = generate_kernel_map(c, c, (1, 1, 1), (3, 3, 3))
+    y = sparse_conv_fused(xq.to(DEV), wq.to(DEV), kmap, n, algo=CONV_TCGEN05)
+    check_device_status(DEV)
+    assert y.dtype == dtype
+    assert rel_l2(y.float().cpu().numpy(), ref) < TOL[dtype]
+    y32 = sparse_conv_fused(xq.to(DEV), wq.to(DEV), kmap, n, out_dtype=torch.float32, algo=CONV_TCGEN05)
+    assert rel_l2(y32.cpu().numpy(), ref) < 1e-4  # fp32 accumulation: only summation order differs
+    ys = sparse_conv_fused(xq.to(DEV), wq.to(DEV), kmap, n, out_dtype=torch.float32, algo=CONV_SIMT)
+    assert rel_l2(ys.cpu().numpy(), ref) < 1e-4
+    # bit-reproducible
+    y2 = sparse_conv_fused(xq.to(DEV), wq.to(DEV), kmap, n, algo=CONV_TCGEN05)
+    assert torch.equal(y, y2)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+def test_fused_epilogue_matches_unfused_chain(dtype):
+    """conv -> BatchNorm1d(eval) -> + residual -> ReLU in one kernel vs the separate torch ops."""
+    n, c_in, c_out = 9000, 64, 96
+    coords, x, w = _layer_case(n, c_in, c_out, 77, "sample")
+    g = torch.Generator().manual_seed(1)
+    scale, shift = torch.rand(c_out, generator=g) + 0.5, torch.randn(c_out, generator=g) * 0.2
+    res = torch.randn(n, c_out, generator=g)
+    xq, wq, rq = x.to(dtype), w.to(dtype), res.to(dtype)
+    i, o, f, iden = km.generate_kernel_map(coords, coords, (1, 1, 1), (3, 3, 3))
+    conv = osc.explicit_gemm_forward(xq.float(), wq.float(), i, o, f, iden, n)
+    ref = torch.relu(conv * scale + shift + rq.float()).numpy()
+    c = torch.from_numpy(coords).to(DEV)
+    kmap = generate_kernel_map(c, c, (1, 1, 1), (3, 3, 3))
+    ep = ConvEpilogue(scale=scale.to(DEV), shift=shift.to(DEV), residual=rq.to(DEV), relu=True)
+    y = sparse_conv_fused(xq.to(DEV), wq.to(DEV), kmap, n, epilogue=ep)
+    assert rel_l2(y.float().cpu().numpy(), ref) < TOL[dtype]
+    assert float(y.min()) >= 0.0
+    check_device_status(DEV)
+
+
+def test_sequential_fuses_conv_bn_relu_in_eval():
+    n = 5000
+    coords, x, _ = _layer_case(n, 32, 64, 91, "sample")
+    vox = make_voxels(coords, x)
+    torch.manual_seed(0)
+    block = Sequential(SparseConv3d(32, 64, 3, bias=True), nn.BatchNorm1d(64), nn.ReLU()).to(DEV)
+    randomize_batchnorm_(block, 3)
+    block.eval()
+    with torch.no_grad():
+        fused = block(vox).feature_tensor
+        conv_out = block[0](vox)
+        unfused = block[2](block[1](conv_out.feature_tensor))
+    assert rel_l2(fused.cpu().numpy(), unfused.cpu().numpy()) < 1e-5
+    block.train()
+    out_train = block(vox)  # layer by layer, batch statistics, autograd alive
+    assert out_train.feature_tensor.requires_grad
+
+
+def test_backward_matches_explicit_formulas():
+    n = 3000
+    coords, x, w = _layer_case(n, 8, 12, 13, "sample")
+    i, o, f, iden = km.generate_kernel_map(coords, coords, (1, 1, 1), (3, 3, 3))
+    xr, wr = x.clone().requires_grad_(True), w.clone().requires_grad_(True)
+    yr = torch.zeros(n, 12)
+    for k in range(27):
+        s, e = int(f[k]), int(f[k + 1])
+        yr = yr.index_add(0, torch.from_numpy(o[s:e]).long(), xr[torch.from_numpy(i[s:e]).long()] @ wr[k])
+    go = torch.randn(n, 12, generator=torch.Generator().manual_seed(2))
+    yr.backward(go)
+    for algo in (ALGO.EXPLICIT_GEMM, ALGO.IMPLICIT_GEMM):
+        xg = x.clone().to(DEV).requires_grad_(True)
+        wg = w.clone().to(DEV).requires_grad_(True)
+        vox = make_voxels(coords, xg)
+        y = spatially_sparse_conv(vox, wg, 3, fwd_algo=algo)
+        y.feature_tensor.backward(go.to(DEV))
+        assert rel_l2(xg.grad.cpu().numpy(), xr.grad.numpy()) < 1e-4
+        assert rel_l2(wg.grad.cpu().numpy(), wr.grad.numpy()) < 1e-4
+
+
+def test_surface_errors_and_shortcuts():
+    n = 2000
+    coords, x, w = _layer_case(n, 8, 12, 5, "sample")
+    vox = make_voxels(coords, x)
+    with pytest.raises(TypeError):
+        spatially_sparse_conv(x.to(DEV), w.to(DEV), 3)
+    with pytest.raises(AssertionError):
+        spatially_sparse_conv(vox, w[:8].to(DEV), 2, stride=2, transposed=True)
+    with pytest.raises(ValueError):
+        spatially_sparse_conv(vox, w.to(DEV), 3, fwd_algo="winograd")
+    # 1x1x1: a plain matmul, coordinates and cache untouched
+    w1 = torch.randn(1, 8, 5)
+    b = torch.randn(5)
+    y = spatially_sparse_conv(vox, w1.to(DEV), 1, bias=b.to(DEV))
+    assert rel_l2(y.feature_tensor.cpu().numpy(), (x @ w1[0] + b).numpy()) < 1e-5 and vox.cache is None
+    # list of algorithms, string algorithm, bias on the fused path
+    y2 = spatially_sparse_conv(vox, w.to(DEV), 3, bias=torch.ones(12, device=DEV),
+                               fwd_algo=[ALGO.EXPLICIT_GEMM, ALGO.IMPLICIT_GEMM])
+    y3 = spatially_sparse_conv(vox, w.to(DEV), 3, bias=torch.ones(12, device=DEV), fwd_algo="explicit_gemm")
+    assert rel_l2(y2.feature_tensor.cpu().numpy(), y3.feature_tensor.cpu().numpy()) < 1e-5
+    # a compact user-supplied map drives the fused kernel too
+    i, o, f, iden = km.generate_kernel_map(coords, coords, (1, 1, 1), (3, 3, 3))
+    user = IntSearchResult(torch.from_numpy(i).to(DEV), torch.from_numpy(o).to(DEV), torch.from_numpy(f), iden)
+    y4 = sparse_conv_fused(x.to(DEV), w.to(DEV), user, n)
+    assert rel_l2(y4.cpu().numpy(), (y3.feature_tensor - 1).cpu().numpy()) < 1e-5
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+def test_minkunet_matches_oracle(dtype):
+    """U-Net forward (all layer kinds: 1x1, 3x3x3, stride-2 down, transposed up, skip concat,
+    fused BN/ReLU/residual) against the CPU restatement of the reference model."""
+    scenes = [synthetic.room_scene(6000, 0.05, 600 + s, "raster_crop") for s in range(2)]
+    coords, offsets = synthetic.batch_scenes(scenes)
+    feats = torch.rand(len(coords), 3, generator=torch.Generator().manual_seed(0))
+    torch.manual_seed(0)
+    model = MinkUNet18(3, 20)
+    randomize_batchnorm_(model, 1)
+    model.eval()
+    ref = osc.minkunet_forward(model.state_dict(), coords, feats, layers=(2,) * 8).numpy()
+    m = model.to(DEV).to(dtype)
+    vox = Voxels(torch.from_numpy(coords[:, 1:].copy()).to(DEV), feats.to(DEV).to(dtype), offsets=torch.from_numpy(offsets))
+    with torch.no_grad():
+        out = m(vox)
+    check_device_status(DEV)
+    assert out.feature_tensor.shape == (len(coords), 20)
+    err = rel_l2(out.feature_tensor.float().cpu().numpy(), ref)
+    assert err < (1e-4 if dtype == torch.float32 else 2e-2), err
+    assert len(out.cache) == 13  # 5 3x3x3 maps + 4 down maps + 4 transposed views

@@ -1,0 +1,210 @@
+"""GPU parity: hash table, kernel map, strided coordinates and Morton code against
+the oracle and the golden vectors generated from the reference (bit-exact)."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import kernel_map as km
+from warpconvnet_b200 import (HashMethod, IntSearchResult, TorchHashTable, generate_kernel_map, morton_code,
+                              stride_coords)
+from warpconvnet_b200._native import check_device_status
+from warpconvnet_b200.datasets import synthetic
+from warpconvnet_b200.geometry.coords.ops.stride import unique_strided_rows
+from warpconvnet_b200.geometry.coords.search.torch_discrete import _kernel_map_from_size
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(DEV)
+
+
+def assert_map_equal(res: IntSearchResult, i, o, f):
+    assert np.array_equal(res.offsets.numpy(), f)
+    assert np.array_equal(res.in_maps.cpu().numpy(), i)
+    assert np.array_equal(res.out_maps.cpu().numpy(), o)
+
+
+@pytest.mark.parametrize("method", list(HashMethod))
+def test_hash_search_golden(golden, method):
+    g = golden("kmap_small.npz")
+    t = TorchHashTable.from_keys(dev(g["coords"]), hash_method=method)
+    assert t.capacity == max(16, 2 * len(g["coords"])) and t.key_dim == 4
+    r = t.search(dev(g["queries"])).cpu().numpy()
+    assert np.array_equal(r, g["search"])
+    # every inserted key is found at its own row; absent keys give -1
+    assert np.array_equal(t.search(dev(g["coords"])).cpu().numpy(), np.arange(len(g["coords"]), dtype=np.int32))
+    check_device_status(DEV)
+
+
+def test_hash_duplicates_and_unique_index():
+    rng = np.random.default_rng(5)
+    base = rng.integers(0, 6, size=(5000, 4)).astype(np.int32)
+    t = TorchHashTable(2 * len(base))
+    t.insert(dev(base))
+    r = t.search(dev(base)).cpu().numpy()
+    assert np.array_equal(r, km.hash_search(base, base))  # smallest row index of each key
+    uniq = t.unique_index.cpu().numpy()
+    assert len(uniq) == len(np.unique(base, axis=0))
+    assert np.array_equal(np.unique(base[uniq], axis=0), np.unique(base, axis=0))
+    d = t.to_dict()
+    t2 = TorchHashTable.from_dict(d, device=DEV)
+    assert np.array_equal(t2.search(dev(base)).cpu().numpy(), r)
+
+
+def test_hash_errors():
+    t = TorchHashTable(16)
+    with pytest.raises(RuntimeError):
+        t.search(torch.zeros(1, 4, dtype=torch.int32, device=DEV))
+    with pytest.raises(AssertionError):
+        t.insert(torch.zeros(9, 4, dtype=torch.int32, device=DEV))  # > capacity / 2
+    with pytest.raises(ValueError):
+        t.insert(torch.zeros(4, dtype=torch.int32, device=DEV))
+    with pytest.raises(TypeError):
+        t.insert(torch.zeros(2, 4, dtype=torch.float32, device=DEV))
+    with pytest.raises(ValueError):
+        t.insert(torch.zeros(2, 4, dtype=torch.int32))
+
+
+@pytest.mark.parametrize("tag,stride,ks", [("333", (1, 1, 1), (3, 3, 3)), ("222", (2, 2, 2), (2, 2, 2)),
+                                            ("312", (1, 1, 1), (3, 1, 2))])
+def test_kernel_map_golden(golden, tag, stride, ks):
+    g = golden("kmap_small.npz")
+    out_coords = g["out_coords"] if tag == "222" else g["coords"]
+    res = generate_kernel_map(dev(g["coords"]), dev(out_coords), stride, ks)
+    assert res.identity_map_index == (13 if tag == "333" else None)
+    nbr = res.neighbor_table(len(out_coords)).cpu().numpy()
+    assert np.array_equal(nbr, km.kernel_map_found(g["coords"], out_coords, stride, ks))
+    assert_map_equal(res, g["in" + tag], g["out" + tag], g["off" + tag])
+    # per-offset slices and the dense form rebuilt from the compact one
+    a, b = res[5]
+    assert len(a) == res.numel(5) == int(g["off" + tag][6] - g["off" + tag][5])
+    rebuilt = IntSearchResult(res.in_maps, res.out_maps, res.offsets).neighbor_table(len(out_coords))
+    assert np.array_equal(rebuilt.cpu().numpy(), nbr)
+
+
+def test_transposed_map_golden(golden):
+    g = golden("kmap_small.npz")
+    fwd = generate_kernel_map(dev(g["coords"]), dev(g["out_coords"]), (2, 2, 2), (2, 2, 2))
+    tr = fwd.swapped(num_in=len(g["coords"]))
+    nbr_t = tr.neighbor_table(len(g["coords"])).cpu().numpy()
+    expect = np.full((8, len(g["coords"])), -1, np.int32)
+    for k in range(8):
+        s, e = g["tr_off"][k], g["tr_off"][k + 1]
+        expect[k, g["tr_out"][s:e]] = g["tr_in"][s:e]
+    assert np.array_equal(nbr_t, expect)
+    assert_map_equal(tr, g["tr_in"], g["tr_out"], g["tr_off"])
+
+
+@pytest.mark.parametrize("method", list(HashMethod))
+def test_kernel_map_vs_direct_search(method):
+    """Per-offset map equals a direct hash search of out*stride + offset
+    (the check of the reference's tests/nn/test_sparse_conv.py:109-134)."""
+    scenes = [synthetic.room_scene(20000, 0.05, 310 + s, "sample") for s in range(2)]
+    coords, _ = synthetic.batch_scenes(scenes)
+    c = dev(coords)
+    res = generate_kernel_map(c, c, (1, 1, 1), (3, 3, 3), hash_method=method)
+    table = TorchHashTable.from_keys(c, hash_method=method)
+    offs = km.kernel_offsets_from_size((3, 3, 3))
+    for k in (0, 7, 13, 26):
+        direct = table.search(c + dev(offs[k])[None, :]).cpu().numpy()
+        i, o = res[k]
+        hit = direct >= 0
+        assert np.array_equal(i.cpu().numpy(), direct[hit]) and np.array_equal(o.cpu().numpy(), np.nonzero(hit)[0])
+    a = km.generate_kernel_map(coords, coords, (1, 1, 1), (3, 3, 3))
+    assert_map_equal(res, *a[:3])
+
+
+def test_skip_symmetric_is_prefix():
+    """skip_symmetric map = first K//2 offsets of the full map (tests/nn/test_sparse_conv.py:137-181)."""
+    xyz = synthetic.random_cells(5000, 24, seed=2)
+    c = dev(np.concatenate([np.zeros((len(xyz), 1), np.int32), xyz], 1))
+    full = generate_kernel_map(c, c, (1, 1, 1), (3, 3, 3))
+    half = generate_kernel_map(c, c, (1, 1, 1), (3, 3, 3), skip_symmetric_kernel_map=True)
+    assert len(half) == 13 and half.identity_map_index == 13
+    n = int(full.offsets[13])
+    assert np.array_equal(half.offsets.numpy(), full.offsets.numpy()[:14])
+    assert torch.equal(half.in_maps, full.in_maps[:n]) and torch.equal(half.out_maps, full.out_maps[:n])
+
+
+def test_kernel_map_edge_cases():
+    # single voxel
+    one = torch.tensor([[0, 5, -3, 2]], dtype=torch.int32, device=DEV)
+    res = generate_kernel_map(one, one, (1, 1, 1), (3, 3, 3))
+    assert res.offsets.tolist() == [0] * 14 + [1] * 14
+    assert res.in_maps.tolist() == [0] and res.out_maps.tolist() == [0]
+    # no query at all
+    empty = torch.zeros((0, 4), dtype=torch.int32, device=DEV)
+    res = generate_kernel_map(one, empty, (1, 1, 1), (3, 3, 3))
+    assert res.offsets.tolist() == [0] * 28 and len(res.in_maps) == 0
+    # a batch item without voxels, coordinates near the int range
+    c = np.array([[0, 2**30, -2**30, 7], [0, 2**30 + 1, -2**30, 7], [2, 0, 0, 0], [2, 0, 0, 1]], np.int32)
+    res = generate_kernel_map(dev(c), dev(c), (1, 1, 1), (3, 3, 3))
+    exp = km.generate_kernel_map(c, c, (1, 1, 1), (3, 3, 3))
+    assert_map_equal(res, *exp[:3])
+    with pytest.raises(AssertionError):
+        generate_kernel_map(dev(c).long(), dev(c), (1, 1, 1), (3, 3, 3))
+    with pytest.raises(AssertionError):
+        generate_kernel_map(dev(c), dev(c), (1, 1, 1), (3, 3, 3), kernel_dilation=(2, 2, 2))
+
+
+def test_stride_coords(golden):
+    g = golden("kmap_small.npz")
+    out, offsets = stride_coords(dev(g["coords"]), (2, 2, 2))
+    assert np.array_equal(out.cpu().numpy(), g["out_coords"])  # first-occurrence order, as the oracle
+    assert offsets.tolist() == np.concatenate([[0], np.cumsum(np.bincount(g["out_coords"][:, 0]))]).tolist()
+    rows, uidx, parent = unique_strided_rows(dev(g["coords"]), (2, 2, 2), return_parent=True)
+    q = np.floor_divide(g["coords"], np.array([1, 2, 2, 2]))
+    assert np.array_equal(rows.cpu().numpy()[parent.cpu().numpy()], q)
+    assert np.array_equal(q[uidx.cpu().numpy()], rows.cpu().numpy()) and (np.diff(uidx.cpu().numpy()) > 0).all()
+    same, offs1 = stride_coords(dev(g["coords"]), (1, 1, 1))
+    assert same.shape[0] == len(g["coords"]) and offs1[-1] == len(g["coords"])
+    # anisotropic stride with negatives: floor division, not truncation
+    out2, _ = stride_coords(dev(g["coords"]), (2, 1, 3))
+    exp2, _ = km.stride_coords(g["coords"], (2, 1, 3))
+    assert np.array_equal(out2.cpu().numpy(), exp2)
+
+
+def test_morton(golden):
+    g = golden("kmap_small.npz")
+    xyz = dev(g["morton_xyz"].astype(np.int32))
+    codes = morton_code(xyz)
+    assert np.array_equal(codes.cpu().numpy(), g["morton"])
+    shifted = morton_code(xyz - 1000)  # the minimum is subtracted first
+    assert torch.equal(shifted, codes)
+    big = torch.tensor([[0, 0, 0], [2**20 - 1, 2**20 - 1, 2**20 - 1], [1, 0, 0], [0, 1, 0], [0, 0, 1]],
+                       dtype=torch.int32, device=DEV)
+    assert morton_code(big).tolist() == [0, 2**60 - 1, 1, 2, 4]
+
+
+@pytest.mark.parametrize("mode,n_per_scene", [("raster_crop", 250000), ("sample", 250000)])
+def test_kernel_map_full_size_properties(mode, n_per_scene):
+    """Config-2 size (4 rooms x 250k voxels): properties that need no CPU replay —
+    symmetry of the 3x3x3 map, one parent per voxel in the 2x2x2 map, swap involution —
+    plus a replay of a slice against the oracle."""
+    scenes = [synthetic.room_scene(n_per_scene, 0.02, 100 + s, mode) for s in range(4)]
+    coords, _ = synthetic.batch_scenes(scenes)
+    c = dev(coords)
+    res = generate_kernel_map(c, c, (1, 1, 1), (3, 3, 3))
+    nbr = res.neighbor_table(len(coords))
+    n = len(coords)
+    ar = torch.arange(n, device=DEV, dtype=torch.int32)
+    assert torch.equal(nbr[13], ar)
+    for k in (0, 4, 12):  # pair (m -> j at k) <=> (j -> m at 26-k)
+        j = nbr[k].long()
+        hit = j >= 0
+        assert torch.equal(nbr[26 - k][j[hit]], ar[hit])
+    off = res.offsets
+    assert off[-1] == int((nbr >= 0).sum()) and all(int(off[k + 1] - off[k]) == int(off[27 - k] - off[26 - k]) for k in range(13))
+    sub = slice(0, 3000)
+    exp = km.kernel_map_found(coords, coords[sub], (1, 1, 1), (3, 3, 3))
+    assert np.array_equal(nbr[:, sub].cpu().numpy(), exp)
+    out, offsets = stride_coords(c, (2, 2, 2))
+    exp_out, _ = km.stride_coords(coords, (2, 2, 2))
+    assert np.array_equal(out.cpu().numpy(), exp_out)
+    down = generate_kernel_map(c, out, (2, 2, 2), (2, 2, 2))
+    assert int(down.offsets[-1]) == n and len(torch.unique(down.in_maps)) == n
+    up = down.swapped(num_in=n)
+    assert int((up.neighbor_table(n) >= 0).sum(0).min()) == 1 and int((up.neighbor_table(n) >= 0).sum(0).max()) == 1
+    check_device_status(DEV)

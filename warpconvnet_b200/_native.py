@@ -8,6 +8,7 @@ from __future__ import annotations
 
 import ctypes
 import os
+from collections import Counter
 from typing import Optional
 
 import torch
@@ -46,14 +47,49 @@ SIGNATURES = {
                      _c_vp, _c_vp, _c_vp, _c_i32, _c_vp, _c_i32, _c_vp, _c_vp],
 }
 
-_lib: Optional[ctypes.CDLL] = None
+_lib = None
+
+# Kernels launched by one call of each entry point (0: host-only query).  Used to
+# count this library's launches, e.g. by the benchmark harness.
+KERNELS_PER_CALL = {
+    "wcn_hash_build": 2, "wcn_hash_search": 1, "wcn_unique_mark": 3, "wcn_unique_emit": 2, "wcn_kmap_search": 1,
+    "wcn_kmap_scan": 2, "wcn_kmap_compact": 1, "wcn_nbr_from_maps": 1, "wcn_nbr_transpose": 1, "wcn_morton20": 1,
+    "wcn_gather_rows": 1, "wcn_scatter_add_rows": 1, "wcn_conv_pack_weight": 1, "wcn_conv_fwd": 1,
+}
+LAUNCH_COUNTS: Counter = Counter()
+
+
+class _CountingLib:
+    """Attribute access returns the C function wrapped so that calls are counted."""
+
+    def __init__(self, handle):
+        self._handle = handle
+        self._wrapped = {}
+
+    def __getattr__(self, name):
+        fn = self._wrapped.get(name)
+        if fn is None:
+            raw = getattr(self._handle, name)
+            n = KERNELS_PER_CALL.get(name, 0)
+            if n:
+                def fn(*args, _raw=raw, _name=name, _n=n):
+                    LAUNCH_COUNTS[_name] += _n
+                    return _raw(*args)
+            else:
+                fn = raw
+            self._wrapped[name] = fn
+        return fn
+
+
+def launches_total() -> int:
+    return sum(LAUNCH_COUNTS.values())
 
 
 class NativeLibraryError(RuntimeError):
     pass
 
 
-def lib() -> ctypes.CDLL:
+def lib():
     """The loaded library; raises NativeLibraryError when it is not built."""
     global _lib
     if _lib is None:
@@ -71,7 +107,7 @@ def lib() -> ctypes.CDLL:
             fn.restype = ctypes.c_int
         handle.wcn_status_string.argtypes = [ctypes.c_int]
         handle.wcn_status_string.restype = ctypes.c_char_p
-        _lib = handle
+        _lib = _CountingLib(handle)
     return _lib
 
 

@@ -76,6 +76,7 @@ class Voxels(Geometry):
         kwargs = self.extra_attributes
         kwargs["ordering"] = ordering
         kwargs["code"] = res.codes
+        kwargs["perm"] = res.perm  # sorted = original[perm]
         kwargs.pop("_cache", None)  # cached maps index the old row order
         return self.__class__(
             batched_coordinates=IntCoords(self.coordinate_tensor[res.perm], self.offsets,
