@@ -21,11 +21,10 @@
 namespace {
 
 constexpr int BLOCK_M = 128;
-constexpr int STAGES = 4;
-constexpr int LAG = STAGES - 1;       // copy groups kept in flight per producer thread
+constexpr int MAX_STAGES = 8;
 constexpr int PRODUCERS = 128;        // warps 0..3; also the epilogue warps
 constexpr int THREADS = PRODUCERS + 32;
-constexpr int MAX_OFFSETS = 32;
+constexpr int MAX_OFFSETS = 27;
 constexpr long long kWaitCycles = 4000000000ll;  // about two seconds
 
 struct ConvTcParams {
@@ -41,6 +40,8 @@ struct ConvTcParams {
   void* out;
   int32_t* dev_status;
   uint32_t tmem_cols;
+  int block_n;   // output columns per CTA (blockIdx.y selects the column block)
+  int stages;    // shared-memory pipeline depth, 2..MAX_STAGES
 };
 
 // ------------------------------------------------------------------ PTX wrappers
@@ -83,6 +84,10 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int32_t
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32_t src_bytes) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+// Arrive on `bar` once all cp.async copies issued so far by this thread have landed.
+__device__ __forceinline__ void cp_async_arrive(uint32_t bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N> __device__ __forceinline__ void cp_async_wait() {
@@ -183,13 +188,17 @@ template <int BK, bool BF16, typename TO>
 __global__ void __launch_bounds__(THREADS, 1) conv_tcgen05_kernel(const ConvTcParams p) {
   constexpr int RB = BK * 2;         // bytes per tile row
   constexpr int CH = RB / 16;        // 16-byte chunks per tile row
+  constexpr int RPI = 32 / CH;       // tile rows covered by one warp-wide copy instruction
   constexpr int A_BYTES = BLOCK_M * RB;
   extern __shared__ uint8_t smem_raw[];
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int64_t m0 = (int64_t)blockIdx.x * BLOCK_M;
+  const int n0 = blockIdx.y * p.block_n;
+  const int BN = p.block_n;
+  const int S = p.stages;
   const int KB = p.c_in / BK;
-  const int B_BYTES = p.c_out * RB;
+  const int B_BYTES = BN * RB;
 
   __shared__ int s_skip;  // block-uniform: an earlier launch on this status word failed
   if (tid == 0) s_skip = *(volatile int32_t*)p.dev_status;
@@ -199,17 +208,17 @@ __global__ void __launch_bounds__(THREADS, 1) conv_tcgen05_kernel(const ConvTcPa
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* gen = smem_raw + (base - smem_u32(smem_raw));
   const uint32_t a_base = base;
-  const uint32_t b_base = a_base + STAGES * A_BYTES;
-  const uint32_t misc = b_base + STAGES * B_BYTES;
+  const uint32_t b_base = a_base + S * A_BYTES;
+  const uint32_t misc = b_base + S * B_BYTES;
   uint8_t* misc_gen = gen + (misc - base);
-  int32_t* rows_idx = reinterpret_cast<int32_t*>(misc_gen);                       // [K][128]
+  int32_t* rows_idx = reinterpret_cast<int32_t*>(misc_gen);                            // [K][128]
   uint64_t* bars = reinterpret_cast<uint64_t*>(misc_gen + MAX_OFFSETS * BLOCK_M * 4);  // full[S], empty[S], acc
-  uint32_t* holder = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 1);
+  uint32_t* holder = reinterpret_cast<uint32_t*>(bars + 2 * MAX_STAGES + 1);
   uint32_t* act_mask = holder + 1;
-  const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8 * STAGES, acc_bar = full0 + 16 * STAGES;
+  const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8 * MAX_STAGES, acc_bar = full0 + 16 * MAX_STAGES;
 
   if (tid == 0) {
-    for (int s = 0; s < STAGES; ++s) {
+    for (int s = 0; s < S; ++s) {
       mbar_init(full0 + 8 * s, PRODUCERS);
       mbar_init(empty0 + 8 * s, 1);
     }
@@ -240,45 +249,49 @@ __global__ void __launch_bounds__(THREADS, 1) conv_tcgen05_kernel(const ConvTcPa
 
   bool ok = true;
   if (tid < PRODUCERS) {
-    // ---------------- producers: gather A rows + copy the weight slice
+    // ---------------- producers: gather A rows + copy the weight slice.
+    // A: one warp instruction covers RPI rows x one full tile row each (CH lanes per row),
+    //    so every request is a whole RB-byte segment of a feature row.
+    const int sub_row = lane / CH, chunk = lane % CH;
     int it = 0;
     uint32_t rest = mask;
     while (rest && ok) {
       const int k = __ffs(rest) - 1;
       rest &= rest - 1;
-      const int src = rows_idx[k * BLOCK_M + tid];
-      const char* arow = p.feats + (int64_t)(src >= 0 ? src : 0) * p.c_in * 2;
-      const uint32_t asz = src >= 0 ? 16u : 0u;
+      const char* asrc[CH];
+      uint32_t aoff[CH];
+#pragma unroll
+      for (int j = 0; j < CH; ++j) {
+        const int row = warp * 32 + j * RPI + sub_row;
+        const int src = rows_idx[k * BLOCK_M + row];
+        asrc[j] = src >= 0 ? p.feats + (int64_t)src * p.c_in * 2 + chunk * 16 : nullptr;
+        aoff[j] = tile_offset<RB>(row, chunk);
+      }
+      const char* bsrc_k = p.wpacked + ((int64_t)k * KB * p.c_out + n0) * RB;
       for (int kb = 0; kb < KB; ++kb, ++it) {
-        const int s = it % STAGES;
-        if (!mbar_wait(empty0 + 8 * s, ((it / STAGES) & 1) ^ 1, p.dev_status)) { ok = false; break; }
+        const int s = it % S;
+        if (!mbar_wait(empty0 + 8 * s, ((it / S) & 1) ^ 1, p.dev_status)) { ok = false; break; }
         const uint32_t a_dst = a_base + s * A_BYTES;
 #pragma unroll
-        for (int c = 0; c < CH; ++c) cp_async16(a_dst + tile_offset<RB>(tid, c), arow + kb * RB + c * 16, asz);
+        for (int j = 0; j < CH; ++j)
+          cp_async16(a_dst + aoff[j], asrc[j] ? asrc[j] + kb * RB : p.feats, asrc[j] ? 16u : 0u);
         const uint32_t b_dst = b_base + s * B_BYTES;
-        const char* bsrc = p.wpacked + ((int64_t)(k * KB + kb) * p.c_out) * RB;
-        for (int j = tid; j < p.c_out * CH; j += PRODUCERS)
+        const char* bsrc = bsrc_k + (int64_t)kb * p.c_out * RB;
+        for (int j = tid; j < BN * CH; j += PRODUCERS)
           cp_async16(b_dst + tile_offset<RB>(j / CH, j % CH), bsrc + (int64_t)j * 16, 16u);
-        cp_async_commit();
-        if (it >= LAG) {
-          cp_async_wait<LAG>();
-          fence_proxy_async();
-          mbar_arrive(full0 + 8 * ((it - LAG) % STAGES));
-        }
+        cp_async_arrive(full0 + 8 * s);  // hardware arrives when this thread's copies have landed
       }
     }
+    cp_async_commit();
     cp_async_wait<0>();
-    fence_proxy_async();
-    if (ok) {
-      for (int j = (T > LAG ? T - LAG : 0); j < T; ++j) mbar_arrive(full0 + 8 * (j % STAGES));
-    }
   } else if (lane == 0) {
     // ---------------- MMA issuer
     const uint32_t idesc = (1u << 4) | ((BF16 ? 1u : 0u) << 7) | ((BF16 ? 1u : 0u) << 10) |
-                           ((uint32_t)(p.c_out >> 3) << 17) | ((uint32_t)(BLOCK_M >> 4) << 24);
+                           ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BLOCK_M >> 4) << 24);
     for (int it = 0; it < T; ++it) {
-      const int s = it % STAGES;
-      if (!mbar_wait(full0 + 8 * s, (it / STAGES) & 1, p.dev_status)) { ok = false; break; }
+      const int s = it % S;
+      if (!mbar_wait(full0 + 8 * s, (it / S) & 1, p.dev_status)) { ok = false; break; }
+      fence_proxy_async();  // copies were written through the generic proxy, the MMA reads through the async one
       tc_fence_after();
       const uint64_t adesc = smem_desc<RB>(a_base + s * A_BYTES);
       const uint64_t bdesc = smem_desc<RB>(b_base + s * B_BYTES);
@@ -299,13 +312,13 @@ __global__ void __launch_bounds__(THREADS, 1) conv_tcgen05_kernel(const ConvTcPa
     // tcgen05.ld is warp-collective, so the decision to read must be warp-uniform
     if (__all_sync(0xFFFFFFFFu, ok && *(volatile int32_t*)p.dev_status == 0)) {
       const uint32_t trow = tmem_base + ((uint32_t)(warp * 32) << 16);
-      TO* orow = reinterpret_cast<TO*>(p.out) + m * p.c_out;
-      const TO* rrow = p.residual ? reinterpret_cast<const TO*>(p.residual) + m * p.c_out : nullptr;
-      for (int c0 = 0; c0 < p.c_out; c0 += 16) {
+      TO* orow = reinterpret_cast<TO*>(p.out) + m * p.c_out + n0;
+      const TO* rrow = p.residual ? reinterpret_cast<const TO*>(p.residual) + m * p.c_out + n0 : nullptr;
+      for (int c0 = 0; c0 < BN; c0 += 16) {
         float y[16];
         if (T > 0) {
           uint32_t r[16];
-          tmem_ld16(trow + (uint32_t)c0, r);  // warp-collective: executed by all lanes
+          tmem_ld16(trow + (uint32_t)c0, r);  // executed by all lanes of the warp
           tmem_ld_wait();
 #pragma unroll
           for (int i = 0; i < 16; ++i) y[i] = __uint_as_float(r[i]);
@@ -316,11 +329,11 @@ __global__ void __launch_bounds__(THREADS, 1) conv_tcgen05_kernel(const ConvTcPa
         if (m < p.M) {
           if (p.scale) {
 #pragma unroll
-            for (int i = 0; i < 16; ++i) y[i] *= __ldg(&p.scale[c0 + i]);
+            for (int i = 0; i < 16; ++i) y[i] *= __ldg(&p.scale[n0 + c0 + i]);
           }
           if (p.shift) {
 #pragma unroll
-            for (int i = 0; i < 16; ++i) y[i] += __ldg(&p.shift[c0 + i]);
+            for (int i = 0; i < 16; ++i) y[i] += __ldg(&p.shift[n0 + c0 + i]);
           }
           if (rrow) {
             float res[16];
@@ -361,17 +374,53 @@ __global__ void pack_weight_kernel(const T* __restrict__ w, T* __restrict__ pack
 
 inline int pick_bk(int c_in) { return c_in % 64 == 0 ? 64 : 32; }
 
-inline size_t smem_bytes(int bk, int c_out) {
-  return 1024 + (size_t)STAGES * (BLOCK_M + c_out) * bk * 2 + MAX_OFFSETS * BLOCK_M * 4 + (2 * STAGES + 1) * 8 + 64;
+inline size_t smem_bytes(int bk, int block_n, int stages) {
+  return 1024 + (size_t)stages * (BLOCK_M + block_n) * bk * 2 + MAX_OFFSETS * BLOCK_M * 4 +
+         (2 * MAX_STAGES + 1) * 8 + 64;
+}
+
+// Column split: small problems do not have enough 128-row tiles to occupy 148 SMs, so the
+// output columns are divided among CTAs (each re-gathers the rows, which stay in L2).
+inline int pick_block_n(int64_t tiles, int c_out) {
+  int best = c_out;
+  for (int split = 1; split <= 8; split *= 2) {
+    if (c_out % (16 * split) != 0 || c_out / split < 32) break;
+    best = c_out / split;
+    if (tiles * split >= 256) break;
+  }
+  return best;
+}
+
+// Pipeline depth: as deep as fits, leaving room for a second CTA per SM when stages are small.
+inline int pick_stages(int bk, int block_n) {
+  const size_t stage = (size_t)(BLOCK_M + block_n) * bk * 2;
+  const size_t budget = stage <= 24 * 1024 ? 96 * 1024 : 204 * 1024;  // <= 96 KiB: two CTAs share an SM
+  int s = (int)(budget / stage);
+  return s < 2 ? 2 : (s > MAX_STAGES ? MAX_STAGES : s);
 }
 
 template <int BK, bool BF16, typename TO>
-int launch_tc(const ConvTcParams& p, cudaStream_t st) {
-  const size_t smem = smem_bytes(BK, p.c_out);
+int launch_tc(ConvTcParams& p, cudaStream_t st) {
+  const int64_t tiles = (p.M + BLOCK_M - 1) / BLOCK_M;
+  p.block_n = pick_block_n(tiles, p.c_out);
+  p.stages = pick_stages(BK, p.block_n);
+  uint32_t cols = 32;
+  while ((int)cols < p.block_n) cols <<= 1;
+  p.tmem_cols = cols;
+  const size_t smem = smem_bytes(BK, p.block_n, p.stages);
   auto kern = conv_tcgen05_kernel<BK, BF16, TO>;
-  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
-    return WCN_ERR_INITIALIZATION;
-  const unsigned grid = (unsigned)((p.M + BLOCK_M - 1) / BLOCK_M);
+  static bool configured[64] = {};  // per template instance and device: opt in to large shared memory once
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return WCN_ERR_INITIALIZATION;
+  if (!configured[dev]) {
+    // the kernel also has a few bytes of static shared memory, which count against the 227 KiB limit
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 225 * 1024) != cudaSuccess) {
+      (void)cudaGetLastError();  // do not leave a sticky error for the caller's next CUDA call
+      return WCN_ERR_INITIALIZATION;
+    }
+    configured[dev] = true;
+  }
+  dim3 grid((unsigned)tiles, (unsigned)(p.c_out / p.block_n));
   kern<<<grid, THREADS, smem, st>>>(p);
   return cudaGetLastError() == cudaSuccess ? WCN_OK : WCN_ERR_EXECUTION;
 }
@@ -406,9 +455,6 @@ int wcn_conv_tcgen05_fwd(const void* feats, const void* packed, const int32_t* n
   p.M = M; p.K = K; p.c_in = c_in; p.c_out = c_out;
   p.scale = scale; p.shift = shift; p.residual = residual; p.relu = relu; p.out = out;
   p.dev_status = dev_status;
-  uint32_t cols = 32;
-  while ((int)cols < c_out) cols <<= 1;
-  p.tmem_cols = cols;
   const int bk = pick_bk(c_in);
   const bool bf = dtype == WCN_BF16;
 #define WCN_TC_CASE(BKV, BFV, TO) if (bk == BKV && bf == BFV) return launch_tc<BKV, BFV, TO>(p, st);

@@ -1,0 +1,111 @@
+"""Single-layer sweep of the sparse convolution: one synthetic room, kernel 3x3x3
+stride 1, 2x2x2 stride-2 down-sampling and 2x2x2 transposed up-sampling, for
+C_in = C_out in a list of widths and fp16 / bf16 features with fp32 accumulation.
+
+    python -m warpconvnet_b200.examples.layer_sweep --voxels 500000 --voxel-size 0.01
+
+Prints one JSON line per case: milliseconds (CUDA events, L2 flushed between
+iterations), useful TFLOP/s (2 * pairs * C_in * C_out / t; zero-filled rows do not
+count), algorithmic GB/s, the binding roofline and the fraction of it.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import numpy as np
+import torch
+
+from .. import POINT_ORDERING, Voxels, generate_kernel_map, stride_coords
+from .._native import CONV_AUTO, CONV_SIMT, CONV_TCGEN05, check_device_status
+from ..datasets import synthetic
+from ..nn.functional.sparse_conv import sparse_conv_fused
+
+DT = {"fp16": torch.float16, "bf16": torch.bfloat16, "fp32": torch.float32}
+ALGOS = {"auto": CONV_AUTO, "simt": CONV_SIMT, "tcgen05": CONV_TCGEN05}
+
+
+def peaks():
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))),
+                        "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        p = json.load(open(path))
+        return float(p["hbm_gbs"]), float(p["bf16_tflops"]), "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+def time_ms(fn, iters, flush):
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    total = 0.0
+    for _ in range(iters):
+        flush.zero_()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        fn()
+        e.record()
+        torch.cuda.synchronize()
+        total += s.elapsed_time(e)
+    return total / iters
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--voxels", type=int, default=500000)
+    ap.add_argument("--voxel-size", type=float, default=0.01)
+    ap.add_argument("--mode", default="raster_crop")
+    ap.add_argument("--channels", default="32,64,128,256")
+    ap.add_argument("--dtypes", default="fp16,bf16")
+    ap.add_argument("--kinds", default="conv3,down2,up2")
+    ap.add_argument("--algo", default="auto", choices=list(ALGOS))
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--no-sort", action="store_true", help="keep the generator's random row order")
+    args = ap.parse_args()
+    dev = torch.device("cuda", 0)
+    hbm, tflops, src = peaks()
+
+    xyz = synthetic.room_scene(args.voxels, args.voxel_size, 100, args.mode)
+    n = len(xyz)
+    vox = Voxels(torch.from_numpy(xyz).to(dev), torch.zeros(n, 1, device=dev), offsets=torch.tensor([0, n]))
+    if not args.no_sort:
+        vox = vox.sort(POINT_ORDERING.MORTON_XYZ)
+    fine = vox.batch_indexed_coordinates.contiguous()
+    coarse, _ = stride_coords(fine, (2, 2, 2))
+    maps = {
+        "conv3": (generate_kernel_map(fine, fine, (1, 1, 1), (3, 3, 3)), n, n),
+        "down2": (generate_kernel_map(fine, coarse, (2, 2, 2), (2, 2, 2)), n, len(coarse)),
+    }
+    maps["up2"] = (maps["down2"][0].swapped(num_in=n), len(coarse), n)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    g = torch.Generator(device="cpu").manual_seed(0)
+
+    for kind in args.kinds.split(","):
+        kmap, n_in, n_out = maps[kind]
+        nbr = kmap.neighbor_table(n_out)
+        pairs = int((nbr >= 0).sum().item())
+        K = nbr.shape[0]
+        for c in [int(v) for v in args.channels.split(",")]:
+            for dname in args.dtypes.split(","):
+                dt = DT[dname]
+                x = torch.randn(n_in, c, generator=g).to(dev, dt)
+                bound = (3.0 / (K * c)) ** 0.5 * 1.73
+                w = ((torch.rand(K, c, c, generator=g) * 2 - 1) * bound).to(dev, dt)
+                fn = lambda: sparse_conv_fused(x, w, kmap, n_out, algo=ALGOS[args.algo])
+                ms = time_ms(fn, args.iters, flush)
+                check_device_status(dev)
+                es = 4 if dt == torch.float32 else 2
+                flop = 2.0 * pairs * c * c
+                byts = es * (n_in * c + n_out * c + K * c * c) + 4.0 * n_out * K
+                t_tc, t_hbm = flop / (tflops * 1e12), byts / (hbm * 1e9)
+                print(json.dumps({
+                    "kind": kind, "c": c, "dtype": dname, "voxels_in": n_in, "voxels_out": n_out, "pairs": pairs,
+                    "pairs_per_out": pairs / n_out, "ms": ms, "useful_tflops": flop / ms / 1e9,
+                    "alg_gbs": byts / ms / 1e6, "bound": "tensor" if t_tc > t_hbm else "hbm",
+                    "roofline_frac": max(t_tc, t_hbm) / (ms * 1e-3), "peaks": src,
+                    "mvoxels_per_s": n_in / ms / 1e3}), flush=True)
+
+
+if __name__ == "__main__":
+    main()

@@ -407,9 +407,22 @@ def spatially_sparse_conv(
             out = _implicit_gemm_forward_logic(feats, weight, kernel_map, num_out, effective_compute_dtype,
                                                epilogue=ep)
 
-    return input_sparse_tensor.replace(
-        batched_coordinates=IntCoords(out_coords[:, 1:], offsets=out_offsets.cpu().int()),
-        batched_features=out, tensor_stride=out_tensor_stride)
+    # Output coordinates: the input's own coordinate object when they are unchanged, the
+    # target's for a transposed convolution, else a new one that already knows its
+    # batch-indexed form (so nothing is rebuilt layer after layer).
+    if output_spatially_sparse_tensor is not None and order == POINT_ORDERING.RANDOM:
+        src = output_spatially_sparse_tensor.batched_coordinates
+        out_ic = IntCoords(src.batched_tensor, offsets=src.offsets)
+        out_ic._bcoords, out_ic._hashmap = src._bcoords, src._hashmap
+    elif all(s == 1 for s in _stride) and order == POINT_ORDERING.RANDOM:
+        src = input_sparse_tensor.batched_coordinates
+        out_ic = IntCoords(src.batched_tensor, offsets=src.offsets)
+        out_ic._bcoords, out_ic._hashmap = src._bcoords, src._hashmap
+    else:
+        out_ic = IntCoords(out_coords[:, 1:], offsets=out_offsets.cpu().int())
+        out_ic._bcoords = out_coords
+    return input_sparse_tensor.replace(batched_coordinates=out_ic, batched_features=out,
+                                       tensor_stride=out_tensor_stride)
 
 
 def _merge_bias(epilogue: Optional[ConvEpilogue], bias: Optional[Tensor]) -> Optional[ConvEpilogue]:

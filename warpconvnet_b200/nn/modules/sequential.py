@@ -34,7 +34,19 @@ def run_forward(module: nn.Module, x, in_sf: Geometry):
 
 
 def fold_batchnorm(bn: nn.BatchNorm1d):
-    """Eval-mode BatchNorm as y = x * scale + shift (fp32 vectors)."""
+    """Eval-mode BatchNorm as y = x * scale + shift (fp32 vectors), cached on the
+    module until one of its tensors changes."""
+    tensors = (bn.running_var, bn.running_mean, bn.weight, bn.bias)
+    tag = tuple((t.data_ptr(), t._version) if t is not None else None for t in tensors)
+    hit = bn.__dict__.get("_wcn_folded")
+    if hit is not None and hit[0] == tag:
+        return hit[1], hit[2]
+    scale, shift = _fold_batchnorm(bn)
+    bn.__dict__["_wcn_folded"] = (tag, scale, shift)
+    return scale, shift
+
+
+def _fold_batchnorm(bn: nn.BatchNorm1d):
     var = bn.running_var.detach().float()
     mean = bn.running_mean.detach().float()
     gamma = bn.weight.detach().float() if bn.weight is not None else torch.ones_like(var)
