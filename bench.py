@@ -50,6 +50,7 @@ def parse_args():
     ap.add_argument("--mode", choices=["raster_crop", "sample"], default="raster_crop")
     ap.add_argument("--cpu-sample-voxels", type=int, default=150000)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--layers", action="store_true", help="print a per-launch table of the convolutions to stderr")
     return ap.parse_args()
 
 
@@ -206,6 +207,15 @@ class ConvProfile:
                 tc_ms += ms; tc_flop += fl; tc_n += 1
         return {"launches": n, "ms": tot_ms, "flop": tot_flop, "tc_launches": tc_n, "tc_ms": tc_ms, "tc_flop": tc_flop}
 
+    def table(self, last_n):
+        rows = []
+        for s, e, nbr, c_in, c_out, kind in self.records[-last_n:]:
+            pairs = int((nbr >= 0).sum().item())
+            ms = s.elapsed_time(e)
+            rows.append(f"{kind:8s} K={nbr.shape[0]:2d} M={nbr.shape[1]:8d} {c_in:4d}->{c_out:4d} pairs/M={pairs / max(nbr.shape[1], 1):5.2f} "
+                        f"{ms * 1e3:8.1f} us {2.0 * pairs * c_in * c_out / ms / 1e9:7.1f} TFLOP/s")
+        return "\n".join(rows)
+
 
 def install_conv_profiler(profile):
     """Wrap the fused-convolution entry so each launch is bracketed by events on the launching stream."""
@@ -316,6 +326,8 @@ def run_gpu_arm(args):
         barrier()
         restore()
         prof = profile.summarise()
+        if args.layers and rank == 0:
+            print(profile.table(len(profile.records) // prof_steps), file=sys.stderr)
 
     total_vox = n_vox * world  # every rank holds a batch of the same size
     if world > 1:

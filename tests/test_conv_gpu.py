@@ -98,6 +98,45 @@ def test_tcgen05_matches_oracle(dtype, c_in, c_out):
     assert torch.equal(y, y2)
 
 
+def _oracle_rows(coords, xq, wq, rows):
+    """Reference output for a subset of output rows (pairs restricted to those rows)."""
+    found = km.kernel_map_found(coords, coords[rows], (1, 1, 1), (3, 3, 3))
+    out = torch.zeros(len(rows), wq.shape[2])
+    for k in range(27):
+        hit = np.nonzero(found[k] >= 0)[0]
+        if len(hit):
+            out[torch.from_numpy(hit)] += xq[torch.from_numpy(found[k][hit]).long()] @ wq[k]
+    return out.numpy()
+
+
+@pytest.mark.parametrize("c_in,c_out,n", [(32, 32, 200000), (64, 64, 200000), (96, 96, 160000), (128, 128, 120000),
+                                          (256, 256, 100000), (64, 128, 40000)])
+def test_tcgen05_large_problem(c_in, c_out, n):
+    """Sizes at which the kernel runs several 128-row sub-tiles per CTA pass and double-buffered
+    accumulators: tensor-core kernel == FP32-pipe kernel everywhere, == oracle on row samples,
+    with the fused epilogue on, and bit-reproducible."""
+    coords, x, w = _layer_case(n, c_in, c_out, 900 + c_in, "raster_crop")
+    order = np.argsort(km.morton_code(coords[:, 1:]), kind="stable")  # spatially coherent tiles
+    coords = np.ascontiguousarray(coords[order])
+    xq, wq = x.half(), w.half()
+    g = torch.Generator().manual_seed(3)
+    scale, shift = torch.rand(c_out, generator=g) + 0.5, torch.randn(c_out, generator=g) * 0.1
+    res = torch.randn(n, c_out, generator=g).half()
+    c = torch.from_numpy(coords).to(DEV)
+    kmap = generate_kernel_map(c, c, (1, 1, 1), (3, 3, 3))
+    ep = ConvEpilogue(scale=scale.to(DEV), shift=shift.to(DEV), residual=res.to(DEV), relu=True)
+    y = sparse_conv_fused(xq.to(DEV), wq.to(DEV), kmap, n, epilogue=ep, algo=CONV_TCGEN05)
+    check_device_status(DEV)
+    ys = sparse_conv_fused(xq.to(DEV), wq.to(DEV), kmap, n, epilogue=ep, algo=CONV_SIMT)
+    assert rel_l2(y.float().cpu().numpy(), ys.float().cpu().numpy()) < 2e-3  # both rounded to fp16
+    for rows in (np.arange(0, 1500), np.arange(n - 1500, n), np.arange(n // 2, n // 2 + 1500)):
+        conv = torch.from_numpy(_oracle_rows(coords, xq.float(), wq.float(), rows))
+        ref = torch.relu(conv * scale + shift + res[rows].float()).numpy()
+        assert rel_l2(y[rows].float().cpu().numpy(), ref) < 1e-2
+    y2 = sparse_conv_fused(xq.to(DEV), wq.to(DEV), kmap, n, epilogue=ep, algo=CONV_TCGEN05)
+    assert torch.equal(y, y2)
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
 def test_fused_epilogue_matches_unfused_chain(dtype):
     """conv -> BatchNorm1d(eval) -> + residual -> ReLU in one kernel vs the separate torch ops."""

@@ -10,7 +10,7 @@ int wcn_conv_simt_fwd(const void* feats, const void* weight, const int32_t* nbr,
 bool wcn_conv_tcgen05_supported(int K, int c_in, int c_out, int dtype, int out_dtype);
 int64_t wcn_conv_tcgen05_packed_bytes(int K, int c_in, int c_out);
 int wcn_conv_tcgen05_pack(const void* weight, int K, int c_in, int c_out, void* packed, cudaStream_t st);
-int wcn_conv_tcgen05_fwd(const void* feats, const void* packed, const int32_t* nbr, int64_t M, int K, int c_in,
+int wcn_conv_tcgen05_fwd(const void* feats, int64_t num_in, const void* packed, const int32_t* nbr, int64_t M, int K, int c_in,
                          int c_out, int dtype, const float* scale, const float* shift, const void* residual,
                          int relu, void* out, int out_dtype, int32_t* dev_status, cudaStream_t st);
 
@@ -62,9 +62,9 @@ extern "C" int wcn_conv_fwd(int algo, const void* feats, int64_t num_in, const v
   if (!nbr || !out || (num_in > 0 && !feats)) return WCN_ERR_INVALID_PARAMETERS;
   cudaStream_t st = wcn_stream(stream);
   const bool tc_ok = wcn_conv_tcgen05_supported(num_offsets, c_in, c_out, dtype, out_dtype);
-  if (algo == WCN_CONV_TCGEN05 || (algo == WCN_CONV_AUTO && tc_ok && packed_weight && dev_status)) {
+  if (algo == WCN_CONV_TCGEN05 || (algo == WCN_CONV_AUTO && tc_ok && packed_weight && dev_status && num_in > 0)) {
     if (!tc_ok) return WCN_ERR_UNSUPPORTED_CONFIG;
-    return wcn_conv_tcgen05_fwd(feats, packed_weight, nbr, num_out, num_offsets, c_in, c_out, dtype, scale, shift,
+    return wcn_conv_tcgen05_fwd(feats, num_in, packed_weight, nbr, num_out, num_offsets, c_in, c_out, dtype, scale, shift,
                                 residual, relu, out, out_dtype, dev_status, st);
   }
   if (algo != WCN_CONV_SIMT && algo != WCN_CONV_AUTO) return WCN_ERR_INVALID_PARAMETERS;

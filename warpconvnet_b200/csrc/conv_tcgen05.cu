@@ -1,37 +1,64 @@
 // Output-stationary sparse convolution on the 5th-generation tensor cores.
 //
-// One CTA owns 128 consecutive output rows (the 128 TMEM lanes of an M=128
-// tcgen05.mma) and all c_out columns.  It walks the kernel offsets that have at
-// least one neighbour among its rows; for each (offset, 64- or 32-channel slice)
-// the four producer warps gather the neighbour rows of the feature matrix into a
-// K-major, hardware-swizzled shared-memory tile with 16-byte cp.async copies
-// (absent neighbours are zero-filled) next to the matching slice of the
-// pre-tiled weights, and one thread of a fifth warp issues tcgen05.mma
-// instructions that accumulate in fp32 in tensor memory.  When every offset has
-// been consumed the producer warps turn into the epilogue: tcgen05.ld the
-// accumulator, apply scale/shift (folded BatchNorm or bias), residual add and
-// ReLU, convert and store each output row exactly once.  No atomics, no
-// split-K workspace, bit-reproducible.
+// A persistent CTA (one per SM) walks "supertiles" of G x 128 consecutive output
+// rows.  Each 128-row sub-tile owns one fp32 accumulator in tensor memory (the
+// 128 TMEM lanes of an M=128 tcgen05.mma); the accumulators are double-buffered
+// when they fit, so the epilogue of one supertile overlaps the main loop of the
+// next.  Five warp roles, connected by mbarrier rings:
+//  * index warps read the neighbour table of the NEXT supertile (which input row
+//    feeds each output row at each kernel offset), stage it in shared memory and
+//    derive, per sub-tile, the set of offsets that have any neighbour;
+//  * all roles then walk  offsets with a neighbour x channel slices x sub-tiles :
+//    one thread fetches the weight slice of (offset, channel slice) ONCE per
+//    supertile with a bulk copy (the packed weights hold the swizzled shared-memory
+//    image), and eight gather warps copy, for every sub-tile with a neighbour at
+//    that offset, the 128 neighbour rows of the feature matrix into a K-major
+//    swizzled tile (16-byte cp.async, whole row segments per request, absent rows
+//    zero-filled); the copies signal the ring's mbarrier themselves when they land;
+//  * one thread issues tcgen05.mma (weight slice shared by the G sub-tiles) and
+//    releases ring slots with tcgen05.commit;
+//  * epilogue warps read the accumulators with tcgen05.ld, apply scale/shift
+//    (folded BatchNorm or bias), residual add and ReLU, convert and store every
+//    output row exactly once.  No atomics, no split-K workspace, bit-reproducible.
 //
 // Every wait is bounded: a wait that runs out stores WCN_ERR_WAIT_EXPIRED in the
-// device status word, all other waits notice it and the CTA leaves through the
-// normal exit path (pending copies drained, tensor memory released).
+// device status word, the other waits notice it and the CTA leaves through the
+// normal exit path (tensor memory released).
 #include "wcn_common.cuh"
 
 namespace {
 
 constexpr int BLOCK_M = 128;
-constexpr int MAX_STAGES = 8;
-constexpr int PRODUCERS = 128;        // warps 0..3; also the epilogue warps
-constexpr int THREADS = PRODUCERS + 32;
+constexpr int MAX_G = 4;              // sub-tiles per supertile
+constexpr int MAX_RING = 12;          // slots per ring
 constexpr int MAX_OFFSETS = 27;
-constexpr long long kWaitCycles = 4000000000ll;  // about two seconds
+constexpr int EPI_THREADS = 128;      // warps 0..3: TMEM lane quarter = warp index
+constexpr int IDX_THREADS = 128;      // warps 4..7: neighbour-table staging
+constexpr int GATHER_WARP0 = 8;       // warps 8..15: row gathers
+constexpr int GATHER_THREADS = 256;
+constexpr int MMA_WARP = 16;          // MMA issuer, TMEM owner
+constexpr int WEIGHT_WARP = 17;       // weight bulk copies
+constexpr int THREADS = 576;
+constexpr long long kWaitCycles = 4000000000ll;        // about two seconds
+constexpr unsigned kSuspendNs = 20000;                  // per-attempt parking limit of a barrier wait
+constexpr long long kStatusPollCycles = 2000000ll;     // about a millisecond between looks at the status word
+
+#ifdef WCN_WAIT_STATS
+// Development aid (never compiled into the shipped library): cycles each role spends
+// waiting, summed over CTAs into a global array.
+__device__ long long g_wait_stats[16];
+#define WCN_T0(var) const long long var = clock64()
+#define WCN_ACC(slot, var, cond) do { if (cond) atomicAdd((unsigned long long*)&g_wait_stats[slot], (unsigned long long)(clock64() - var)); } while (0)
+#else
+#define WCN_T0(var)
+#define WCN_ACC(slot, var, cond)
+#endif
 
 struct ConvTcParams {
   const char* feats;
   const char* wpacked;
   const int32_t* nbr;
-  int64_t M;
+  int64_t M, num_in;
   int K, c_in, c_out;
   const float* scale;
   const float* shift;
@@ -39,9 +66,12 @@ struct ConvTcParams {
   int relu;
   void* out;
   int32_t* dev_status;
-  uint32_t tmem_cols;
-  int block_n;   // output columns per CTA (blockIdx.y selects the column block)
-  int stages;    // shared-memory pipeline depth, 2..MAX_STAGES
+  int block_n;      // output columns per CTA (blockIdx.y selects the column block)
+  int G;            // sub-tiles per supertile: 1, 2 or 4
+  int nbuf;         // accumulator sets in TMEM: 1 or 2
+  int cols;         // TMEM columns per accumulator (power of two >= block_n)
+  int sa, sb;       // ring depths
+  int64_t supertiles;
 };
 
 // ------------------------------------------------------------------ PTX wrappers
@@ -54,47 +84,63 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.shared::cta.b64 st, [%0];\n\t}" ::"r"(bar) : "memory");
 }
+// One wait attempt.  The hardware may park the thread until the phase completes or
+// `kSuspendNs` elapse, so a waiting warp does not compete for issue slots with the
+// warps that are doing work.
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t done;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(done)
-      : "r"(bar), "r"(parity)
+      : "r"(bar), "r"(parity), "r"(kSuspendNs)
       : "memory");
   return done != 0;
 }
-// Bounded wait.  Returns false when the deadline passed or another thread
-// already reported a failure.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int32_t* dev_status) {
+// Bounded wait.  Returns false when the deadline passed or another thread already
+// reported a failure.  The status word lives in global memory and is looked at about
+// once per millisecond of waiting.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int32_t* dev_status,
+                                          unsigned unused_backoff = 0) {
+  (void)unused_backoff;
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
+  long long next_check = t0 + kStatusPollCycles;
   for (;;) {
 #pragma unroll 1
-    for (int i = 0; i < 32; ++i)
+    for (int i = 0; i < 16; ++i)
       if (mbar_try_wait(bar, parity)) return true;
-    if (*(volatile int32_t*)dev_status != 0) return false;
-    if (clock64() - t0 > kWaitCycles) {
-      atomicMin(dev_status, (int)WCN_ERR_WAIT_EXPIRED);
-      return false;
+    const long long now = clock64();
+    if (now > next_check) {
+      if (*(volatile int32_t*)dev_status != 0) return false;
+      if (now - t0 > kWaitCycles) {
+        atomicMin(dev_status, (int)WCN_ERR_WAIT_EXPIRED);
+        return false;
+      }
+      next_check = now + kStatusPollCycles;
     }
   }
 }
 
+__device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.expect_tx.shared::cta.b64 st, [%0], %1;\n\t}" ::"r"(bar), "r"(bytes)
+               : "memory");
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+               "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32_t src_bytes) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+  // no "memory" clobber: the data is only observed after an mbarrier wait, which has one
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes));
 }
 // Arrive on `bar` once all cp.async copies issued so far by this thread have landed.
 __device__ __forceinline__ void cp_async_arrive(uint32_t bar) {
   asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
 }
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N> __device__ __forceinline__ void cp_async_wait() {
-  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+__device__ __forceinline__ void cp_async_drain() {
+  asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");
 }
-__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
@@ -182,10 +228,37 @@ template <typename T16> struct OutVec16 {
 template <> struct OutVec<__half> : OutVec16<__half> {};
 template <> struct OutVec<__nv_bfloat16> : OutVec16<__nv_bfloat16> {};
 
+// Sub-tiles (bit g) that have a neighbour at offset k, from the per-sub-tile offset masks.
+__device__ __forceinline__ uint32_t subtiles_at(uint32_t m0, uint32_t m1, uint32_t m2, uint32_t m3, int k) {
+  return ((m0 >> k) & 1u) | (((m1 >> k) & 1u) << 1) | (((m2 >> k) & 1u) << 2) | (((m3 >> k) & 1u) << 3);
+}
+
+// Ring cursor: slot index and the parity of the phase the slot is in.
+struct Ring {
+  int slot, phase, depth;
+  __device__ __forceinline__ void advance() {
+    if (++slot == depth) { slot = 0; phase ^= 1; }
+  }
+};
+
+// Control block in shared memory.
+struct Control {
+  uint64_t a_full[MAX_RING], a_empty[MAX_RING];
+  uint64_t b_full[MAX_RING], b_empty[MAX_RING];
+  uint64_t acc_full[2], acc_empty[2];
+  uint64_t info_full[2], info_empty[2];
+  uint64_t idx_sync;              // rendezvous of the index threads (bounded, unlike bar.sync)
+  uint32_t info_mask[2][MAX_G];   // per staged supertile: non-empty offsets of each sub-tile
+  uint32_t mask_acc[2][MAX_G];    // index warps' scratch while building the masks
+  uint32_t tmem_holder;
+  int skip;
+};
+
 // ------------------------------------------------------------------ kernel
 
 template <int BK, bool BF16, typename TO>
-__global__ void __launch_bounds__(THREADS, 1) conv_tcgen05_kernel(const ConvTcParams p) {
+__global__ void __launch_bounds__(THREADS, 1)
+conv_tcgen05_kernel(const ConvTcParams p) {
   constexpr int RB = BK * 2;         // bytes per tile row
   constexpr int CH = RB / 16;        // 16-byte chunks per tile row
   constexpr int RPI = 32 / CH;       // tile rows covered by one warp-wide copy instruction
@@ -193,239 +266,403 @@ __global__ void __launch_bounds__(THREADS, 1) conv_tcgen05_kernel(const ConvTcPa
   extern __shared__ uint8_t smem_raw[];
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int64_t m0 = (int64_t)blockIdx.x * BLOCK_M;
-  const int n0 = blockIdx.y * p.block_n;
-  const int BN = p.block_n;
-  const int S = p.stages;
+  const int G = p.G, BN = p.block_n, K = p.K, NBUF = p.nbuf;
+  const int n0 = blockIdx.y * BN;
   const int KB = p.c_in / BK;
   const int B_BYTES = BN * RB;
-
-  __shared__ int s_skip;  // block-uniform: an earlier launch on this status word failed
-  if (tid == 0) s_skip = *(volatile int32_t*)p.dev_status;
-  __syncthreads();
-  if (s_skip != 0) return;
+  const int IDX_INTS = G * K * BLOCK_M;  // one staged neighbour table
 
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* gen = smem_raw + (base - smem_u32(smem_raw));
   const uint32_t a_base = base;
-  const uint32_t b_base = a_base + S * A_BYTES;
-  const uint32_t misc = b_base + S * B_BYTES;
+  const uint32_t b_base = a_base + p.sa * A_BYTES;
+  const uint32_t misc = b_base + p.sb * B_BYTES;
   uint8_t* misc_gen = gen + (misc - base);
-  int32_t* rows_idx = reinterpret_cast<int32_t*>(misc_gen);                            // [K][128]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(misc_gen + MAX_OFFSETS * BLOCK_M * 4);  // full[S], empty[S], acc
-  uint32_t* holder = reinterpret_cast<uint32_t*>(bars + 2 * MAX_STAGES + 1);
-  uint32_t* act_mask = holder + 1;
-  const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8 * MAX_STAGES, acc_bar = full0 + 16 * MAX_STAGES;
+  Control* ctl = reinterpret_cast<Control*>(misc_gen);
+  int32_t* rows_idx = reinterpret_cast<int32_t*>(misc_gen + sizeof(Control));  // [2][G][K][128]
+  auto bar = [](uint64_t* b) { return smem_u32(b); };
+
+  if (tid == 0) ctl->skip = *(volatile int32_t*)p.dev_status;  // an earlier launch on this status word failed
+  __syncthreads();
+  if (ctl->skip != 0) return;
 
   if (tid == 0) {
-    for (int s = 0; s < S; ++s) {
-      mbar_init(full0 + 8 * s, PRODUCERS);
-      mbar_init(empty0 + 8 * s, 1);
+    for (int s = 0; s < p.sa; ++s) { mbar_init(bar(&ctl->a_full[s]), GATHER_THREADS); mbar_init(bar(&ctl->a_empty[s]), 1); }
+    for (int s = 0; s < p.sb; ++s) { mbar_init(bar(&ctl->b_full[s]), 1); mbar_init(bar(&ctl->b_empty[s]), 1); }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(bar(&ctl->acc_full[i]), 1);
+      mbar_init(bar(&ctl->acc_empty[i]), EPI_THREADS);
+      mbar_init(bar(&ctl->info_full[i]), 1);
+      mbar_init(bar(&ctl->info_empty[i]), EPI_THREADS + 2 + GATHER_THREADS / 32);  // epilogue threads, MMA thread, weight thread, gather warps
     }
-    mbar_init(acc_bar, 1);
-    *act_mask = 0;
+    mbar_init(bar(&ctl->idx_sync), IDX_THREADS);
+    for (int g = 0; g < MAX_G; ++g) ctl->mask_acc[0][g] = ctl->mask_acc[1][g] = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 4) tmem_alloc(smem_u32(holder), p.tmem_cols);
-  __syncthreads();
-
-  // neighbour rows of this tile for every offset, and the set of non-empty offsets
-  if (tid < PRODUCERS) {
-    const int64_t m = m0 + tid;
-    uint32_t mine = 0;
-    for (int k = 0; k < p.K; ++k) {
-      const int r = m < p.M ? __ldg(&p.nbr[(int64_t)k * p.M + m]) : -1;
-      rows_idx[k * BLOCK_M + tid] = r;
-      if (__any_sync(0xFFFFFFFFu, r >= 0)) mine |= 1u << k;
-    }
-    if (lane == 0 && mine) atomicOr(act_mask, mine);
-  }
+  const uint32_t tmem_total = (uint32_t)(NBUF * G * p.cols);
+  if (warp == MMA_WARP) tmem_alloc(smem_u32(&ctl->tmem_holder), tmem_total < 32 ? 32u : tmem_total);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const uint32_t mask = *act_mask;
-  const uint32_t tmem_base = *holder;
-  const int T = __popc(mask) * KB;  // pipeline iterations
+  const uint32_t tmem_base = ctl->tmem_holder;
 
   bool ok = true;
-  if (tid < PRODUCERS) {
-    // ---------------- producers: gather A rows + copy the weight slice.
-    // A: one warp instruction covers RPI rows x one full tile row each (CH lanes per row),
-    //    so every request is a whole RB-byte segment of a feature row.
+  if (warp >= 4 && warp < GATHER_WARP0) {
+    // ================================================================ index warps
+    // Stage the neighbour table of a supertile (one supertile ahead of the copies):
+    // rows_idx[ib][g][k][row] = input row, or -1 where there is no neighbour.
+    const int itid = tid - EPI_THREADS;
+    int ib = 0, iphase = 0, sphase = 0;
+    for (int64_t st = blockIdx.x; st < p.supertiles && ok; st += gridDim.x) {
+      const int64_t m0 = st * G * BLOCK_M;
+      if (!mbar_wait(bar(&ctl->info_empty[ib]), iphase ^ 1, p.dev_status, 64)) { ok = false; break; }
+      int32_t* dst = rows_idx + ib * IDX_INTS;
+      for (int g = 0; g < G; ++g) {
+        const int64_t m = m0 + (int64_t)g * BLOCK_M + itid;
+        uint32_t mine = 0;
+        int r[MAX_OFFSETS];  // all loads are issued before the first one is consumed
+#pragma unroll
+        for (int k = 0; k < MAX_OFFSETS; ++k)
+          r[k] = (k < K && m < p.M) ? __ldg(&p.nbr[(int64_t)k * p.M + m]) : -1;
+#pragma unroll
+        for (int k = 0; k < MAX_OFFSETS; ++k) {
+          if (k < K) {
+            dst[(g * K + k) * BLOCK_M + itid] = r[k];
+            if (__any_sync(0xFFFFFFFFu, r[k] >= 0)) mine |= 1u << k;
+          }
+        }
+        if (lane == 0 && mine) atomicOr(&ctl->mask_acc[ib][g], mine);
+      }
+      // all index threads meet (bounded: a thread that gave up does not arrive, the others time out)
+      mbar_arrive(bar(&ctl->idx_sync));
+      if (!mbar_wait(bar(&ctl->idx_sync), sphase, p.dev_status)) { ok = false; break; }
+      sphase ^= 1;
+      if (itid == 0) {
+        for (int g = 0; g < MAX_G; ++g) {
+          ctl->info_mask[ib][g] = g < G ? ctl->mask_acc[ib][g] : 0u;
+          ctl->mask_acc[ib][g] = 0;  // next use of this entry is two supertiles away, behind info_empty
+        }
+        mbar_arrive(bar(&ctl->info_full[ib]));  // publishes the table and the masks
+      }
+      if (++ib == 2) { ib = 0; iphase ^= 1; }
+    }
+  } else if (warp == WEIGHT_WARP) {
+    // ================================================================ weight loader
+    if (lane == 0) {
+      Ring rb{0, 0, p.sb};
+      int ib = 0, iphase = 0;
+      for (int64_t st = blockIdx.x; st < p.supertiles && ok; st += gridDim.x) {
+        if (!mbar_wait(bar(&ctl->info_full[ib]), iphase, p.dev_status)) { ok = false; break; }
+        uint32_t rest = ctl->info_mask[ib][0] | ctl->info_mask[ib][1] | ctl->info_mask[ib][2] | ctl->info_mask[ib][3];
+        mbar_arrive(bar(&ctl->info_empty[ib]));  // only the masks were needed
+        if (++ib == 2) { ib = 0; iphase ^= 1; }
+        while (rest && ok) {
+          const int k = __ffs(rest) - 1;
+          rest &= rest - 1;
+          const char* bsrc_k = p.wpacked + ((int64_t)k * KB * p.c_out + n0) * RB;
+          for (int kb = 0; kb < KB; ++kb) {
+            // weight slice (offset k, channel slice kb): one bulk copy, shared by all sub-tiles
+            WCN_T0(t_be);
+            if (!mbar_wait(bar(&ctl->b_empty[rb.slot]), rb.phase ^ 1, p.dev_status)) { ok = false; break; }
+            WCN_ACC(1, t_be, true);
+            bulk_copy_g2s(b_base + rb.slot * B_BYTES, bsrc_k + (int64_t)kb * p.c_out * RB, (uint32_t)B_BYTES,
+                          bar(&ctl->b_full[rb.slot]));
+            rb.advance();
+          }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp >= GATHER_WARP0 && warp < MMA_WARP) {
+    // ================================================================ gather warps
+    const int gwarp = warp - GATHER_WARP0;
+    constexpr int ROWS_PER_WARP = BLOCK_M / (GATHER_THREADS / 32);  // 16
+    constexpr int NJ = ROWS_PER_WARP / RPI;                          // copy instructions per warp per A slot
     const int sub_row = lane / CH, chunk = lane % CH;
-    int it = 0;
-    uint32_t rest = mask;
-    while (rest && ok) {
-      const int k = __ffs(rest) - 1;
-      rest &= rest - 1;
-      const char* asrc[CH];
-      uint32_t aoff[CH];
+    uint32_t aoff[NJ];  // this thread's fixed (row, chunk) positions inside an A tile
 #pragma unroll
-      for (int j = 0; j < CH; ++j) {
-        const int row = warp * 32 + j * RPI + sub_row;
-        const int src = rows_idx[k * BLOCK_M + row];
-        asrc[j] = src >= 0 ? p.feats + (int64_t)src * p.c_in * 2 + chunk * 16 : nullptr;
-        aoff[j] = tile_offset<RB>(row, chunk);
-      }
-      const char* bsrc_k = p.wpacked + ((int64_t)k * KB * p.c_out + n0) * RB;
-      for (int kb = 0; kb < KB; ++kb, ++it) {
-        const int s = it % S;
-        if (!mbar_wait(empty0 + 8 * s, ((it / S) & 1) ^ 1, p.dev_status)) { ok = false; break; }
-        const uint32_t a_dst = a_base + s * A_BYTES;
+    for (int j = 0; j < NJ; ++j) aoff[j] = tile_offset<RB>(gwarp * ROWS_PER_WARP + j * RPI + sub_row, chunk);
+    Ring ra{0, 0, p.sa};
+    int ib = 0, iphase = 0;
+    WCN_T0(t_prod);
+    for (int64_t st = blockIdx.x; st < p.supertiles && ok; st += gridDim.x) {
+      WCN_T0(t_idx);
+      if (!mbar_wait(bar(&ctl->info_full[ib]), iphase, p.dev_status)) { ok = false; break; }
+      WCN_ACC(2, t_idx, tid == GATHER_WARP0 * 32);
+      const uint32_t mk0 = ctl->info_mask[ib][0], mk1 = ctl->info_mask[ib][1];
+      const uint32_t mk2 = ctl->info_mask[ib][2], mk3 = ctl->info_mask[ib][3];
+      const int32_t* tab = rows_idx + ib * IDX_INTS + gwarp * ROWS_PER_WARP + sub_row;
+      uint32_t rest = mk0 | mk1 | mk2 | mk3;
+      while (rest && ok) {
+        const int k = __ffs(rest) - 1;
+        rest &= rest - 1;
+        const uint32_t gbits = subtiles_at(mk0, mk1, mk2, mk3, k);
+        for (int kb = 0; kb < KB && ok; ++kb) {
+          for (uint32_t gb = gbits; gb; gb &= gb - 1) {
+            const int g = __ffs(gb) - 1;
+            WCN_T0(t_ae);
+            if (!mbar_wait(bar(&ctl->a_empty[ra.slot]), ra.phase ^ 1, p.dev_status)) { ok = false; break; }
+            WCN_ACC(0, t_ae, tid == GATHER_WARP0 * 32);
+            const uint32_t a_dst = a_base + ra.slot * A_BYTES;
+            const int32_t* rk = tab + (g * K + k) * BLOCK_M;
+            int src[NJ];  // all index reads first, so the copies below issue back to back
 #pragma unroll
-        for (int j = 0; j < CH; ++j)
-          cp_async16(a_dst + aoff[j], asrc[j] ? asrc[j] + kb * RB : p.feats, asrc[j] ? 16u : 0u);
-        const uint32_t b_dst = b_base + s * B_BYTES;
-        const char* bsrc = bsrc_k + (int64_t)kb * p.c_out * RB;
-        for (int j = tid; j < BN * CH; j += PRODUCERS)
-          cp_async16(b_dst + tile_offset<RB>(j / CH, j % CH), bsrc + (int64_t)j * 16, 16u);
-        cp_async_arrive(full0 + 8 * s);  // hardware arrives when this thread's copies have landed
+            for (int j = 0; j < NJ; ++j) src[j] = rk[j * RPI];
+            const char* fbase = p.feats + (int64_t)kb * RB + chunk * 16;
+#pragma unroll
+            for (int j = 0; j < NJ; ++j) {
+              const char* sp = src[j] >= 0 ? fbase + (int64_t)src[j] * p.c_in * 2 : p.feats;
+              cp_async16(a_dst + aoff[j], sp, src[j] >= 0 ? 16u : 0u);
+            }
+            cp_async_arrive(bar(&ctl->a_full[ra.slot]));  // hardware arrives when this thread's copies land
+            ra.advance();
+          }
+        }
       }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(&ctl->info_empty[ib]));  // this warp is done with the staged table
+      if (++ib == 2) { ib = 0; iphase ^= 1; }
     }
-    cp_async_commit();
-    cp_async_wait<0>();
-  } else if (lane == 0) {
-    // ---------------- MMA issuer
-    const uint32_t idesc = (1u << 4) | ((BF16 ? 1u : 0u) << 7) | ((BF16 ? 1u : 0u) << 10) |
-                           ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BLOCK_M >> 4) << 24);
-    for (int it = 0; it < T; ++it) {
-      const int s = it % S;
-      if (!mbar_wait(full0 + 8 * s, (it / S) & 1, p.dev_status)) { ok = false; break; }
-      fence_proxy_async();  // copies were written through the generic proxy, the MMA reads through the async one
+    WCN_ACC(3, t_prod, tid == GATHER_WARP0 * 32);
+    cp_async_drain();
+  } else if (warp == MMA_WARP) {
+    // ================================================================ MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = (1u << 4) | ((BF16 ? 1u : 0u) << 7) | ((BF16 ? 1u : 0u) << 10) |
+                             ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BLOCK_M >> 4) << 24);
+      Ring ra{0, 0, p.sa}, rb{0, 0, p.sb};
+      int ib = 0, iphase = 0, ab = 0, aphase = 0;
+      WCN_T0(t_mma);
+      for (int64_t st = blockIdx.x; st < p.supertiles && ok; st += gridDim.x) {
+        WCN_T0(t_info);
+        if (!mbar_wait(bar(&ctl->info_full[ib]), iphase, p.dev_status)) { ok = false; break; }
+        WCN_ACC(6, t_info, true);
+        const uint32_t mk0 = ctl->info_mask[ib][0], mk1 = ctl->info_mask[ib][1];
+        const uint32_t mk2 = ctl->info_mask[ib][2], mk3 = ctl->info_mask[ib][3];
+        const uint32_t uni = mk0 | mk1 | mk2 | mk3;
+        // the accumulator set must have been read out by the epilogue of its previous use
+        WCN_T0(t_acce);
+        if (!mbar_wait(bar(&ctl->acc_empty[ab]), aphase ^ 1, p.dev_status)) { ok = false; break; }
+        WCN_ACC(8, t_acce, true);
+        tc_fence_after();
+        uint32_t started = 0;
+        uint32_t rest = uni;
+        while (rest && ok) {
+          const int k = __ffs(rest) - 1;
+          rest &= rest - 1;
+          const uint32_t gbits = subtiles_at(mk0, mk1, mk2, mk3, k);
+          for (int kb = 0; kb < KB && ok; ++kb) {
+            WCN_T0(t_bf);
+            if (!mbar_wait(bar(&ctl->b_full[rb.slot]), rb.phase, p.dev_status)) { ok = false; break; }
+            WCN_ACC(4, t_bf, true);
+            const uint64_t bdesc = smem_desc<RB>(b_base + rb.slot * B_BYTES);
+            for (uint32_t gb = gbits; gb; gb &= gb - 1) {
+              const int g = __ffs(gb) - 1;
+              WCN_T0(t_af);
+              if (!mbar_wait(bar(&ctl->a_full[ra.slot]), ra.phase, p.dev_status)) { ok = false; break; }
+              WCN_ACC(5, t_af, true);
+              tc_fence_after();
+              const uint64_t adesc = smem_desc<RB>(a_base + ra.slot * A_BYTES);
+              const uint32_t d = tmem_base + (uint32_t)((ab * G + g) * p.cols);
+#pragma unroll
+              for (int kk = 0; kk < BK / 16; ++kk)
+                umma_f16(d, adesc + (uint64_t)(kk * 2), bdesc + (uint64_t)(kk * 2), idesc,
+                         (((started >> g) & 1u) | (uint32_t)kk) ? 1u : 0u);
+              started |= 1u << g;
+              umma_commit(bar(&ctl->a_empty[ra.slot]));  // slot is free once these MMAs have read it
+              ra.advance();
+            }
+            umma_commit(bar(&ctl->b_empty[rb.slot]));
+            rb.advance();
+          }
+        }
+        if (started && ok) umma_commit(bar(&ctl->acc_full[ab]));  // accumulators of this supertile complete
+        else mbar_arrive(bar(&ctl->acc_full[ab]));
+        mbar_arrive(bar(&ctl->info_empty[ib]));
+        if (++ib == 2) { ib = 0; iphase ^= 1; }
+        if (++ab == NBUF) { ab = 0; aphase ^= 1; }
+      }
+      WCN_ACC(7, t_mma, true);
+    }
+    __syncwarp();
+  } else {
+    // ================================================================ epilogue (warps 0..3)
+    int ib = 0, iphase = 0, ab = 0, aphase = 0;
+    WCN_T0(t_epi);
+    for (int64_t st = blockIdx.x; st < p.supertiles; st += gridDim.x) {
+      WCN_T0(t_accf);
+      if (ok) ok = mbar_wait(bar(&ctl->info_full[ib]), iphase, p.dev_status, 256);
+      if (ok) ok = mbar_wait(bar(&ctl->acc_full[ab]), aphase, p.dev_status, 256);
+      WCN_ACC(9, t_accf, tid == 0);
+      // tcgen05.ld is warp-collective, so the decision to read must be warp-uniform
+      if (!__all_sync(0xFFFFFFFFu, ok)) { ok = false; break; }
       tc_fence_after();
-      const uint64_t adesc = smem_desc<RB>(a_base + s * A_BYTES);
-      const uint64_t bdesc = smem_desc<RB>(b_base + s * B_BYTES);
+      const int64_t m0 = st * G * BLOCK_M;
+      for (int g = 0; g < G; ++g) {
+        const uint32_t gmask = ctl->info_mask[ib][g];
+        const int64_t m = m0 + (int64_t)g * BLOCK_M + tid;
+        if (m0 + (int64_t)g * BLOCK_M >= p.M) break;
+        const uint32_t trow = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)((ab * G + g) * p.cols);
+        TO* orow = reinterpret_cast<TO*>(p.out) + m * p.c_out + n0;
+        const TO* rrow = p.residual ? reinterpret_cast<const TO*>(p.residual) + m * p.c_out + n0 : nullptr;
+        for (int c0 = 0; c0 < BN; c0 += 16) {
+          float y[16];
+          if (gmask) {
+            uint32_t r[16];
+            tmem_ld16(trow + (uint32_t)c0, r);  // executed by all lanes of the warp
+            tmem_ld_wait();
 #pragma unroll
-      for (int kk = 0; kk < BK / 16; ++kk)
-        umma_f16(tmem_base, adesc + (uint64_t)(kk * 2), bdesc + (uint64_t)(kk * 2), idesc, (it | kk) ? 1u : 0u);
-      umma_commit(empty0 + 8 * s);  // frees the stage once these MMAs have read it
-    }
-    if (T > 0 && ok) umma_commit(acc_bar);  // accumulator complete
-    else mbar_arrive(acc_bar);
-  }
-
-  if (tid < PRODUCERS) {
-    // ---------------- epilogue: TMEM -> registers -> global
-    if (ok) ok = mbar_wait(acc_bar, 0, p.dev_status);
-    tc_fence_after();
-    const int64_t m = m0 + tid;
-    // tcgen05.ld is warp-collective, so the decision to read must be warp-uniform
-    if (__all_sync(0xFFFFFFFFu, ok && *(volatile int32_t*)p.dev_status == 0)) {
-      const uint32_t trow = tmem_base + ((uint32_t)(warp * 32) << 16);
-      TO* orow = reinterpret_cast<TO*>(p.out) + m * p.c_out + n0;
-      const TO* rrow = p.residual ? reinterpret_cast<const TO*>(p.residual) + m * p.c_out + n0 : nullptr;
-      for (int c0 = 0; c0 < BN; c0 += 16) {
-        float y[16];
-        if (T > 0) {
-          uint32_t r[16];
-          tmem_ld16(trow + (uint32_t)c0, r);  // executed by all lanes of the warp
-          tmem_ld_wait();
+            for (int i = 0; i < 16; ++i) y[i] = __uint_as_float(r[i]);
+          } else {
 #pragma unroll
-          for (int i = 0; i < 16; ++i) y[i] = __uint_as_float(r[i]);
-        } else {
-#pragma unroll
-          for (int i = 0; i < 16; ++i) y[i] = 0.f;
-        }
-        if (m < p.M) {
-          if (p.scale) {
-#pragma unroll
-            for (int i = 0; i < 16; ++i) y[i] *= __ldg(&p.scale[n0 + c0 + i]);
+            for (int i = 0; i < 16; ++i) y[i] = 0.f;
           }
-          if (p.shift) {
+          if (m < p.M) {
+            if (p.scale) {
 #pragma unroll
-            for (int i = 0; i < 16; ++i) y[i] += __ldg(&p.shift[n0 + c0 + i]);
-          }
-          if (rrow) {
-            float res[16];
-            OutVec<TO>::load(rrow + c0, res);
+              for (int i = 0; i < 16; ++i) y[i] *= __ldg(&p.scale[n0 + c0 + i]);
+            }
+            if (p.shift) {
 #pragma unroll
-            for (int i = 0; i < 16; ++i) y[i] += res[i];
-          }
-          if (p.relu) {
+              for (int i = 0; i < 16; ++i) y[i] += __ldg(&p.shift[n0 + c0 + i]);
+            }
+            if (rrow) {
+              float res[16];
+              OutVec<TO>::load(rrow + c0, res);
 #pragma unroll
-            for (int i = 0; i < 16; ++i) y[i] = fmaxf(y[i], 0.f);
+              for (int i = 0; i < 16; ++i) y[i] += res[i];
+            }
+            if (p.relu) {
+#pragma unroll
+              for (int i = 0; i < 16; ++i) y[i] = fmaxf(y[i], 0.f);
+            }
+            OutVec<TO>::store(orow + c0, y);
           }
-          OutVec<TO>::store(orow + c0, y);
         }
       }
+      tc_fence_before();
+      mbar_arrive(bar(&ctl->acc_empty[ab]));   // accumulator set may be overwritten
+      mbar_arrive(bar(&ctl->info_empty[ib]));
+      if (++ib == 2) { ib = 0; iphase ^= 1; }
+      if (++ab == NBUF) { ab = 0; aphase ^= 1; }
     }
+    WCN_ACC(10, t_epi, tid == 0);
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 4) tmem_dealloc(tmem_base, p.tmem_cols);
+  if (warp == MMA_WARP) tmem_dealloc(tmem_base, tmem_total < 32 ? 32u : tmem_total);
 }
 
-// weight[K, c_in, c_out] -> packed[K][c_in/BK][c_out][BK]: every (offset, channel
-// slice) becomes one contiguous K-major tile.
+// weight[K, c_in, c_out] -> packed[K][c_in/BK] tiles of [c_out][BK]: every (offset, channel
+// slice) becomes one contiguous K-major tile stored as its swizzled shared-memory image
+// (the layout of tile_offset above), so the kernel moves it with a single bulk copy.
 template <typename T>
 __global__ void pack_weight_kernel(const T* __restrict__ w, T* __restrict__ packed, int K, int c_in, int c_out,
                                    int bk) {
   const int64_t total = (int64_t)K * c_in * c_out;
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= total) return;
-  const int c = (int)(i % bk);
-  int64_t r = i / bk;
-  const int n = (int)(r % c_out);
-  r /= c_out;
-  const int kb = (int)(r % (c_in / bk));
-  const int k = (int)(r / (c_in / bk));
-  packed[i] = w[((int64_t)k * c_in + kb * bk + c) * c_out + n];
+  const int n = (int)(i % c_out);
+  int64_t r = i / c_out;
+  const int cin = (int)(r % c_in);
+  const int k = (int)(r / c_in);
+  const int kb = cin / bk, c = cin % bk;
+  const int rb = bk * 2, chunk = c >> 3, within = c & 7, r8 = n & 7;
+  const int x = rb == 128 ? r8 : (r8 >> 1);
+  const int64_t tile = ((int64_t)k * (c_in / bk) + kb) * c_out * bk;  // elements
+  const int64_t off_bytes = (int64_t)(n >> 3) * (8 * rb) + r8 * rb + ((chunk ^ x) << 4);
+  packed[tile + off_bytes / 2 + within] = w[i];
 }
 
 inline int pick_bk(int c_in) { return c_in % 64 == 0 ? 64 : 32; }
 
-inline size_t smem_bytes(int bk, int block_n, int stages) {
-  return 1024 + (size_t)stages * (BLOCK_M + block_n) * bk * 2 + MAX_OFFSETS * BLOCK_M * 4 +
-         (2 * MAX_STAGES + 1) * 8 + 64;
-}
-
-// Column split: small problems do not have enough 128-row tiles to occupy 148 SMs, so the
-// output columns are divided among CTAs (each re-gathers the rows, which stay in L2).
-inline int pick_block_n(int64_t tiles, int c_out) {
-  int best = c_out;
-  for (int split = 1; split <= 8; split *= 2) {
-    if (c_out % (16 * split) != 0 || c_out / split < 32) break;
-    best = c_out / split;
-    if (tiles * split >= 256) break;
+int num_sms() {
+  static int cached[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (!cached[dev]) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cached[dev] = n;
   }
-  return best;
+  return cached[dev];
 }
 
-// Pipeline depth: as deep as fits, leaving room for a second CTA per SM when stages are small.
-inline int pick_stages(int bk, int block_n) {
-  const size_t stage = (size_t)(BLOCK_M + block_n) * bk * 2;
-  const size_t budget = stage <= 24 * 1024 ? 96 * 1024 : 204 * 1024;  // <= 96 KiB: two CTAs share an SM
-  int s = (int)(budget / stage);
-  return s < 2 ? 2 : (s > MAX_STAGES ? MAX_STAGES : s);
+// Launch geometry.  Small problems do not have enough 128-row tiles to occupy
+// every SM, so their output columns are divided among CTAs (each re-gathers the
+// rows, which stay in L2) and they use fewer sub-tiles per supertile.
+bool plan_launch(ConvTcParams& p, int bk, size_t* smem, dim3* grid) {
+  const int sms = num_sms();
+  const int64_t tiles = (p.M + BLOCK_M - 1) / BLOCK_M;
+  int split = 1;
+  while (tiles * split < sms && p.c_out % (16 * split * 2) == 0 && p.c_out / (split * 2) >= 32 && split < 8) split *= 2;
+  p.block_n = p.c_out / split;
+  int cols = 32;
+  while (cols < p.block_n) cols <<= 1;
+  p.cols = cols;
+  int g = cols >= 128 ? 2 : 4;
+  while (g > 1 && ((tiles + g - 1) / g) * split < 2 * (int64_t)sms) g /= 2;
+  const size_t a_stage = (size_t)BLOCK_M * bk * 2, b_stage = (size_t)p.block_n * bk * 2;
+  const size_t limit = 224 * 1024;
+  size_t fixed = 0;
+  for (;; g /= 2) {  // two staged neighbour tables + at least 4 A slots and 2 B slots must fit
+    fixed = 1024 + sizeof(Control) + 2 * (size_t)g * p.K * BLOCK_M * 4 + 128;
+    if (fixed + 4 * a_stage + 2 * b_stage <= limit) break;
+    if (g == 1) return false;
+  }
+  p.G = g;
+  p.nbuf = (g * cols * 2 <= 512) ? 2 : 1;
+  p.supertiles = (tiles + g - 1) / g;
+  const size_t budget = limit - fixed;
+  int sb = 3;
+  while (sb > 2 && sb * b_stage > budget / 2) --sb;
+  int sa = (int)((budget - sb * b_stage) / a_stage);
+  if (sa > MAX_RING) sa = MAX_RING;
+  if (sa < 2) return false;
+  // leftover room goes to the weight ring
+  while (sb < 6 && fixed + sa * a_stage + (sb + 1) * b_stage <= limit) ++sb;
+  p.sa = sa;
+  p.sb = sb;
+  *smem = fixed + sa * a_stage + sb * b_stage;
+  int64_t gx = p.supertiles;
+  const int64_t cap = sms / split > 0 ? sms / split : 1;
+  if (gx > cap) gx = cap;
+  *grid = dim3((unsigned)gx, (unsigned)split);
+  return true;
 }
 
 template <int BK, bool BF16, typename TO>
 int launch_tc(ConvTcParams& p, cudaStream_t st) {
-  const int64_t tiles = (p.M + BLOCK_M - 1) / BLOCK_M;
-  p.block_n = pick_block_n(tiles, p.c_out);
-  p.stages = pick_stages(BK, p.block_n);
-  uint32_t cols = 32;
-  while ((int)cols < p.block_n) cols <<= 1;
-  p.tmem_cols = cols;
-  const size_t smem = smem_bytes(BK, p.block_n, p.stages);
+  size_t smem = 0;
+  dim3 grid;
+  if (!plan_launch(p, BK, &smem, &grid)) return WCN_ERR_UNSUPPORTED_CONFIG;
   auto kern = conv_tcgen05_kernel<BK, BF16, TO>;
   static bool configured[64] = {};  // per template instance and device: opt in to large shared memory once
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return WCN_ERR_INITIALIZATION;
   if (!configured[dev]) {
-    // the kernel also has a few bytes of static shared memory, which count against the 227 KiB limit
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 225 * 1024) != cudaSuccess) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024) != cudaSuccess) {
       (void)cudaGetLastError();  // do not leave a sticky error for the caller's next CUDA call
       return WCN_ERR_INITIALIZATION;
     }
     configured[dev] = true;
   }
-  dim3 grid((unsigned)tiles, (unsigned)(p.c_out / p.block_n));
   kern<<<grid, THREADS, smem, st>>>(p);
   return cudaGetLastError() == cudaSuccess ? WCN_OK : WCN_ERR_EXECUTION;
 }
 
 }  // namespace
+
+#ifdef WCN_WAIT_STATS
+extern "C" int wcn_debug_wait_stats(long long* host16, int reset) {
+  if (host16 && cudaMemcpyFromSymbol(host16, g_wait_stats, sizeof(long long) * 16) != cudaSuccess) return -3;
+  if (reset) {
+    long long z[16] = {};
+    if (cudaMemcpyToSymbol(g_wait_stats, z, sizeof(z)) != cudaSuccess) return -3;
+  }
+  return 0;
+}
+#endif
 
 bool wcn_conv_tcgen05_supported(int K, int c_in, int c_out, int dtype, int out_dtype) {
   return (dtype == WCN_F16 || dtype == WCN_BF16) && (out_dtype == dtype || out_dtype == WCN_F32) && K >= 1 &&
@@ -442,17 +679,17 @@ int wcn_conv_tcgen05_pack(const void* weight, int K, int c_in, int c_out, void* 
   return cudaGetLastError() == cudaSuccess ? WCN_OK : WCN_ERR_EXECUTION;
 }
 
-int wcn_conv_tcgen05_fwd(const void* feats, const void* packed, const int32_t* nbr, int64_t M, int K, int c_in,
+int wcn_conv_tcgen05_fwd(const void* feats, int64_t num_in, const void* packed, const int32_t* nbr, int64_t M, int K, int c_in,
                          int c_out, int dtype, const float* scale, const float* shift, const void* residual,
                          int relu, void* out, int out_dtype, int32_t* dev_status, cudaStream_t st) {
   if (!wcn_conv_tcgen05_supported(K, c_in, c_out, dtype, out_dtype)) return WCN_ERR_UNSUPPORTED_CONFIG;
-  if (!dev_status || !packed) return WCN_ERR_INVALID_PARAMETERS;
+  if (!dev_status || !packed || num_in <= 0 || num_in >= 0x7FFFFFFFll) return WCN_ERR_INVALID_PARAMETERS;
   if ((reinterpret_cast<uintptr_t>(feats) & 15) || (reinterpret_cast<uintptr_t>(packed) & 15) ||
       (reinterpret_cast<uintptr_t>(out) & 15) || (reinterpret_cast<uintptr_t>(residual) & 15))
     return WCN_ERR_INVALID_PARAMETERS;
   ConvTcParams p;
   p.feats = (const char*)feats; p.wpacked = (const char*)packed; p.nbr = nbr;
-  p.M = M; p.K = K; p.c_in = c_in; p.c_out = c_out;
+  p.M = M; p.num_in = num_in; p.K = K; p.c_in = c_in; p.c_out = c_out;
   p.scale = scale; p.shift = shift; p.residual = residual; p.relu = relu; p.out = out;
   p.dev_status = dev_status;
   const int bk = pick_bk(c_in);
