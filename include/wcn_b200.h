@@ -42,7 +42,8 @@ enum wcn_status {
   WCN_ERR_INVALID_PARAMETERS = -5,
   WCN_ERR_HASH_OVERFLOW = -6,
   WCN_ERR_WAIT_EXPIRED = -7,
-  WCN_ERR_BOUNDS = -8
+  WCN_ERR_BOUNDS = -8,
+  WCN_ERR_SCRATCH_TOO_SMALL = -9
 };
 
 /* Element types of feature / weight tensors. */
@@ -127,6 +128,29 @@ int wcn_kmap_search(const void* table, int64_t capacity, int hash_method, const 
  * (warpconvnet/geometry/coords/search/torch_discrete.py:103-119). */
 int wcn_kmap_scan(void* workspace, int64_t num_queries, int32_t num_offsets, int32_t* offsets,
                   void* stream);
+
+/* wcn_kmap_search followed by wcn_kmap_scan, for callers that must not allocate device
+ * memory.  Some hosts of this library cannot call cudaMalloc around it: plugins that are
+ * handed a fixed arena by their framework and own no allocator, serving loops whose latency
+ * budget forbids allocator calls (cudaMalloc synchronises the device), processes whose
+ * memory pool is already exhausted or too fragmented for one more block.  For them the
+ * per-block hit counts live in a fixed 4 MiB array inside the library image instead of a
+ * caller-supplied workspace; the caller passes only inputs (table, queries) and outputs
+ * (nbr[num_offsets * num_queries], offsets[num_offsets + 1], both device memory).
+ * Limit: num_offsets * ceil(num_queries / 256) + num_offsets + 16 <= 1048576 (about 9.9 M
+ * queries for a 3x3x3 window); larger problems return WCN_ERR_SCRATCH_TOO_SMALL and launch
+ * nothing.  The entry point calls no allocator of any kind.  The first call on a device
+ * looks up the array's device address (cudaGetSymbolAddress); make that call before any
+ * stream capture begins.  All calls on a device share the one array and it keeps the last
+ * call's contents (nothing in it needs clearing between calls), so two calls whose kernels
+ * overlap on the GPU — different streams, no ordering between them — race; serialise them.
+ * Every GPU that loads the library holds the array until the process exits.
+ * No counterpart in the reference (its kernel-map path allocates through CuPy / torch on
+ * every call, warpconvnet/geometry/coords/search/torch_discrete.py:312-315, 103-124). */
+int wcn_kmap_search_static(const void* table, int64_t capacity, int hash_method,
+                           const int32_t* queries, int64_t num_queries, const int32_t* stride,
+                           const int32_t* kernel_size, int32_t num_offsets, int32_t* nbr,
+                           int32_t* offsets, void* stream);
 
 /* Compact nbr into in_maps / out_maps (length offsets[num_offsets]); within one offset the
  * pairs are in ascending output row.

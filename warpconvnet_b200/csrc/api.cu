@@ -27,6 +27,7 @@ extern "C" const char* wcn_status_string(int status) {
     case WCN_ERR_HASH_OVERFLOW: return "hash table overflow";
     case WCN_ERR_WAIT_EXPIRED: return "a bounded device-side wait expired";
     case WCN_ERR_BOUNDS: return "index out of bounds";
+    case WCN_ERR_SCRATCH_TOO_SMALL: return "problem larger than the library's built-in scratch array";
     default: return "unknown status";
   }
 }

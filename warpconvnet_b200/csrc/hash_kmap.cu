@@ -446,6 +446,49 @@ extern "C" int wcn_kmap_search(const void* table, int64_t capacity, int hash_met
   return WCN_OK;
 }
 
+// ------------------------------------------------------------------ allocation-free variant
+//
+// Scratch for wcn_kmap_search_static: per-block hit counts [num_offsets][blocks] followed by
+// the per-offset totals, the same layout wcn_kmap_search / wcn_kmap_scan keep in the
+// caller's workspace.  It lives in the library image, so every GPU that loads the library
+// holds these 4 MiB until the process exits.
+constexpr int64_t kStaticScratchInts = 1 << 20;
+static __device__ __align__(256) int g_kmap_static_scratch[kStaticScratchInts];
+
+// In host code the array's name is only a handle; the device address has to be asked for,
+// once per device, with that device current.
+static int* kmap_static_scratch_ptr() {
+  static int* cached[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  if (!cached[dev]) {
+    void* ptr = nullptr;
+    if (cudaGetSymbolAddress(&ptr, g_kmap_static_scratch) != cudaSuccess || !ptr) {
+      (void)cudaGetLastError();
+      return nullptr;
+    }
+    cached[dev] = static_cast<int*>(ptr);
+  }
+  return cached[dev];
+}
+
+extern "C" int wcn_kmap_search_static(const void* table, int64_t capacity, int hash_method,
+                                      const int32_t* queries, int64_t num_queries, const int32_t* stride,
+                                      const int32_t* kernel_size, int32_t num_offsets, int32_t* nbr,
+                                      int32_t* offsets, void* stream) {
+  if (num_queries < 0 || num_offsets <= 0 || !offsets) return WCN_ERR_INVALID_PARAMETERS;
+  const int64_t nblk = (num_queries + kThreads - 1) / kThreads;
+  if ((int64_t)num_offsets * nblk + num_offsets + 16 > kStaticScratchInts) return WCN_ERR_SCRATCH_TOO_SMALL;
+  int* scratch = kmap_static_scratch_ptr();  // first call on a device resolves the address
+  if (!scratch) return WCN_ERR_INITIALIZATION;
+  // Nothing in the scratch has to start at zero: the search writes every count it later
+  // reads, the scan writes every total.
+  const int rc = wcn_kmap_search(table, capacity, hash_method, queries, num_queries, stride, kernel_size,
+                                 num_offsets, nbr, scratch, stream);
+  if (rc != WCN_OK) return rc;
+  return wcn_kmap_scan(scratch, num_queries, num_offsets, offsets, stream);
+}
+
 extern "C" int wcn_kmap_scan(void* workspace, int64_t num_queries, int32_t num_offsets, int32_t* offsets,
                              void* stream) {
   if (!workspace || !offsets || num_queries < 0 || num_offsets <= 0) return WCN_ERR_INVALID_PARAMETERS;
