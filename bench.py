@@ -90,7 +90,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", "50"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
         except OSError:
@@ -100,7 +100,11 @@ class ClockSampler:
         for line in self.proc.stdout:
             self.lines.append(line.strip())
 
-    def stop(self):
+    def mark(self):
+        """Index of the next sample; samples between two marks belong to a timed region."""
+        return len(self.lines)
+
+    def stop(self, first=0, last=None):
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
@@ -110,7 +114,8 @@ class ClockSampler:
             self.proc.kill()
         sm, smax, reasons = [], None, set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for ln in self.lines:
+        window = self.lines[first:last] if last is not None and last > first else self.lines[first:]
+        for ln in window:
             parts = [p.strip() for p in ln.split(",")]
             if len(parts) < 6:
                 continue
@@ -187,52 +192,67 @@ def workload_config(args, note=None):
 
 
 class ConvProfile:
-    """CUDA-event durations and useful FLOPs of the convolution launches of one step."""
+    """Per-launch durations and useful FLOPs of the convolution launches of a step.
+
+    While a step runs, every fused-convolution call is recorded (its arguments stay alive).
+    After the step the recorded launches are replayed in order behind a device-side delay, so
+    the host is far ahead of the GPU and each launch is bracketed by CUDA events on the
+    launching stream without host-induced gaps."""
 
     def __init__(self):
-        self.records = []  # (start, end, nbr tensor, c_in, c_out, kind)
+        self.calls = []    # (callable, nbr tensor, c_in, c_out, kind) of the step being recorded
+        self.records = []  # (ms, pairs, M, K, c_in, c_out, kind) of replayed launches
+        self._pairs = {}
+
+    def replay(self):
+        torch.cuda.synchronize()
+        torch.cuda._sleep(200_000_000)  # ~0.1 s: time for the host to enqueue every launch below
+        evs = []
+        for fn, nbr, c_in, c_out, kind in self.calls:
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            fn()
+            e.record()
+            evs.append((s, e))
+        torch.cuda.synchronize()
+        for (s, e), (fn, nbr, c_in, c_out, kind) in zip(evs, self.calls):
+            key = nbr.data_ptr()
+            if key not in self._pairs:
+                self._pairs[key] = int((nbr >= 0).sum().item())
+            self.records.append((s.elapsed_time(e), self._pairs[key], nbr.shape[1], nbr.shape[0], c_in, c_out, kind))
+        self.calls = []
+        self._pairs = {}
 
     def summarise(self):
-        pair_counts = {}
-        tot_ms, tot_flop, n = 0.0, 0.0, 0
-        tc_ms, tc_flop, tc_n = 0.0, 0.0, 0
-        for s, e, nbr, c_in, c_out, kind in self.records:
-            key = nbr.data_ptr()
-            if key not in pair_counts:
-                pair_counts[key] = int((nbr >= 0).sum().item())
-            ms = s.elapsed_time(e)
-            fl = 2.0 * pair_counts[key] * c_in * c_out
-            tot_ms += ms; tot_flop += fl; n += 1
+        out = {"launches": 0, "ms": 0.0, "flop": 0.0, "tc_launches": 0, "tc_ms": 0.0, "tc_flop": 0.0}
+        for ms, pairs, M, K, c_in, c_out, kind in self.records:
+            fl = 2.0 * pairs * c_in * c_out
+            out["launches"] += 1; out["ms"] += ms; out["flop"] += fl
             if kind == "tcgen05":
-                tc_ms += ms; tc_flop += fl; tc_n += 1
-        return {"launches": n, "ms": tot_ms, "flop": tot_flop, "tc_launches": tc_n, "tc_ms": tc_ms, "tc_flop": tc_flop}
+                out["tc_launches"] += 1; out["tc_ms"] += ms; out["tc_flop"] += fl
+        return out
 
     def table(self, last_n):
         rows = []
-        for s, e, nbr, c_in, c_out, kind in self.records[-last_n:]:
-            pairs = int((nbr >= 0).sum().item())
-            ms = s.elapsed_time(e)
-            rows.append(f"{kind:8s} K={nbr.shape[0]:2d} M={nbr.shape[1]:8d} {c_in:4d}->{c_out:4d} pairs/M={pairs / max(nbr.shape[1], 1):5.2f} "
+        for ms, pairs, M, K, c_in, c_out, kind in self.records[-last_n:]:
+            rows.append(f"{kind:8s} K={K:2d} M={M:8d} {c_in:4d}->{c_out:4d} pairs/M={pairs / max(M, 1):5.2f} "
                         f"{ms * 1e3:8.1f} us {2.0 * pairs * c_in * c_out / ms / 1e9:7.1f} TFLOP/s")
         return "\n".join(rows)
 
 
 def install_conv_profiler(profile):
-    """Wrap the fused-convolution entry so each launch is bracketed by events on the launching stream."""
+    """Wrap the fused-convolution entry so that each call of a step is recorded for replay."""
     import warpconvnet_b200.nn.functional.sparse_conv as F
     from warpconvnet_b200._native import query_bytes, dtype_code
     orig = F.sparse_conv_fused
 
     def wrapped(in_features, weight, kernel_map, num_out_coords, epilogue=None, out_dtype=None, algo=0):
-        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        s.record()
         out = orig(in_features, weight, kernel_map, num_out_coords, epilogue, out_dtype, algo)
-        e.record()
         K, c_in, c_out = weight.shape
         tc = in_features.dtype != torch.float32 and query_bytes(
             "wcn_conv_packed_weight_bytes", 0, K, c_in, c_out, dtype_code(in_features.dtype)) > 0
-        profile.records.append((s, e, kernel_map.neighbor_table(num_out_coords), c_in, c_out,
-                                "tcgen05" if tc else "simt"))
+        profile.calls.append((lambda: orig(in_features, weight, kernel_map, num_out_coords, epilogue, out_dtype, algo),
+                              kernel_map.neighbor_table(num_out_coords), c_in, c_out, "tcgen05" if tc else "simt"))
         return out
 
     F.sparse_conv_fused = wrapped
@@ -301,28 +321,33 @@ def run_gpu_arm(args):
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         return float(ms.item())
 
+    sampler = ClockSampler(local_rank)
+    sampler.start()  # nvidia-smi needs about a second before its first sample
     with torch.no_grad():
         for _ in range(max(args.warmup, 3)):
             step_resident()
         _native.check_device_status(dev)
-        sampler = ClockSampler(local_rank)
-        sampler.start()
+        mark0 = sampler.mark()
         before = _native.launches_total()
         ms = timed(step_resident, args.steps)
         launches = _native.launches_total() - before
-        clocks = sampler.stop()
         for _ in range(2):
             step_e2e()
         ms_e2e = timed(step_e2e, args.steps)
+        mark1 = sampler.mark()
         _native.check_device_status(dev)
+        time.sleep(0.06)
+        clocks = sampler.stop(mark0, max(mark1, mark0 + 1))
+        clocks["window"] = "device-resident and end-to-end timed regions"
 
         # roofline of the dominant kernel: per-launch CUDA events over a timed region of its own
         profile = ConvProfile()
         restore = install_conv_profiler(profile)
         barrier()
-        prof_steps = min(args.steps, 5)
+        prof_steps = min(args.steps, 3)
         for _ in range(prof_steps):
             step_resident()
+            profile.replay()
         barrier()
         restore()
         prof = profile.summarise()
