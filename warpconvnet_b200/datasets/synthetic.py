@@ -149,6 +149,10 @@ def lidar_scene(target_voxels: Optional[int] = None, sweeps: int = 4, azimuth_st
     chunks = []
     total = np.zeros((0, 3), dtype=np.int32)
     n_sweeps = 0
+    n_el, n_az = len(elev), azimuth_steps
+    d_az = 2 * np.pi / n_az
+    corners = np.stack([np.stack([blo[:, 0], blo[:, 1]], 1), np.stack([blo[:, 0], bhi[:, 1]], 1),
+                        np.stack([bhi[:, 0], blo[:, 1]], 1), np.stack([bhi[:, 0], bhi[:, 1]], 1)], 1)  # [nb,4,2]
     while True:
         cy, sy = np.cos(yaw), np.sin(yaw)
         R = np.array([[cy, -sy, 0], [sy, cy, 0], [0, 0, 1.0]])
@@ -156,15 +160,33 @@ def lidar_scene(target_voxels: Optional[int] = None, sweeps: int = 4, azimuth_st
         t_hit = np.full(len(d), np.inf)
         down = d[:, 2] < -1e-6
         t_hit[down] = (-1.7 - pos[2]) / d[down, 2]
-        inv = 1.0 / np.where(np.abs(d) < 1e-12, 1e-12, d)
-        for b0 in range(0, nb, 50):  # slab test against boxes, in blocks to bound memory
-            lo = (blo[None, b0:b0 + 50] - pos) * inv[:, None, :]
-            hi = (bhi[None, b0:b0 + 50] - pos) * inv[:, None, :]
+        t2 = t_hit.reshape(n_el, n_az)
+        d3 = d.reshape(n_el, n_az, 3)
+        # every box only meets the rays inside the azimuth interval its footprint subtends
+        rel = corners - pos[None, None, :2]
+        caz = np.arctan2(rel[:, :, 1], rel[:, :, 0])
+        cen = np.arctan2((blo[:, 1] + bhi[:, 1]) / 2 - pos[1], (blo[:, 0] + bhi[:, 0]) / 2 - pos[0])
+        dd = (caz - cen[:, None] + np.pi) % (2 * np.pi) - np.pi
+        inside = (blo[:, 0] <= pos[0]) & (pos[0] <= bhi[:, 0]) & (blo[:, 1] <= pos[1]) & (pos[1] <= bhi[:, 1])
+        for b0 in range(nb):
+            if inside[b0]:
+                cols = np.arange(n_az)
+            else:
+                a0 = cen[b0] + dd[b0].min() - yaw
+                a1 = cen[b0] + dd[b0].max() - yaw
+                c0 = int(np.floor(a0 / d_az)) - 1
+                c1 = int(np.ceil(a1 / d_az)) + 1
+                cols = np.arange(c0, c1 + 1) % n_az
+            dv = d3[:, cols, :]
+            inv = 1.0 / np.where(np.abs(dv) < 1e-12, 1e-12, dv)
+            lo = (blo[b0] - pos) * inv
+            hi = (bhi[b0] - pos) * inv
             tmin = np.minimum(lo, hi).max(axis=2)
             tmax = np.maximum(lo, hi).min(axis=2)
-            ok = (tmax >= np.maximum(tmin, 0.0))
-            tb = np.where(ok, np.maximum(tmin, 0.0), np.inf).min(axis=1)
-            t_hit = np.minimum(t_hit, tb)
+            ok = tmax >= np.maximum(tmin, 0.0)
+            tb = np.where(ok, np.maximum(tmin, 0.0), np.inf)
+            t2[:, cols] = np.minimum(t2[:, cols], tb)
+        t_hit = t2.reshape(-1)
         rng_noise = 1.0 + 0.005 * rng.standard_normal(len(d))
         t = t_hit * rng_noise
         good = np.isfinite(t) & (t <= 80.0) & (t > 0.5)
