@@ -71,6 +71,7 @@ struct ConvTcParams {
   int nbuf;         // accumulator sets in TMEM: 1 or 2
   int cols;         // TMEM columns per accumulator (power of two >= block_n)
   int sa, sb;       // ring depths
+  int kbc;          // channel slices per ring slot (a slot holds kbc K-major tiles side by side)
   int64_t supertiles;
 };
 
@@ -123,9 +124,11 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int32_t
   }
 }
 
-__device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.expect_tx.shared::cta.b64 st, [%0], %1;\n\t}" ::"r"(bar), "r"(bytes)
                : "memory");
+}
+__device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
                "l"(src), "r"(bytes), "r"(bar)
                : "memory");
@@ -256,7 +259,7 @@ struct Control {
 
 // ------------------------------------------------------------------ kernel
 
-template <int BK, bool BF16, typename TO>
+template <int BK, int KBC, bool BF16, typename TO>
 __global__ void __launch_bounds__(THREADS, 1)
 conv_tcgen05_kernel(const ConvTcParams p) {
   constexpr int RB = BK * 2;         // bytes per tile row
@@ -269,14 +272,16 @@ conv_tcgen05_kernel(const ConvTcParams p) {
   const int G = p.G, BN = p.block_n, K = p.K, NBUF = p.nbuf;
   const int n0 = blockIdx.y * BN;
   const int KB = p.c_in / BK;
-  const int B_BYTES = BN * RB;
+  const int B_BYTES = BN * RB;         // one weight tile
+  constexpr int A_SLOT = KBC * A_BYTES;  // KBC channel slices per ring slot (KBC divides c_in / BK)
+  const int B_SLOT = KBC * B_BYTES;
   const int IDX_INTS = G * K * BLOCK_M;  // one staged neighbour table
 
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* gen = smem_raw + (base - smem_u32(smem_raw));
   const uint32_t a_base = base;
-  const uint32_t b_base = a_base + p.sa * A_BYTES;
-  const uint32_t misc = b_base + p.sb * B_BYTES;
+  const uint32_t b_base = a_base + p.sa * A_SLOT;
+  const uint32_t misc = b_base + p.sb * B_SLOT;
   uint8_t* misc_gen = gen + (misc - base);
   Control* ctl = reinterpret_cast<Control*>(misc_gen);
   int32_t* rows_idx = reinterpret_cast<int32_t*>(misc_gen + sizeof(Control));  // [2][G][K][128]
@@ -360,13 +365,17 @@ conv_tcgen05_kernel(const ConvTcParams p) {
           const int k = __ffs(rest) - 1;
           rest &= rest - 1;
           const char* bsrc_k = p.wpacked + ((int64_t)k * KB * p.c_out + n0) * RB;
-          for (int kb = 0; kb < KB; ++kb) {
-            // weight slice (offset k, channel slice kb): one bulk copy, shared by all sub-tiles
+          for (int kb0 = 0; kb0 < KB; kb0 += KBC) {
+            // weight tiles (offset k, channel slices kb0..): bulk copies onto one barrier, shared by all sub-tiles
             WCN_T0(t_be);
             if (!mbar_wait(bar(&ctl->b_empty[rb.slot]), rb.phase ^ 1, p.dev_status)) { ok = false; break; }
             WCN_ACC(1, t_be, true);
-            bulk_copy_g2s(b_base + rb.slot * B_BYTES, bsrc_k + (int64_t)kb * p.c_out * RB, (uint32_t)B_BYTES,
-                          bar(&ctl->b_full[rb.slot]));
+            const uint32_t fullb = bar(&ctl->b_full[rb.slot]);
+            mbar_expect_tx(fullb, (uint32_t)(KBC * B_BYTES));
+#pragma unroll
+            for (int u = 0; u < KBC; ++u)
+              bulk_copy_g2s(b_base + rb.slot * B_SLOT + u * B_BYTES, bsrc_k + (int64_t)(kb0 + u) * p.c_out * RB,
+                            (uint32_t)B_BYTES, fullb);
             rb.advance();
           }
         }
@@ -397,22 +406,25 @@ conv_tcgen05_kernel(const ConvTcParams p) {
         const int k = __ffs(rest) - 1;
         rest &= rest - 1;
         const uint32_t gbits = subtiles_at(mk0, mk1, mk2, mk3, k);
-        for (int kb = 0; kb < KB && ok; ++kb) {
+        for (int kb0 = 0; kb0 < KB && ok; kb0 += KBC) {
           for (uint32_t gb = gbits; gb; gb &= gb - 1) {
             const int g = __ffs(gb) - 1;
             WCN_T0(t_ae);
             if (!mbar_wait(bar(&ctl->a_empty[ra.slot]), ra.phase ^ 1, p.dev_status)) { ok = false; break; }
             WCN_ACC(0, t_ae, tid == GATHER_WARP0 * 32);
-            const uint32_t a_dst = a_base + ra.slot * A_BYTES;
+            const uint32_t a_dst = a_base + ra.slot * A_SLOT;
             const int32_t* rk = tab + (g * K + k) * BLOCK_M;
             int src[NJ];  // all index reads first, so the copies below issue back to back
 #pragma unroll
             for (int j = 0; j < NJ; ++j) src[j] = rk[j * RPI];
-            const char* fbase = p.feats + (int64_t)kb * RB + chunk * 16;
+            const char* fbase = p.feats + (int64_t)kb0 * RB + chunk * 16;
 #pragma unroll
             for (int j = 0; j < NJ; ++j) {
-              const char* sp = src[j] >= 0 ? fbase + (int64_t)src[j] * p.c_in * 2 : p.feats;
-              cp_async16(a_dst + aoff[j], sp, src[j] >= 0 ? 16u : 0u);
+              const bool have = src[j] >= 0;
+              const char* sp = have ? fbase + (int64_t)src[j] * p.c_in * 2 : p.feats;
+#pragma unroll
+              for (int u = 0; u < KBC; ++u)  // the row's next channel slices are contiguous in memory
+                cp_async16(a_dst + u * A_BYTES + aoff[j], have ? sp + u * RB : sp, have ? 16u : 0u);
             }
             cp_async_arrive(bar(&ctl->a_full[ra.slot]));  // hardware arrives when this thread's copies land
             ra.advance();
@@ -451,23 +463,29 @@ conv_tcgen05_kernel(const ConvTcParams p) {
           const int k = __ffs(rest) - 1;
           rest &= rest - 1;
           const uint32_t gbits = subtiles_at(mk0, mk1, mk2, mk3, k);
-          for (int kb = 0; kb < KB && ok; ++kb) {
+          for (int kb0 = 0; kb0 < KB && ok; kb0 += KBC) {
             WCN_T0(t_bf);
             if (!mbar_wait(bar(&ctl->b_full[rb.slot]), rb.phase, p.dev_status)) { ok = false; break; }
             WCN_ACC(4, t_bf, true);
-            const uint64_t bdesc = smem_desc<RB>(b_base + rb.slot * B_BYTES);
+            const uint32_t b_slot = b_base + rb.slot * B_SLOT;
             for (uint32_t gb = gbits; gb; gb &= gb - 1) {
               const int g = __ffs(gb) - 1;
               WCN_T0(t_af);
               if (!mbar_wait(bar(&ctl->a_full[ra.slot]), ra.phase, p.dev_status)) { ok = false; break; }
               WCN_ACC(5, t_af, true);
               tc_fence_after();
-              const uint64_t adesc = smem_desc<RB>(a_base + ra.slot * A_BYTES);
+              const uint32_t a_slot = a_base + ra.slot * A_SLOT;
               const uint32_t d = tmem_base + (uint32_t)((ab * G + g) * p.cols);
+              const uint32_t acc0 = (started >> g) & 1u;
 #pragma unroll
-              for (int kk = 0; kk < BK / 16; ++kk)
-                umma_f16(d, adesc + (uint64_t)(kk * 2), bdesc + (uint64_t)(kk * 2), idesc,
-                         (((started >> g) & 1u) | (uint32_t)kk) ? 1u : 0u);
+              for (int u = 0; u < KBC; ++u) {
+                const uint64_t adesc = smem_desc<RB>(a_slot + u * A_BYTES);
+                const uint64_t bdesc = smem_desc<RB>(b_slot + u * B_BYTES);
+#pragma unroll
+                for (int kk = 0; kk < BK / 16; ++kk)
+                  umma_f16(d, adesc + (uint64_t)(kk * 2), bdesc + (uint64_t)(kk * 2), idesc,
+                           (acc0 | (uint32_t)(u | kk)) ? 1u : 0u);
+              }
               started |= 1u << g;
               umma_commit(bar(&ctl->a_empty[ra.slot]));  // slot is free once these MMAs have read it
               ra.advance();
@@ -602,14 +620,29 @@ bool plan_launch(ConvTcParams& p, int bk, size_t* smem, dim3* grid) {
   p.cols = cols;
   int g = cols >= 128 ? 2 : 4;
   while (g > 1 && ((tiles + g - 1) / g) * split < 2 * (int64_t)sms) g /= 2;
-  const size_t a_stage = (size_t)BLOCK_M * bk * 2, b_stage = (size_t)p.block_n * bk * 2;
+  const size_t a_unit = (size_t)BLOCK_M * bk * 2, b_unit = (size_t)p.block_n * bk * 2;
   const size_t limit = 224 * 1024;
-  size_t fixed = 0;
-  for (;; g /= 2) {  // two staged neighbour tables + at least 4 A slots and 2 B slots must fit
+  const int kb_total = p.c_in / bk;
+  // Channel slices per ring slot: as many as give a 32 KiB row slot, fewer if the rings would not fit.
+  int kbc = (int)((32 * 1024) / a_unit);
+  if (kbc > kb_total) kbc = kb_total;
+  if (kbc > 4) kbc = 4;
+  if (kbc < 1) kbc = 1;
+  while (kb_total % kbc != 0) --kbc;
+  size_t fixed = 0, a_stage = 0, b_stage = 0;
+  for (;;) {  // two staged neighbour tables + a few row slots and 2 weight slots must fit
     fixed = 1024 + sizeof(Control) + 2 * (size_t)g * p.K * BLOCK_M * 4 + 128;
-    if (fixed + 4 * a_stage + 2 * b_stage <= limit) break;
+    a_stage = kbc * a_unit;
+    b_stage = kbc * b_unit;
+    if (fixed + (kbc > 1 ? 3 : 4) * a_stage + 2 * b_stage <= limit) break;
+    if (kbc > 1) {
+      do { --kbc; } while (kb_total % kbc != 0);
+      continue;
+    }
     if (g == 1) return false;
+    g /= 2;
   }
+  p.kbc = kbc;
   p.G = g;
   p.nbuf = (g * cols * 2 <= 512) ? 2 : 1;
   p.supertiles = (tiles + g - 1) / g;
@@ -631,12 +664,9 @@ bool plan_launch(ConvTcParams& p, int bk, size_t* smem, dim3* grid) {
   return true;
 }
 
-template <int BK, bool BF16, typename TO>
-int launch_tc(ConvTcParams& p, cudaStream_t st) {
-  size_t smem = 0;
-  dim3 grid;
-  if (!plan_launch(p, BK, &smem, &grid)) return WCN_ERR_UNSUPPORTED_CONFIG;
-  auto kern = conv_tcgen05_kernel<BK, BF16, TO>;
+template <int BK, int KBC, bool BF16, typename TO>
+int launch_kbc(const ConvTcParams& p, size_t smem, dim3 grid, cudaStream_t st) {
+  auto kern = conv_tcgen05_kernel<BK, KBC, BF16, TO>;
   static bool configured[64] = {};  // per template instance and device: opt in to large shared memory once
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return WCN_ERR_INITIALIZATION;
@@ -649,6 +679,20 @@ int launch_tc(ConvTcParams& p, cudaStream_t st) {
   }
   kern<<<grid, THREADS, smem, st>>>(p);
   return cudaGetLastError() == cudaSuccess ? WCN_OK : WCN_ERR_EXECUTION;
+}
+
+template <int BK, bool BF16, typename TO>
+int launch_tc(ConvTcParams& p, cudaStream_t st) {
+  size_t smem = 0;
+  dim3 grid;
+  if (!plan_launch(p, BK, &smem, &grid)) return WCN_ERR_UNSUPPORTED_CONFIG;
+  switch (p.kbc) {
+    case 1: return launch_kbc<BK, 1, BF16, TO>(p, smem, grid, st);
+    case 2: return launch_kbc<BK, 2, BF16, TO>(p, smem, grid, st);
+    case 3: return launch_kbc<BK, 3, BF16, TO>(p, smem, grid, st);
+    case 4: return launch_kbc<BK, 4, BF16, TO>(p, smem, grid, st);
+    default: return WCN_ERR_UNSUPPORTED_CONFIG;
+  }
 }
 
 }  // namespace
