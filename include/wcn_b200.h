@@ -181,7 +181,9 @@ int wcn_nbr_transpose(const int32_t* nbr_fwd, int32_t num_offsets, int64_t num_o
 
 /* codes[i] = 3-D Morton code of (x - min_xyz[0], y - min_xyz[1], z - min_xyz[2]), x in bit
  * 0, y in bit 1, z in bit 2, up to 21 bits per axis.  coords has `row_ints` int32 per row
- * and the x column at `col0` (3,0 for xyz rows; 4,1 for batch-indexed rows).
+ * and the x column at `col0` (3,0 for xyz rows; 4,1 for batch-indexed rows).  `min_xyz` is a
+ * DEVICE pointer to three int32 (or NULL for no shift), so the caller's min-reduction needs
+ * no round trip to the host.
  * Replaces assign_order_discrete_20bit_kernel_4points (warpconvnet/csrc/morton_code.cu:71-94)
  * and the min subtraction of morton_code (coords/ops/serialization.py:224-225). */
 int wcn_morton20(const int32_t* coords, int64_t n, int32_t row_ints, int32_t col0,

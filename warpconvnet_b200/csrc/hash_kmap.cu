@@ -296,9 +296,11 @@ __device__ __forceinline__ unsigned long long spread3(unsigned long long n) {
 }
 
 __global__ void morton20_kernel(const int32_t* __restrict__ coords, int64_t n, int row_ints, int col0,
-                                int mx, int my, int mz, int64_t* __restrict__ codes) {
+                                const int32_t* __restrict__ min_xyz, int64_t* __restrict__ codes) {
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
+  const int mx = min_xyz ? __ldg(&min_xyz[0]) : 0, my = min_xyz ? __ldg(&min_xyz[1]) : 0,
+            mz = min_xyz ? __ldg(&min_xyz[2]) : 0;
   const int32_t* r = coords + i * row_ints + col0;
   const unsigned long long x = (unsigned long long)(uint32_t)(r[0] - mx);
   const unsigned long long y = (unsigned long long)(uint32_t)(r[1] - my);
@@ -559,8 +561,7 @@ extern "C" int wcn_morton20(const int32_t* coords, int64_t n, int32_t row_ints, 
   if (n < 0 || row_ints < 3 || col0 < 0 || col0 + 3 > row_ints) return WCN_ERR_INVALID_PARAMETERS;
   if (n == 0) return WCN_OK;
   if (!coords || !codes) return WCN_ERR_INVALID_PARAMETERS;
-  const int mx = min_xyz ? min_xyz[0] : 0, my = min_xyz ? min_xyz[1] : 0, mz = min_xyz ? min_xyz[2] : 0;
-  morton20_kernel<<<grid_for(n), kThreads, 0, wcn_stream(stream)>>>(coords, n, row_ints, col0, mx, my, mz, codes);
+  morton20_kernel<<<grid_for(n), kThreads, 0, wcn_stream(stream)>>>(coords, n, row_ints, col0, min_xyz, codes);
   WCN_CHECK_LAUNCH();
   return WCN_OK;
 }

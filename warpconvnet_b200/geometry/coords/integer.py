@@ -31,8 +31,9 @@ class IntCoords(Coords):
         self.voxel_origin = voxel_origin
         self.tensor_stride = (ntuple(tensor_stride, ndim=batched_tensor.shape[1])
                               if tensor_stride is not None else None)
-        self._hashmap = None
-        self._bcoords = None
+        # derived data (batch-indexed form, hash table), shared by reference between coordinate
+        # objects that view the same rows (see share_derived)
+        self._shared = {}
         self.check()
 
     def check(self):
@@ -48,17 +49,31 @@ class IntCoords(Coords):
                          self.tensor_stride)
 
     @property
+    def _bcoords(self):
+        return self._shared.get("bcoords")
+
+    @_bcoords.setter
+    def _bcoords(self, value):
+        self._shared["bcoords"] = value
+
+    def share_derived(self, other: "IntCoords") -> "IntCoords":
+        """Use the same derived data as ``other``, which must hold the same rows."""
+        self._shared = other._shared
+        return self
+
+    @property
     def batch_indexed_coordinates(self) -> Tensor:
-        """[N, 4] (batch, x, y, z); built once per coordinate object."""
-        if self._bcoords is None:
-            self._bcoords = batch_indexed_coordinates(self.batched_tensor, self.offsets)
-        return self._bcoords
+        """[N, 4] (batch, x, y, z); built once per set of rows."""
+        if self._shared.get("bcoords") is None:
+            self._shared["bcoords"] = batch_indexed_coordinates(self.batched_tensor, self.offsets)
+        return self._shared["bcoords"]
 
     @property
     def hashmap(self) -> TorchHashTable:
-        if self._hashmap is None:
-            self._hashmap = TorchHashTable.from_keys(self.batch_indexed_coordinates.to(torch.int32))
-        return self._hashmap
+        """Hash table of the batch-indexed int32 coordinates; built once per set of rows."""
+        if self._shared.get("hashmap") is None:
+            self._shared["hashmap"] = TorchHashTable.from_keys(self.batch_indexed_coordinates.to(torch.int32))
+        return self._shared["hashmap"]
 
     @property
     def stride(self):

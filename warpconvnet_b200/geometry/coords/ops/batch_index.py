@@ -12,12 +12,17 @@ def batch_index_from_offset(offsets: Tensor) -> Tensor:
 
 
 @torch.no_grad()
+def batch_index_on(offsets: Tensor, n: int, device, dtype=torch.int32) -> Tensor:
+    """Batch index of rows 0..n-1 on ``device``: one bucketize of an arange against the
+    batch boundaries (no host synchronisation, no repeat_interleave)."""
+    bounds = offsets[1:].to(device=device, dtype=torch.int64)
+    return torch.bucketize(torch.arange(n, device=device, dtype=torch.int64), bounds, right=True).to(dtype)
+
+
+@torch.no_grad()
 def batch_indexed_coordinates(batched_coords: Tensor, offsets: Tensor) -> Tensor:
     """Prepend the batch index column: [N, D] -> [N, D+1]."""
-    counts = torch.diff(offsets.to(batched_coords.device))
-    batch_index = torch.repeat_interleave(
-        torch.arange(len(counts), device=batched_coords.device, dtype=batched_coords.dtype), counts,
-        output_size=batched_coords.shape[0])
+    batch_index = batch_index_on(offsets, batched_coords.shape[0], batched_coords.device, batched_coords.dtype)
     return torch.cat([batch_index.unsqueeze(1), batched_coords], dim=1)
 
 

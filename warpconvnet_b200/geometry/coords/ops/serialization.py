@@ -62,11 +62,10 @@ def morton_code(coords: Tensor, threads_per_block: int = 256,
     if perm != [0, 1, 2]:
         c = c[:, perm]
     c = c.contiguous()
-    mins = c.min(dim=0).values.cpu()
-    min_xyz = (ctypes.c_int32 * 3)(*[int(v) for v in mins])
+    mins = c.min(dim=0).values.contiguous()  # stays on the device: no host synchronisation
     codes = torch.empty(c.shape[0], dtype=torch.int64, device=c.device)
-    check(lib().wcn_morton20(ptr(c), c.shape[0], 3, 0, ctypes.addressof(min_xyz), ptr(codes),
-                             stream_ptr(c.device)), "wcn_morton20")
+    check(lib().wcn_morton20(ptr(c), c.shape[0], 3, 0, ptr(mins), ptr(codes), stream_ptr(c.device)),
+          "wcn_morton20")
     return codes
 
 
@@ -91,9 +90,8 @@ def encode(grid_coord: Tensor, batch_offsets: Optional[Tensor] = None,
         return SerializationResult(codes, e if return_perm else None, e if return_inverse else None)
     if batch_offsets is not None and len(batch_offsets) > 2:
         # sort by code inside each batch segment: stable sort by code, then stable sort by batch
-        counts = torch.diff(batch_offsets.to(codes.device))
-        seg = torch.repeat_interleave(torch.arange(len(counts), device=codes.device), counts,
-                                      output_size=codes.shape[0])
+        from .batch_index import batch_index_on
+        seg = batch_index_on(batch_offsets, codes.shape[0], codes.device, torch.int64)
         by_code = torch.argsort(codes, stable=True)
         perm = by_code[torch.argsort(seg[by_code], stable=True)]
     else:

@@ -21,12 +21,15 @@ from .batch_index import offsets_from_batch_index
 
 @torch.no_grad()
 def unique_strided_rows(bcoords: Tensor, stride: Tuple[int, int, int] = (1, 1, 1),
-                        hash_method: HashMethod = HashMethod.CITY, return_parent: bool = False):
+                        hash_method: HashMethod = HashMethod.CITY, return_parent: bool = False,
+                        in_offsets: Optional[Tensor] = None):
     """Distinct rows of ``floor(bcoords / [1, *stride])``.
 
     Returns ``(rows [M,4] int32, unique_index [M] int32, parent [N] int32 | None)``:
     ``unique_index`` are the (ascending) source rows of the first occurrences and
-    ``parent[i]`` the output row input i collapsed into.
+    ``parent[i]`` the output row input i collapsed into.  With ``in_offsets`` (the batch
+    offsets of the input rows) a fourth value is returned, the CPU batch offsets of the
+    output rows, obtained with the same single host synchronisation as the row count.
     """
     assert bcoords.is_cuda, f"Batched coordinates must be on cuda device, got {bcoords.device}"
     assert bcoords.dtype == torch.int32 and bcoords.ndim == 2 and bcoords.shape[1] == 4
@@ -35,7 +38,8 @@ def unique_strided_rows(bcoords: Tensor, stride: Tuple[int, int, int] = (1, 1, 1
     n = c.shape[0]
     if n == 0:
         e = torch.empty(0, dtype=torch.int32, device=dev)
-        return c.clone(), e, (e.clone() if return_parent else None)
+        base = (c.clone(), e, (e.clone() if return_parent else None))
+        return base if in_offsets is None else base + (torch.zeros(len(in_offsets), dtype=torch.long),)
     cap = max(16, 2 * n)
     table = torch.empty(query_bytes("wcn_hash_table_bytes", cap), dtype=torch.uint8, device=dev)
     strd = (ctypes.c_int32 * 3)(*[int(s) for s in stride])
@@ -47,24 +51,40 @@ def unique_strided_rows(bcoords: Tensor, stride: Tuple[int, int, int] = (1, 1, 1
     count = torch.empty(1, dtype=torch.int64, device=dev)
     check(lib().wcn_unique_mark(ptr(c), n, sp, ptr(table), cap, hash_method.value, ptr(ws), ptr(count), st),
           "wcn_unique_mark")
-    m = int(count.item())  # output size is needed on the host to allocate
-    rows = torch.empty((m, 4), dtype=torch.int32, device=dev)
-    uidx = torch.empty(m, dtype=torch.int32, device=dev)
+    # Outputs are sized for the worst case (every row distinct) so that nothing has to be read
+    # back before the rows are emitted; the one host synchronisation happens in the caller's
+    # read of the count / batch offsets.
+    rows = torch.empty((n, 4), dtype=torch.int32, device=dev)
+    uidx = torch.full((n,), torch.iinfo(torch.int32).max, dtype=torch.int32, device=dev)
     parent = torch.empty(n, dtype=torch.int32, device=dev) if return_parent else None
     check(lib().wcn_unique_emit(ptr(c), n, sp, ptr(ws), ptr(rows), ptr(uidx), ptr(parent), st), "wcn_unique_emit")
-    return rows, uidx, parent
+    if in_offsets is not None:
+        # first occurrences are emitted in ascending source row, so the output batch boundaries are
+        # the ranks of the input boundaries among the first-occurrence rows
+        out_offsets = torch.searchsorted(uidx, in_offsets.to(device=dev, dtype=torch.int32)).cpu().long()
+        m = int(out_offsets[-1])
+        return rows[:m], uidx[:m], parent, out_offsets
+    m = int(count.item())
+    return rows[:m], uidx[:m], parent
 
 
 @torch.no_grad()
-def stride_coords(batch_indexed_coords: Tensor, stride: Tuple[int, ...], order=None):
-    """Down-sample coordinates by ``stride``; returns (coords [M,4], CPU offsets [B+1])."""
+def stride_coords(batch_indexed_coords: Tensor, stride: Tuple[int, ...], order=None,
+                  in_offsets: Optional[Tensor] = None):
+    """Down-sample coordinates by ``stride``; returns (coords [M,4], CPU offsets [B+1]).
+    ``in_offsets`` (batch offsets of the input, when the caller has them) saves a second host
+    synchronisation for the output offsets."""
     nd = batch_indexed_coords.shape[1] - 1
     assert len(stride) == nd, (f"Stride must match the number of spatial dimensions. Got {len(stride)} spatial "
                                f"dimensions for but coordinates with {nd} spatial dimensions.")
     if all(s == 1 for s in stride):
         return batch_indexed_coords, offsets_from_batch_index(batch_indexed_coords[:, 0])
-    rows, _, _ = unique_strided_rows(batch_indexed_coords, ntuple(stride, ndim=nd))
     from .serialization import POINT_ORDERING, encode
+    if in_offsets is not None and (order is None or order == POINT_ORDERING.RANDOM):
+        rows, _, _, out_offsets = unique_strided_rows(batch_indexed_coords, ntuple(stride, ndim=nd),
+                                                      in_offsets=in_offsets)
+        return rows, out_offsets
+    rows, _, _ = unique_strided_rows(batch_indexed_coords, ntuple(stride, ndim=nd))
     if order is not None and order != POINT_ORDERING.RANDOM:
         offsets = offsets_from_batch_index(rows[:, 0])
         perm = encode(rows[:, 1:], batch_offsets=offsets, order=order, return_perm=True).perm

@@ -88,8 +88,11 @@ def generate_kernel_map(batch_indexed_in_coords: Tensor, batch_indexed_out_coord
                         kernel_center_offset: Optional[Tuple[int, ...]] = None,
                         method: Literal["offset", "size"] = "size",
                         hash_method: HashMethod = HashMethod.CITY,
-                        skip_symmetric_kernel_map: bool = False) -> IntSearchResult:
-    """Kernel map between input and output coordinates ([N,4] / [M,4] int32)."""
+                        skip_symmetric_kernel_map: bool = False,
+                        hashtable: Optional[TorchHashTable] = None) -> IntSearchResult:
+    """Kernel map between input and output coordinates ([N,4] / [M,4] int32).
+    ``hashtable`` (an addition to the reference signature): a table already built over
+    ``batch_indexed_in_coords``, to skip rebuilding it."""
     dev = batch_indexed_in_coords.device
     assert dev == batch_indexed_out_coords.device
     assert batch_indexed_in_coords.dtype == torch.int32
@@ -117,7 +120,10 @@ def generate_kernel_map(batch_indexed_in_coords: Tensor, batch_indexed_out_coord
         "Kernel dilation is not supported."
     assert kernel_center_offset is None, "Custom kernel_center_offset is not supported."
 
-    hashtable = TorchHashTable.from_keys(batch_indexed_in_coords, hash_method=hash_method, device=dev)
+    if hashtable is None or hashtable.hash_method != hash_method:
+        hashtable = TorchHashTable.from_keys(batch_indexed_in_coords, hash_method=hash_method, device=dev)
+    else:
+        assert len(hashtable.vector_keys) == batch_indexed_in_coords.shape[0], "hashtable was built over other keys"
     return _kernel_map_from_size(hashtable, batch_indexed_out_coords, kernel_size,
                                  identity_map_index=identity_map_index, return_type="offsets",
                                  skip_symmetric_kernel_map=skip_symmetric_kernel_map, query_stride=stride,

@@ -234,7 +234,7 @@ def generate_output_coords_and_kernel_map(input_sparse_tensor: Voxels, kernel_si
             out_coords = out_coords.to(torch.int32)
         out_offsets = output_spatially_sparse_tensor.offsets
     elif any(s != 1 for s in stride):
-        out_coords, out_offsets = stride_coords(in_coords, stride)
+        out_coords, out_offsets = stride_coords(in_coords, stride, in_offsets=input_sparse_tensor.offsets)
     else:
         out_coords, out_offsets = in_coords, input_sparse_tensor.offsets
 
@@ -260,15 +260,29 @@ def generate_output_coords_and_kernel_map(input_sparse_tensor: Voxels, kernel_si
             fwd = cache.get(key_for(False, out_offsets, input_sparse_tensor.offsets))
         if fwd is None:
             # forward map: table on the (fine) output coordinates, (coarse) inputs * stride as queries
-            fwd = generate_kernel_map(out_coords, in_coords, stride, kernel_size, None)
+            fwd = generate_kernel_map(out_coords, in_coords, stride, kernel_size, None,
+                                      hashtable=_cached_table(output_spatially_sparse_tensor, out_coords))
         kernel_map = fwd.swapped(num_in=out_coords.shape[0])
     else:
-        kernel_map = generate_kernel_map(in_coords, out_coords, stride, kernel_size, None)
+        kernel_map = generate_kernel_map(in_coords, out_coords, stride, kernel_size, None,
+                                         hashtable=_cached_table(input_sparse_tensor, in_coords))
 
     if input_sparse_tensor.cache is None:
         input_sparse_tensor._extra_attributes["_cache"] = IntSearchCache()
     input_sparse_tensor.cache.put(key, kernel_map)
     return out_coords, out_offsets, kernel_map
+
+
+def _cached_table(voxels: Optional[Voxels], coords: Tensor):
+    """The hash table of a tensor's own coordinates (built once per coordinate set and shared
+    by every layer that searches it), or None when ``coords`` is not that tensor's own array."""
+    if voxels is None:
+        return None
+    ic = voxels.batched_coordinates
+    own = ic.batch_indexed_coordinates
+    if own.dtype != torch.int32 or own.data_ptr() != coords.data_ptr() or own.shape != coords.shape:
+        return None
+    return ic.hashmap
 
 
 # --------------------------------------------------------------------------- autograd
@@ -412,12 +426,10 @@ def spatially_sparse_conv(
     # batch-indexed form (so nothing is rebuilt layer after layer).
     if output_spatially_sparse_tensor is not None and order == POINT_ORDERING.RANDOM:
         src = output_spatially_sparse_tensor.batched_coordinates
-        out_ic = IntCoords(src.batched_tensor, offsets=src.offsets)
-        out_ic._bcoords, out_ic._hashmap = src._bcoords, src._hashmap
+        out_ic = IntCoords(src.batched_tensor, offsets=src.offsets).share_derived(src)
     elif all(s == 1 for s in _stride) and order == POINT_ORDERING.RANDOM:
         src = input_sparse_tensor.batched_coordinates
-        out_ic = IntCoords(src.batched_tensor, offsets=src.offsets)
-        out_ic._bcoords, out_ic._hashmap = src._bcoords, src._hashmap
+        out_ic = IntCoords(src.batched_tensor, offsets=src.offsets).share_derived(src)
     else:
         out_ic = IntCoords(out_coords[:, 1:], offsets=out_offsets.cpu().int())
         out_ic._bcoords = out_coords
