@@ -36,9 +36,10 @@ constexpr int EPI_THREADS = 128;      // warps 0..3: TMEM lane quarter = warp in
 constexpr int IDX_THREADS = 128;      // warps 4..7: neighbour-table staging
 constexpr int GATHER_WARP0 = 8;       // warps 8..15: row gathers
 constexpr int GATHER_THREADS = 256;
-constexpr int MMA_WARP = 16;          // MMA issuer, TMEM owner
-constexpr int WEIGHT_WARP = 17;       // weight bulk copies
-constexpr int THREADS = 576;
+constexpr int MMA_WARP = 16;          // warps 16, 17: MMA issuers (even / odd sub-tiles); warp 16 owns TMEM
+constexpr int MMA_ISSUERS = 2;
+constexpr int WEIGHT_WARP = 18;       // weight bulk copies
+constexpr int THREADS = 608;
 constexpr long long kWaitCycles = 4000000000ll;        // about two seconds
 constexpr unsigned kSuspendNs = 20000;                  // per-attempt parking limit of a barrier wait
 constexpr long long kStatusPollCycles = 2000000ll;     // about a millisecond between looks at the status word
@@ -293,12 +294,12 @@ conv_tcgen05_kernel(const ConvTcParams p) {
 
   if (tid == 0) {
     for (int s = 0; s < p.sa; ++s) { mbar_init(bar(&ctl->a_full[s]), GATHER_THREADS); mbar_init(bar(&ctl->a_empty[s]), 1); }
-    for (int s = 0; s < p.sb; ++s) { mbar_init(bar(&ctl->b_full[s]), 1); mbar_init(bar(&ctl->b_empty[s]), 1); }
+    for (int s = 0; s < p.sb; ++s) { mbar_init(bar(&ctl->b_full[s]), 1); mbar_init(bar(&ctl->b_empty[s]), MMA_ISSUERS); }
     for (int i = 0; i < 2; ++i) {
-      mbar_init(bar(&ctl->acc_full[i]), 1);
+      mbar_init(bar(&ctl->acc_full[i]), MMA_ISSUERS);
       mbar_init(bar(&ctl->acc_empty[i]), EPI_THREADS);
       mbar_init(bar(&ctl->info_full[i]), 1);
-      mbar_init(bar(&ctl->info_empty[i]), EPI_THREADS + 2 + GATHER_THREADS / 32);  // epilogue threads, MMA thread, weight thread, gather warps
+      mbar_init(bar(&ctl->info_empty[i]), EPI_THREADS + MMA_ISSUERS + 1 + GATHER_THREADS / 32);  // epilogue threads, MMA threads, weight thread, gather warps
     }
     mbar_init(bar(&ctl->idx_sync), IDX_THREADS);
     for (int g = 0; g < MAX_G; ++g) ctl->mask_acc[0][g] = ctl->mask_acc[1][g] = 0;
@@ -437,8 +438,12 @@ conv_tcgen05_kernel(const ConvTcParams p) {
     }
     WCN_ACC(3, t_prod, tid == GATHER_WARP0 * 32);
     cp_async_drain();
-  } else if (warp == MMA_WARP) {
-    // ================================================================ MMA issuer
+  } else if (warp >= MMA_WARP && warp < MMA_WARP + MMA_ISSUERS) {
+    // ================================================================ MMA issuers
+    // Two threads share the issue work: issuer w takes the sub-tiles with (g & 1) == w.  Both
+    // walk the same slot sequence (skipping the other's row slots), both release every weight
+    // slot and both sign off the accumulator set.
+    const uint32_t issuer = (uint32_t)(warp - MMA_WARP);
     if (lane == 0) {
       const uint32_t idesc = (1u << 4) | ((BF16 ? 1u : 0u) << 7) | ((BF16 ? 1u : 0u) << 10) |
                              ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BLOCK_M >> 4) << 24);
@@ -470,6 +475,10 @@ conv_tcgen05_kernel(const ConvTcParams p) {
             const uint32_t b_slot = b_base + rb.slot * B_SLOT;
             for (uint32_t gb = gbits; gb; gb &= gb - 1) {
               const int g = __ffs(gb) - 1;
+              if (((uint32_t)g & 1u) != issuer) {  // the other issuer's slot
+                ra.advance();
+                continue;
+              }
               WCN_T0(t_af);
               if (!mbar_wait(bar(&ctl->a_full[ra.slot]), ra.phase, p.dev_status)) { ok = false; break; }
               WCN_ACC(5, t_af, true);
