@@ -126,7 +126,11 @@ def ptr(t: Optional[torch.Tensor]) -> Optional[int]:
 
 
 def stream_ptr(device: torch.device) -> int:
-    return torch.cuda.current_stream(device).cuda_stream
+    """Raw handle of torch's current stream on ``device`` (the launches go there)."""
+    idx = device.index
+    if idx is None:
+        idx = torch.cuda.current_device()
+    return torch._C._cuda_getCurrentRawStream(idx)
 
 
 def dtype_code(dtype: torch.dtype) -> int:

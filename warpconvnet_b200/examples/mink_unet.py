@@ -15,7 +15,7 @@ import torch
 import torch.nn as nn
 
 from ..geometry.types.voxels import Voxels
-from ..nn.functional.sparse_conv import ConvEpilogue
+from ..nn.functional.sparse_conv import ConvEpilogue, prefetch_strided_coordinates
 from ..nn.functional.transforms import cat
 from ..nn.modules.activations import ReLU
 from ..nn.modules.sequential import Sequential, fold_batchnorm
@@ -108,6 +108,9 @@ class MinkUNetBase(nn.Module):
         return nn.Sequential(*layers)
 
     def forward(self, x: Voxels) -> Voxels:
+        # all four coarse coordinate sets first: their size read-backs then wait for coordinate
+        # kernels only, and the convolutions below queue without a host synchronisation
+        prefetch_strided_coordinates(x, [2, 2, 2, 2])
         out_p1 = self.conv0(x)
         out_b1p2 = self.block1(self.conv1(out_p1))
         out_b2p4 = self.block2(self.conv2(out_b1p2))

@@ -22,6 +22,8 @@ def list_to_cat_tensor(tensors: Sequence[Tensor]):
 
 def _as_cpu_offsets(offsets) -> Tensor:
     if isinstance(offsets, Tensor):
+        if offsets.device.type == "cpu" and not offsets.requires_grad and offsets.dtype in (torch.int32, torch.int64):
+            return offsets
         offsets = offsets.detach().cpu()
     elif isinstance(offsets, (list, tuple)):
         offsets = torch.tensor(list(offsets), dtype=torch.int64)

@@ -40,7 +40,8 @@ class Geometry:
         self.batched_coordinates = batched_coordinates
         self.batched_features = to_batched_features(batched_features, batched_coordinates.offsets,
                                                     device=kwargs.get("device", None))
-        assert bool((batched_coordinates.offsets.long() == self.batched_features.offsets.long()).all())
+        a, b = batched_coordinates.offsets, self.batched_features.offsets
+        assert a is b or bool((a.long() == b.long()).all())
         if "_extra_attributes" in kwargs:
             attr = kwargs.pop("_extra_attributes")
             assert isinstance(attr, dict), f"_extra_attributes must be a dictionary, got {attr}"

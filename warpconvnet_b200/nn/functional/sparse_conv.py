@@ -159,13 +159,21 @@ def _prepared_weight(weight: Tensor, dtype: torch.dtype, algo: int = CONV_AUTO):
     return w, packed
 
 
+def _as_f32_on(t: Optional[Tensor], dev: torch.device) -> Optional[Tensor]:
+    if t is None:
+        return None
+    if t.dtype != torch.float32 or t.device != dev:
+        t = t.to(device=dev, dtype=torch.float32)
+    return t if t.is_contiguous() else t.contiguous()
+
+
 def sparse_conv_fused(in_features: Tensor, weight: Tensor, kernel_map: IntSearchResult, num_out_coords: int,
                       epilogue: Optional[ConvEpilogue] = None, out_dtype: Optional[torch.dtype] = None,
                       algo: int = CONV_AUTO) -> Tensor:
     """One launch: all kernel offsets + epilogue.  The weight is used in the
     feature dtype (fp32, fp16 or bf16); accumulation is fp32."""
     require_cuda(in_features, "in_features")
-    x = in_features.contiguous()
+    x = in_features if in_features.is_contiguous() else in_features.contiguous()
     w, packed = _prepared_weight(weight, x.dtype, algo)
     K, c_in, c_out = w.shape
     assert x.shape[1] == c_in, f"features have {x.shape[1]} channels, weight expects {c_in}"
@@ -177,11 +185,13 @@ def sparse_conv_fused(in_features: Tensor, weight: Tensor, kernel_map: IntSearch
     nbr = kernel_map.neighbor_table(num_out_coords)
     assert nbr.shape[0] == K, f"kernel map has {nbr.shape[0]} offsets, weight has {K}"
     ep = epilogue or ConvEpilogue()
-    scale = ep.scale.to(device=dev, dtype=torch.float32).contiguous() if ep.scale is not None else None
-    shift = ep.shift.to(device=dev, dtype=torch.float32).contiguous() if ep.shift is not None else None
+    scale = _as_f32_on(ep.scale, dev)
+    shift = _as_f32_on(ep.shift, dev)
     residual = None
     if ep.residual is not None:
-        residual = ep.residual.to(dtype=out_dtype).contiguous()
+        residual = ep.residual if ep.residual.dtype == out_dtype else ep.residual.to(dtype=out_dtype)
+        if not residual.is_contiguous():
+            residual = residual.contiguous()
         assert residual.shape == out.shape, f"residual {tuple(residual.shape)} != output {tuple(out.shape)}"
     check(lib().wcn_conv_fwd(algo, ptr(x), x.shape[0], ptr(w), ptr(packed), ptr(nbr), num_out_coords, K, c_in,
                              c_out, dtype_code(x.dtype), ptr(scale), ptr(shift), ptr(residual), int(ep.relu),
@@ -201,7 +211,9 @@ def _implicit_gemm_forward_logic(in_features: Tensor, weight: Tensor, kernel_map
     min_dtype = _min_dtype(feature_dtype, weight.dtype)
     if min_dtype == torch.float64:
         raise ValueError("float64 is not supported by the native kernels; use explicit_gemm")
-    x = in_features.detach().to(dtype=min_dtype)
+    x = in_features if in_features.dtype == min_dtype else in_features.to(dtype=min_dtype)
+    if x.requires_grad:
+        x = x.detach()
     return sparse_conv_fused(x, weight, kernel_map, num_out_coords, epilogue, out_dtype=in_features.dtype
                              if in_features.dtype in (torch.float32, torch.float16, torch.bfloat16) else None)
 
@@ -234,7 +246,8 @@ def generate_output_coords_and_kernel_map(input_sparse_tensor: Voxels, kernel_si
             out_coords = out_coords.to(torch.int32)
         out_offsets = output_spatially_sparse_tensor.offsets
     elif any(s != 1 for s in stride):
-        out_coords, out_offsets = stride_coords(in_coords, stride, in_offsets=input_sparse_tensor.offsets)
+        down = strided_coordinates(input_sparse_tensor.batched_coordinates, stride)
+        out_coords, out_offsets = down.batch_indexed_coordinates, down.offsets
     else:
         out_coords, out_offsets = in_coords, input_sparse_tensor.offsets
 
@@ -271,6 +284,42 @@ def generate_output_coords_and_kernel_map(input_sparse_tensor: Voxels, kernel_si
         input_sparse_tensor._extra_attributes["_cache"] = IntSearchCache()
     input_sparse_tensor.cache.put(key, kernel_map)
     return out_coords, out_offsets, kernel_map
+
+
+def strided_coordinates(coords: IntCoords, stride: Tuple[int, ...]) -> IntCoords:
+    """The distinct rows of ``floor(coords / stride)`` as an ``IntCoords`` that already knows its
+    batch-indexed form.  Computed once per (coordinate set, stride) and kept with the
+    coordinate set, so that every layer striding the same coordinates shares one result and
+    :func:`prefetch_strided_coordinates` can compute a whole pyramid ahead of the features."""
+    stride = tuple(int(s) for s in stride)
+    key = ("strided", stride)
+    hit = coords._shared.get(key)
+    if hit is None:
+        bc = coords.batch_indexed_coordinates
+        if bc.dtype != torch.int32:
+            bc = bc.to(torch.int32)
+        out_coords, out_offsets = stride_coords(bc, stride, in_offsets=coords.offsets)
+        hit = IntCoords(out_coords[:, 1:], offsets=out_offsets)
+        hit._bcoords = out_coords
+        coords._shared[key] = hit
+    return hit
+
+
+def prefetch_strided_coordinates(voxels: Voxels, strides) -> List[IntCoords]:
+    """Compute the coordinate pyramid ``voxels -> /strides[0] -> /strides[1] ...`` now.
+
+    Sizing each strided coordinate set costs one host synchronisation.  Done lazily inside the
+    strided convolutions, each of those waits for every feature kernel queued before it; done
+    here, before the first convolution is queued, the waits only cover the small coordinate
+    kernels and the whole network can then be queued without the host ever waiting.  (An
+    addition to the reference surface; results are identical with or without the call.)"""
+    nd = voxels.num_spatial_dims
+    level = voxels.batched_coordinates
+    out = []
+    for s in strides:
+        level = strided_coordinates(level, ntuple(s, ndim=nd))
+        out.append(level)
+    return out
 
 
 def _cached_table(voxels: Optional[Voxels], coords: Tensor):
@@ -366,7 +415,7 @@ def spatially_sparse_conv(
     feats = input_sparse_tensor.feature_tensor
     needs_grad = torch.is_grad_enabled() and (feats.requires_grad or weight.requires_grad)
 
-    if np.prod(_kernel_size) == 1 and np.prod(_stride) == 1:
+    if all(k == 1 for k in _kernel_size) and all(s == 1 for s in _stride):
         if epilogue is None:
             out = feats @ weight[0].to(feats.dtype) if weight.dtype != feats.dtype else feats @ weight[0]
             if bias is not None:
@@ -430,8 +479,11 @@ def spatially_sparse_conv(
     elif all(s == 1 for s in _stride) and order == POINT_ORDERING.RANDOM:
         src = input_sparse_tensor.batched_coordinates
         out_ic = IntCoords(src.batched_tensor, offsets=src.offsets).share_derived(src)
+    elif order == POINT_ORDERING.RANDOM:
+        src = strided_coordinates(input_sparse_tensor.batched_coordinates, _stride)
+        out_ic = IntCoords(src.batched_tensor, offsets=src.offsets).share_derived(src)
     else:
-        out_ic = IntCoords(out_coords[:, 1:], offsets=out_offsets.cpu().int())
+        out_ic = IntCoords(out_coords[:, 1:], offsets=out_offsets if out_offsets.device.type == "cpu" else out_offsets.cpu())
         out_ic._bcoords = out_coords
     return input_sparse_tensor.replace(batched_coordinates=out_ic, batched_features=out,
                                        tensor_stride=out_tensor_stride)
