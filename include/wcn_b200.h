@@ -177,6 +177,20 @@ int wcn_nbr_from_maps(const int32_t* in_maps, const int32_t* out_maps, const int
 int wcn_nbr_transpose(const int32_t* nbr_fwd, int32_t num_offsets, int64_t num_out, int64_t num_in,
                       int32_t* nbr_t, void* stream);
 
+/* Tile order of a neighbour table: within each window of 4096 consecutive output rows the
+ * rows are sorted by their neighbour-presence mask (bit k set when nbr[k][m] >= 0; ties by
+ * row), so that rows with the same present offsets share a 128-row tile and the convolution
+ * skips the (tile, offset) pairs that have no neighbour at all.
+ *   out_rows[s]        the output row that slot s of the tiled table stands for (a permutation
+ *                      of 0..num_out-1 that moves no row out of its window)
+ *   nbr_tiled[k][s]    = nbr[k][out_rows[s]]
+ * Pass both to wcn_conv_fwd (nbr = nbr_tiled, out_rows = out_rows); the results are bit
+ * identical to the untiled call.  num_offsets <= 32.  Deterministic.
+ * No reference counterpart: the reference's implicit GEMM walks per-offset pair lists
+ * (warpconvnet/nn/functional/sparse_conv.py:300-310) and never forms output tiles. */
+int wcn_kmap_tile_order(const int32_t* nbr, int64_t num_out, int32_t num_offsets, int32_t* out_rows,
+                        int32_t* nbr_tiled, void* stream);
+
 /* ------------------------------------------------------------------ Morton code */
 
 /* codes[i] = 3-D Morton code of (x - min_xyz[0], y - min_xyz[1], z - min_xyz[2]), x in bit
@@ -213,7 +227,9 @@ int wcn_conv_pack_weight(int algo, const void* weight, int32_t num_offsets, int3
                          int32_t c_out, int dtype, void* packed, void* stream);
 
 /* Output-stationary sparse convolution with a fused epilogue:
- *   acc[m, :] = sum_k feats[nbr[k*M + m], :] @ weight[k]      (rows with nbr < 0 skipped, fp32 accumulation)
+ *   acc[s, :] = sum_k feats[nbr[k*M + s], :] @ weight[k]      (rows with nbr < 0 skipped, fp32 accumulation)
+ *   m = out_rows[s]           (out_rows NULL: m = s; else a permutation of 0..M-1, see
+ *                              wcn_kmap_tile_order, with nbr being that call's nbr_tiled)
  *   y = acc * scale + shift   (scale NULL: y = acc + shift; both NULL: y = acc)
  *   y += residual[m, :]       (residual NULL: skipped; residual has the output dtype)
  *   y = max(y, 0)             (relu != 0)
@@ -230,8 +246,8 @@ int wcn_conv_pack_weight(int algo, const void* weight, int32_t num_offsets, int3
  * the bias add (sparse_conv.py:1794-1795) and the BatchNorm1d / ReLU / residual-add chain of
  * the model blocks (examples/mink_unet.py:36-47, 129-141). */
 int wcn_conv_fwd(int algo, const void* feats, int64_t num_in, const void* weight,
-                 const void* packed_weight, const int32_t* nbr, int64_t num_out,
-                 int32_t num_offsets, int32_t c_in, int32_t c_out, int dtype, const float* scale,
+                 const void* packed_weight, const int32_t* nbr, const int32_t* out_rows,
+                 int64_t num_out, int32_t num_offsets, int32_t c_in, int32_t c_out, int dtype, const float* scale,
                  const float* shift, const void* residual, int relu, void* out, int out_dtype,
                  int32_t* dev_status, void* stream);
 

@@ -271,6 +271,24 @@ def canonical_kernel_map(in_maps, out_maps, offsets, in_coords=None, out_coords=
     return ci, co, offsets
 
 
+
+def tile_order(found: np.ndarray, window: int = 4096) -> Tuple[np.ndarray, np.ndarray]:
+    """Row order used by the product's tiled neighbour table (its own layout, no reference
+    counterpart): inside each window of ``window`` consecutive output rows, rows sorted by
+    the presence mask ``sum_k (found[k, m] >= 0) << k``, ties by row.  Returns
+    ``(out_rows[M], found[:, out_rows])``."""
+    found = np.asarray(found)
+    K, M = found.shape
+    mask = np.zeros(M, dtype=np.uint64)
+    for k in range(K):
+        mask |= (found[k] >= 0).astype(np.uint64) << np.uint64(k)
+    rows = np.arange(M, dtype=np.int64)
+    for s in range(0, M, window):
+        e = min(M, s + window)
+        rows[s:e] = s + np.argsort(mask[s:e], kind="stable")
+    return rows.astype(np.int32), found[:, rows]
+
+
 def canonical_coords(coords: np.ndarray) -> np.ndarray:
     """Rows sorted lexicographically by (b, x, y, z)."""
     coords = np.asarray(coords)

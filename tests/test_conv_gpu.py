@@ -8,7 +8,7 @@ import torch.nn as nn
 from oracle import kernel_map as km
 from oracle import sparse_conv as osc
 from warpconvnet_b200 import (SPARSE_CONV_FWD_ALGO_MODE as ALGO, ConvEpilogue, IntSearchResult, Sequential,
-                              SparseConv3d, Voxels, generate_kernel_map, spatially_sparse_conv)
+                              SparseConv3d, Voxels, generate_kernel_map, spatially_sparse_conv, stride_coords)
 from warpconvnet_b200._native import CONV_SIMT, CONV_TCGEN05, check_device_status
 from warpconvnet_b200.datasets import synthetic
 from warpconvnet_b200.examples.mink_unet import MinkUNet18, randomize_batchnorm_
@@ -135,6 +135,34 @@ def test_tcgen05_large_problem(c_in, c_out, n):
         assert rel_l2(y[rows].float().cpu().numpy(), ref) < 1e-2
     y2 = sparse_conv_fused(xq.to(DEV), wq.to(DEV), kmap, n, epilogue=ep, algo=CONV_TCGEN05)
     assert torch.equal(y, y2)
+
+
+@pytest.mark.parametrize("dtype,algo,c_in,c_out", [(torch.float16, CONV_TCGEN05, 96, 96),
+                                                   (torch.bfloat16, CONV_TCGEN05, 64, 128),
+                                                   (torch.float32, CONV_SIMT, 24, 40)])
+def test_tile_order_is_bit_identical(dtype, algo, c_in, c_out):
+    """Running the output rows in tile order (grouped by neighbour pattern) changes which
+    (tile, offset) pairs are computed, not one bit of the result: 3x3x3, 2x2x2 stride 2 and
+    its transposed map, epilogue with residual on."""
+    n = 50000
+    coords, x, w = _layer_case(n, c_in, c_out, 77, "raster_crop")
+    coords = np.ascontiguousarray(coords[np.argsort(km.morton_code(coords[:, 1:]), kind="stable")])
+    c = torch.from_numpy(coords).to(DEV)
+    coarse, _ = stride_coords(c, (2, 2, 2))
+    g = torch.Generator().manual_seed(9)
+    down = generate_kernel_map(c, coarse, (2, 2, 2), (2, 2, 2))
+    cases = [(generate_kernel_map(c, c, (1, 1, 1), (3, 3, 3)), n, n, 27),
+             (down, n, len(coarse), 8), (down.swapped(num_in=n), len(coarse), n, 8)]
+    for kmap, n_in, n_out, K in cases:
+        xin = torch.randn(n_in, c_in, generator=g).to(dtype).to(DEV)
+        wk = (torch.randn(K, c_in, c_out, generator=g) * 0.1).to(dtype).to(DEV)
+        ep = ConvEpilogue(scale=(torch.rand(c_out, generator=g) + 0.5).to(DEV),
+                          shift=torch.randn(c_out, generator=g).to(DEV),
+                          residual=torch.randn(n_out, c_out, generator=g).to(dtype).to(DEV), relu=True)
+        a = sparse_conv_fused(xin, wk, kmap, n_out, epilogue=ep, algo=algo, tile_order=False)
+        b = sparse_conv_fused(xin, wk, kmap, n_out, epilogue=ep, algo=algo, tile_order=True)
+        check_device_status(DEV)
+        assert torch.equal(a, b)
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.float16])

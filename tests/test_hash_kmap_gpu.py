@@ -208,3 +208,30 @@ def test_kernel_map_full_size_properties(mode, n_per_scene):
     up = down.swapped(num_in=n)
     assert int((up.neighbor_table(n) >= 0).sum(0).min()) == 1 and int((up.neighbor_table(n) >= 0).sum(0).max()) == 1
     check_device_status(DEV)
+
+
+@pytest.mark.parametrize("n,ksize,stride", [(30000, (3, 3, 3), (1, 1, 1)), (4096, (3, 3, 3), (1, 1, 1)),
+                                             (5000, (2, 2, 2), (2, 2, 2)), (37, (3, 3, 3), (1, 1, 1))])
+def test_tile_order_matches_oracle(n, ksize, stride):
+    """Tiled neighbour table: rows of each 4096-row window sorted by presence mask, ties by row;
+    bit-exact against the oracle's restatement, for a forward and a transposed (one-hot) map."""
+    coords = synthetic.room_scene(n, 0.02, 41, "raster_crop")
+    coords = np.concatenate([np.zeros((len(coords), 1), np.int32), coords], axis=1).astype(np.int32)
+    coords = np.ascontiguousarray(coords[np.argsort(km.morton_code(coords[:, 1:]), kind="stable")])
+    if stride == (1, 1, 1):
+        out = coords
+    else:
+        out, _ = km.stride_coords(coords, stride)
+    res = generate_kernel_map(dev(coords), dev(out), stride, ksize)
+    cases = [(res, len(out))]
+    if stride != (1, 1, 1):
+        cases.append((res.swapped(num_in=len(coords)), len(coords)))
+    for r, m in cases:
+        nbr = r.neighbor_table(m).cpu().numpy()
+        tiled, rows = r.tiled_neighbor_table(m)
+        want_rows, want_tiled = km.tile_order(nbr)
+        assert np.array_equal(rows.cpu().numpy(), want_rows)
+        assert np.array_equal(tiled.cpu().numpy(), want_tiled)
+        assert np.array_equal(np.sort(want_rows), np.arange(m))
+        assert np.array_equal(want_rows // 4096, np.arange(m) // 4096)  # no row leaves its window
+    check_device_status(DEV)

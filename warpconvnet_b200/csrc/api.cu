@@ -3,14 +3,16 @@
 #include "wcn_common.cuh"
 
 // conv_simt.cu
-int wcn_conv_simt_fwd(const void* feats, const void* weight, const int32_t* nbr, int64_t M, int K, int c_in,
+int wcn_conv_simt_fwd(const void* feats, const void* weight, const int32_t* nbr, const int32_t* out_rows,
+                      int64_t M, int K, int c_in,
                       int c_out, int dtype, const float* scale, const float* shift, const void* residual,
                       int relu, void* out, int out_dtype, cudaStream_t st);
 // conv_tcgen05.cu
 bool wcn_conv_tcgen05_supported(int K, int c_in, int c_out, int dtype, int out_dtype);
 int64_t wcn_conv_tcgen05_packed_bytes(int K, int c_in, int c_out);
 int wcn_conv_tcgen05_pack(const void* weight, int K, int c_in, int c_out, void* packed, cudaStream_t st);
-int wcn_conv_tcgen05_fwd(const void* feats, int64_t num_in, const void* packed, const int32_t* nbr, int64_t M, int K, int c_in,
+int wcn_conv_tcgen05_fwd(const void* feats, int64_t num_in, const void* packed, const int32_t* nbr,
+                         const int32_t* out_rows, int64_t M, int K, int c_in,
                          int c_out, int dtype, const float* scale, const float* shift, const void* residual,
                          int relu, void* out, int out_dtype, int32_t* dev_status, cudaStream_t st);
 
@@ -52,7 +54,8 @@ extern "C" int wcn_conv_pack_weight(int algo, const void* weight, int32_t num_of
 }
 
 extern "C" int wcn_conv_fwd(int algo, const void* feats, int64_t num_in, const void* weight,
-                            const void* packed_weight, const int32_t* nbr, int64_t num_out,
+                            const void* packed_weight, const int32_t* nbr, const int32_t* out_rows,
+                            int64_t num_out,
                             int32_t num_offsets, int32_t c_in, int32_t c_out, int dtype, const float* scale,
                             const float* shift, const void* residual, int relu, void* out, int out_dtype,
                             int32_t* dev_status, void* stream) {
@@ -65,11 +68,11 @@ extern "C" int wcn_conv_fwd(int algo, const void* feats, int64_t num_in, const v
   const bool tc_ok = wcn_conv_tcgen05_supported(num_offsets, c_in, c_out, dtype, out_dtype);
   if (algo == WCN_CONV_TCGEN05 || (algo == WCN_CONV_AUTO && tc_ok && packed_weight && dev_status && num_in > 0)) {
     if (!tc_ok) return WCN_ERR_UNSUPPORTED_CONFIG;
-    return wcn_conv_tcgen05_fwd(feats, num_in, packed_weight, nbr, num_out, num_offsets, c_in, c_out, dtype, scale, shift,
+    return wcn_conv_tcgen05_fwd(feats, num_in, packed_weight, nbr, out_rows, num_out, num_offsets, c_in, c_out, dtype, scale, shift,
                                 residual, relu, out, out_dtype, dev_status, st);
   }
   if (algo != WCN_CONV_SIMT && algo != WCN_CONV_AUTO) return WCN_ERR_INVALID_PARAMETERS;
   if (!weight) return WCN_ERR_INVALID_PARAMETERS;
-  return wcn_conv_simt_fwd(feats, weight, nbr, num_out, num_offsets, c_in, c_out, dtype, scale, shift, residual,
+  return wcn_conv_simt_fwd(feats, weight, nbr, out_rows, num_out, num_offsets, c_in, c_out, dtype, scale, shift, residual,
                            relu, out, out_dtype, st);
 }

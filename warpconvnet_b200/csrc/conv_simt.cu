@@ -16,7 +16,7 @@ constexpr int NT = 256;  // threads: 16 x 16, each a 4 x 4 micro-tile
 template <typename T, typename TO>
 __global__ void __launch_bounds__(NT)
 conv_simt_kernel(const T* __restrict__ feats, const T* __restrict__ weight, const int32_t* __restrict__ nbr,
-                 int64_t M, int K, int c_in, int c_out, const float* __restrict__ scale,
+                 const int32_t* __restrict__ out_rows, int64_t M, int K, int c_in, int c_out, const float* __restrict__ scale,
                  const float* __restrict__ shift, const TO* __restrict__ residual, int relu,
                  TO* __restrict__ out) {
   __shared__ float As[TK][TM + 4];
@@ -75,8 +75,9 @@ conv_simt_kernel(const T* __restrict__ feats, const T* __restrict__ weight, cons
 
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    const int64_t m = m0 + ty * 4 + i;
-    if (m >= M) continue;
+    const int64_t slot = m0 + ty * 4 + i;
+    if (slot >= M) continue;
+    const int64_t m = out_rows ? (int64_t)__ldg(&out_rows[slot]) : slot;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const int n = n0 + tx * 4 + j;
@@ -92,23 +93,24 @@ conv_simt_kernel(const T* __restrict__ feats, const T* __restrict__ weight, cons
 }
 
 template <typename T, typename TO>
-int launch_simt(const void* feats, const void* weight, const int32_t* nbr, int64_t M, int K, int c_in,
+int launch_simt(const void* feats, const void* weight, const int32_t* nbr, const int32_t* out_rows, int64_t M, int K, int c_in,
                 int c_out, const float* scale, const float* shift, const void* residual, int relu, void* out,
                 cudaStream_t st) {
   dim3 grid((unsigned)((M + TM - 1) / TM), (unsigned)((c_out + TN - 1) / TN));
-  conv_simt_kernel<T, TO><<<grid, NT, 0, st>>>((const T*)feats, (const T*)weight, nbr, M, K, c_in, c_out, scale,
+  conv_simt_kernel<T, TO><<<grid, NT, 0, st>>>((const T*)feats, (const T*)weight, nbr, out_rows, M, K, c_in, c_out, scale,
                                               shift, (const TO*)residual, relu, (TO*)out);
   return cudaGetLastError() == cudaSuccess ? WCN_OK : WCN_ERR_EXECUTION;
 }
 
 }  // namespace
 
-int wcn_conv_simt_fwd(const void* feats, const void* weight, const int32_t* nbr, int64_t M, int K, int c_in,
+int wcn_conv_simt_fwd(const void* feats, const void* weight, const int32_t* nbr, const int32_t* out_rows,
+                      int64_t M, int K, int c_in,
                       int c_out, int dtype, const float* scale, const float* shift, const void* residual,
                       int relu, void* out, int out_dtype, cudaStream_t st) {
 #define WCN_SIMT_CASE(DT, T, ODT, TO) \
   if (dtype == DT && out_dtype == ODT) \
-    return launch_simt<T, TO>(feats, weight, nbr, M, K, c_in, c_out, scale, shift, residual, relu, out, st);
+    return launch_simt<T, TO>(feats, weight, nbr, out_rows, M, K, c_in, c_out, scale, shift, residual, relu, out, st);
   WCN_SIMT_CASE(WCN_F32, float, WCN_F32, float)
   WCN_SIMT_CASE(WCN_F16, __half, WCN_F16, __half)
   WCN_SIMT_CASE(WCN_BF16, __nv_bfloat16, WCN_BF16, __nv_bfloat16)

@@ -59,6 +59,7 @@ struct ConvTcParams {
   const char* feats;
   const char* wpacked;
   const int32_t* nbr;
+  const int32_t* out_rows;  // slot -> output row, or null for the identity
   int64_t M, num_in;
   int K, c_in, c_out;
   const float* scale;
@@ -527,8 +528,10 @@ conv_tcgen05_kernel(const ConvTcParams p) {
       const int64_t m0 = st * G * BLOCK_M;
       for (int g = 0; g < G; ++g) {
         const uint32_t gmask = ctl->info_mask[ib][g];
-        const int64_t m = m0 + (int64_t)g * BLOCK_M + tid;
+        const int64_t slot = m0 + (int64_t)g * BLOCK_M + tid;
         if (m0 + (int64_t)g * BLOCK_M >= p.M) break;
+        // rows past the end keep m >= M and are never stored
+        const int64_t m = (p.out_rows && slot < p.M) ? (int64_t)__ldg(&p.out_rows[slot]) : slot;
         const uint32_t trow = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)((ab * G + g) * p.cols);
         TO* orow = reinterpret_cast<TO*>(p.out) + m * p.c_out + n0;
         const TO* rrow = p.residual ? reinterpret_cast<const TO*>(p.residual) + m * p.c_out + n0 : nullptr;
@@ -732,7 +735,8 @@ int wcn_conv_tcgen05_pack(const void* weight, int K, int c_in, int c_out, void* 
   return cudaGetLastError() == cudaSuccess ? WCN_OK : WCN_ERR_EXECUTION;
 }
 
-int wcn_conv_tcgen05_fwd(const void* feats, int64_t num_in, const void* packed, const int32_t* nbr, int64_t M, int K, int c_in,
+int wcn_conv_tcgen05_fwd(const void* feats, int64_t num_in, const void* packed, const int32_t* nbr,
+                         const int32_t* out_rows, int64_t M, int K, int c_in,
                          int c_out, int dtype, const float* scale, const float* shift, const void* residual,
                          int relu, void* out, int out_dtype, int32_t* dev_status, cudaStream_t st) {
   if (!wcn_conv_tcgen05_supported(K, c_in, c_out, dtype, out_dtype)) return WCN_ERR_UNSUPPORTED_CONFIG;
@@ -741,7 +745,7 @@ int wcn_conv_tcgen05_fwd(const void* feats, int64_t num_in, const void* packed, 
       (reinterpret_cast<uintptr_t>(out) & 15) || (reinterpret_cast<uintptr_t>(residual) & 15))
     return WCN_ERR_INVALID_PARAMETERS;
   ConvTcParams p;
-  p.feats = (const char*)feats; p.wpacked = (const char*)packed; p.nbr = nbr;
+  p.feats = (const char*)feats; p.wpacked = (const char*)packed; p.nbr = nbr; p.out_rows = out_rows;
   p.M = M; p.num_in = num_in; p.K = K; p.c_in = c_in; p.c_out = c_out;
   p.scale = scale; p.shift = shift; p.residual = residual; p.relu = relu; p.out = out;
   p.dev_status = dev_status;

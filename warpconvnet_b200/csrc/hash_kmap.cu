@@ -283,6 +283,55 @@ __global__ void nbr_transpose_kernel(const int32_t* __restrict__ nbr_fwd, int64_
   if (v >= 0 && v < N) nbr_t[(int64_t)k * N + v] = (int32_t)m;
 }
 
+// ------------------------------------------------------------------ tile order
+
+// Rows of one window of kTileWindow consecutive output rows are reordered by their
+// neighbour-presence mask (bit k = offset k has a neighbour), ties by row.  Rows with the
+// same set of present offsets become adjacent, so a 128-row tile of the reordered table has
+// far fewer offsets with any neighbour than a tile of consecutive rows, and the convolution
+// skips a (tile, offset) pair that has none.  The window bounds how far a row moves, which
+// keeps the gather footprint of a tile local.
+constexpr int kTileWindow = 4096;
+constexpr int kTileOrderThreads = 1024;
+
+__global__ void __launch_bounds__(kTileOrderThreads)
+kmap_tile_order_kernel(const int32_t* __restrict__ nbr, int64_t M, int K, int32_t* __restrict__ out_rows,
+                       int32_t* __restrict__ nbr_tiled) {
+  __shared__ unsigned long long keys[kTileWindow];
+  const int64_t base = (int64_t)blockIdx.x * kTileWindow;
+  const int n = (int)min((int64_t)kTileWindow, M - base);
+  for (int i = threadIdx.x; i < kTileWindow; i += kTileOrderThreads) {
+    unsigned long long key = ~0ull;
+    if (i < n) {
+      unsigned mask = 0;
+      for (int k = 0; k < K; ++k) mask |= (unsigned)(__ldg(&nbr[(int64_t)k * M + base + i]) >= 0) << k;
+      key = ((unsigned long long)mask << 12) | (unsigned)i;
+    }
+    keys[i] = key;
+  }
+  __syncthreads();
+  // bitonic sort, ascending; keys are distinct (the low 12 bits are the row)
+  for (int size = 2; size <= kTileWindow; size <<= 1) {
+    for (int stride = size >> 1; stride > 0; stride >>= 1) {
+      for (int t = threadIdx.x; t < kTileWindow / 2; t += kTileOrderThreads) {
+        const int lo = 2 * t - (t & (stride - 1));
+        const int hi = lo + stride;
+        const bool up = (lo & size) == 0;
+        const unsigned long long a = keys[lo], b = keys[hi];
+        if ((a > b) == up) { keys[lo] = b; keys[hi] = a; }
+      }
+      __syncthreads();
+    }
+  }
+  for (int i = threadIdx.x; i < n; i += kTileOrderThreads)
+    out_rows[base + i] = (int32_t)(base + (int64_t)(keys[i] & 4095ull));
+  for (int k = 0; k < K; ++k) {
+    const int32_t* src = nbr + (int64_t)k * M + base;
+    int32_t* dst = nbr_tiled + (int64_t)k * M + base;
+    for (int i = threadIdx.x; i < n; i += kTileOrderThreads) dst[i] = __ldg(&src[keys[i] & 4095ull]);
+  }
+}
+
 // ------------------------------------------------------------------ Morton
 
 __device__ __forceinline__ unsigned long long spread3(unsigned long long n) {
@@ -552,6 +601,18 @@ extern "C" int wcn_nbr_transpose(const int32_t* nbr_fwd, int32_t num_offsets, in
     dim3 grid(grid_for(num_out), (unsigned)num_offsets);
     nbr_transpose_kernel<<<grid, kThreads, 0, st>>>(nbr_fwd, num_out, num_in, nbr_t);
   }
+  WCN_CHECK_LAUNCH();
+  return WCN_OK;
+}
+
+extern "C" int wcn_kmap_tile_order(const int32_t* nbr, int64_t num_out, int32_t num_offsets, int32_t* out_rows,
+                                   int32_t* nbr_tiled, void* stream) {
+  if (num_offsets <= 0 || num_offsets > 32 || num_out < 0 || num_out >= 0x7FFFFFFFll) return WCN_ERR_INVALID_PARAMETERS;
+  if (num_out == 0) return WCN_OK;
+  if (!nbr || !out_rows || !nbr_tiled || nbr == nbr_tiled) return WCN_ERR_INVALID_PARAMETERS;
+  const unsigned blocks = (unsigned)((num_out + kTileWindow - 1) / kTileWindow);
+  kmap_tile_order_kernel<<<blocks, kTileOrderThreads, 0, wcn_stream(stream)>>>(nbr, num_out, num_offsets, out_rows,
+                                                                              nbr_tiled);
   WCN_CHECK_LAUNCH();
   return WCN_OK;
 }

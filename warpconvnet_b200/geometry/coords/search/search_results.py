@@ -36,6 +36,7 @@ class IntSearchResult:
         self._num_in = None
         self._workspace = None    # per-block hit counts of the dense form
         self._forward = None
+        self._tiled = None        # (nbr_tiled [K, M], out_rows [M]) of tiled_neighbor_table
         self._num_offsets = len(self._offsets) - 1
 
     # -- dense construction (used by generate_kernel_map)
@@ -50,6 +51,7 @@ class IntSearchResult:
         self._num_in = int(num_in)
         self._workspace = workspace
         self._forward = None      # set on transposed views: the map this one was swapped from
+        self._tiled = None
         return self
 
     def _compact(self):
@@ -105,6 +107,24 @@ class IntSearchResult:
               "wcn_nbr_from_maps")
         self._nbr, self._num_out = nbr, num_out
         return nbr
+
+    def tiled_neighbor_table(self, num_out: int) -> Tuple[Tensor, Tensor]:
+        """``(nbr_tiled[K, num_out], out_rows[num_out])``: the neighbour table with the output
+        rows of every 4096-row window grouped by which offsets have a neighbour, and the output
+        row each slot stands for.  A 128-row tile of it has far fewer offsets with any
+        neighbour than a tile of consecutive rows (12 instead of 18.5 of 27 on a 2 cm room
+        scan), and the convolution kernels skip the empty ones.  Built once per map, so every
+        layer that shares the map shares the order."""
+        if self._tiled is None:
+            nbr = self.neighbor_table(num_out)
+            dev = nbr.device
+            tiled = torch.empty_like(nbr)
+            rows = torch.empty(num_out, dtype=torch.int32, device=dev)
+            check(lib().wcn_kmap_tile_order(ptr(nbr), num_out, self._num_offsets, ptr(rows), ptr(tiled),
+                                            stream_ptr(dev)), "wcn_kmap_tile_order")
+            self._tiled = (tiled, rows)
+        assert self._tiled[0].shape[1] == num_out
+        return self._tiled
 
     def swapped(self, num_in: Optional[int] = None) -> "IntSearchResult":
         """The map with inputs and outputs exchanged (transposed convolution,

@@ -167,11 +167,17 @@ def _as_f32_on(t: Optional[Tensor], dev: torch.device) -> Optional[Tensor]:
     return t if t.is_contiguous() else t.contiguous()
 
 
+# Kernel maps with at least this many output rows (and 2..32 offsets) are run in tile order.
+TILE_ORDER_MIN_ROWS = 1024
+
+
 def sparse_conv_fused(in_features: Tensor, weight: Tensor, kernel_map: IntSearchResult, num_out_coords: int,
                       epilogue: Optional[ConvEpilogue] = None, out_dtype: Optional[torch.dtype] = None,
-                      algo: int = CONV_AUTO) -> Tensor:
+                      algo: int = CONV_AUTO, tile_order: Optional[bool] = None) -> Tensor:
     """One launch: all kernel offsets + epilogue.  The weight is used in the
-    feature dtype (fp32, fp16 or bf16); accumulation is fp32."""
+    feature dtype (fp32, fp16 or bf16); accumulation is fp32.  ``tile_order`` runs the
+    output rows grouped by neighbour pattern (``IntSearchResult.tiled_neighbor_table``;
+    same numbers, fewer (tile, offset) pairs to compute); None = by size."""
     require_cuda(in_features, "in_features")
     x = in_features if in_features.is_contiguous() else in_features.contiguous()
     w, packed = _prepared_weight(weight, x.dtype, algo)
@@ -182,7 +188,12 @@ def sparse_conv_fused(in_features: Tensor, weight: Tensor, kernel_map: IntSearch
     out = torch.empty((num_out_coords, c_out), dtype=out_dtype, device=dev)
     if num_out_coords == 0:
         return out
-    nbr = kernel_map.neighbor_table(num_out_coords)
+    if tile_order is None:
+        tile_order = 1 < K <= 32 and num_out_coords >= TILE_ORDER_MIN_ROWS
+    if tile_order:
+        nbr, out_rows = kernel_map.tiled_neighbor_table(num_out_coords)
+    else:
+        nbr, out_rows = kernel_map.neighbor_table(num_out_coords), None
     assert nbr.shape[0] == K, f"kernel map has {nbr.shape[0]} offsets, weight has {K}"
     ep = epilogue or ConvEpilogue()
     scale = _as_f32_on(ep.scale, dev)
@@ -193,7 +204,8 @@ def sparse_conv_fused(in_features: Tensor, weight: Tensor, kernel_map: IntSearch
         if not residual.is_contiguous():
             residual = residual.contiguous()
         assert residual.shape == out.shape, f"residual {tuple(residual.shape)} != output {tuple(out.shape)}"
-    check(lib().wcn_conv_fwd(algo, ptr(x), x.shape[0], ptr(w), ptr(packed), ptr(nbr), num_out_coords, K, c_in,
+    check(lib().wcn_conv_fwd(algo, ptr(x), x.shape[0], ptr(w), ptr(packed), ptr(nbr), ptr(out_rows),
+                             num_out_coords, K, c_in,
                              c_out, dtype_code(x.dtype), ptr(scale), ptr(shift), ptr(residual), int(ep.relu),
                              ptr(out), dtype_code(out_dtype), ptr(device_status(dev)), stream_ptr(dev)),
           "wcn_conv_fwd")
