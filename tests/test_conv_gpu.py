@@ -110,7 +110,7 @@ def _oracle_rows(coords, xq, wq, rows):
 
 
 @pytest.mark.parametrize("c_in,c_out,n", [(32, 32, 200000), (64, 64, 200000), (96, 96, 160000), (128, 128, 120000),
-                                          (256, 256, 100000), (64, 128, 40000)])
+                                          (256, 256, 100000), (64, 128, 40000), (128, 96, 300000)])
 def test_tcgen05_large_problem(c_in, c_out, n):
     """Sizes at which the kernel runs several 128-row sub-tiles per CTA pass and double-buffered
     accumulators: tensor-core kernel == FP32-pipe kernel everywhere, == oracle on row samples,

@@ -257,6 +257,7 @@ struct Control {
   uint32_t mask_acc[2][MAX_G];    // index warps' scratch while building the masks
   uint32_t tmem_holder;
   int skip;
+  float sc[256], sh[256];         // this CTA's columns of the epilogue scale / shift (1 / 0 when absent)
 };
 
 // ------------------------------------------------------------------ kernel
@@ -294,7 +295,7 @@ conv_tcgen05_kernel(const ConvTcParams p) {
   if (ctl->skip != 0) return;
 
   if (tid == 0) {
-    for (int s = 0; s < p.sa; ++s) { mbar_init(bar(&ctl->a_full[s]), GATHER_THREADS); mbar_init(bar(&ctl->a_empty[s]), 1); }
+    for (int s = 0; s < p.sa; ++s) { mbar_init(bar(&ctl->a_full[s]), GATHER_THREADS); mbar_init(bar(&ctl->a_empty[s]), MMA_ISSUERS); }
     for (int s = 0; s < p.sb; ++s) { mbar_init(bar(&ctl->b_full[s]), 1); mbar_init(bar(&ctl->b_empty[s]), MMA_ISSUERS); }
     for (int i = 0; i < 2; ++i) {
       mbar_init(bar(&ctl->acc_full[i]), MMA_ISSUERS);
@@ -305,6 +306,10 @@ conv_tcgen05_kernel(const ConvTcParams p) {
     mbar_init(bar(&ctl->idx_sync), IDX_THREADS);
     for (int g = 0; g < MAX_G; ++g) ctl->mask_acc[0][g] = ctl->mask_acc[1][g] = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  for (int i = tid; i < BN; i += THREADS) {
+    ctl->sc[i] = p.scale ? __ldg(&p.scale[n0 + i]) : 1.f;
+    ctl->sh[i] = p.shift ? __ldg(&p.shift[n0 + i]) : 0.f;
   }
   const uint32_t tmem_total = (uint32_t)(NBUF * G * p.cols);
   if (warp == MMA_WARP) tmem_alloc(smem_u32(&ctl->tmem_holder), tmem_total < 32 ? 32u : tmem_total);
@@ -442,8 +447,8 @@ conv_tcgen05_kernel(const ConvTcParams p) {
   } else if (warp >= MMA_WARP && warp < MMA_WARP + MMA_ISSUERS) {
     // ================================================================ MMA issuers
     // Two threads share the issue work: issuer w takes the sub-tiles with (g & 1) == w.  Both
-    // walk the same slot sequence (skipping the other's row slots), both release every weight
-    // slot and both sign off the accumulator set.
+    // walk the same slot sequence, both observe and release every row slot and every weight
+    // slot, and both sign off the accumulator set.
     const uint32_t issuer = (uint32_t)(warp - MMA_WARP);
     if (lane == 0) {
       const uint32_t idesc = (1u << 4) | ((BF16 ? 1u : 0u) << 7) | ((BF16 ? 1u : 0u) << 10) |
@@ -458,6 +463,8 @@ conv_tcgen05_kernel(const ConvTcParams p) {
         const uint32_t mk0 = ctl->info_mask[ib][0], mk1 = ctl->info_mask[ib][1];
         const uint32_t mk2 = ctl->info_mask[ib][2], mk3 = ctl->info_mask[ib][3];
         const uint32_t uni = mk0 | mk1 | mk2 | mk3;
+        mbar_arrive(bar(&ctl->info_empty[ib]));  // only the masks were needed
+        if (++ib == 2) { ib = 0; iphase ^= 1; }
         // the accumulator set must have been read out by the epilogue of its previous use
         WCN_T0(t_acce);
         if (!mbar_wait(bar(&ctl->acc_empty[ab]), aphase ^ 1, p.dev_status)) { ok = false; break; }
@@ -476,13 +483,17 @@ conv_tcgen05_kernel(const ConvTcParams p) {
             const uint32_t b_slot = b_base + rb.slot * B_SLOT;
             for (uint32_t gb = gbits; gb; gb &= gb - 1) {
               const int g = __ffs(gb) - 1;
-              if (((uint32_t)g & 1u) != issuer) {  // the other issuer's slot
-                ra.advance();
-                continue;
-              }
+              // Both issuers pass every row slot in step: a parity wait is only meaningful for a
+              // thread that is never a whole ring lap away from the slot, so the issuer that does
+              // not consume a slot still observes its fill and signs it off.
               WCN_T0(t_af);
               if (!mbar_wait(bar(&ctl->a_full[ra.slot]), ra.phase, p.dev_status)) { ok = false; break; }
               WCN_ACC(5, t_af, true);
+              if (((uint32_t)g & 1u) != issuer) {  // the other issuer's slot
+                mbar_arrive(bar(&ctl->a_empty[ra.slot]));
+                ra.advance();
+                continue;
+              }
               tc_fence_after();
               const uint32_t a_slot = a_base + ra.slot * A_SLOT;
               const uint32_t d = tmem_base + (uint32_t)((ab * G + g) * p.cols);
@@ -506,8 +517,6 @@ conv_tcgen05_kernel(const ConvTcParams p) {
         }
         if (started && ok) umma_commit(bar(&ctl->acc_full[ab]));  // accumulators of this supertile complete
         else mbar_arrive(bar(&ctl->acc_full[ab]));
-        mbar_arrive(bar(&ctl->info_empty[ib]));
-        if (++ib == 2) { ib = 0; iphase ^= 1; }
         if (++ab == NBUF) { ab = 0; aphase ^= 1; }
       }
       WCN_ACC(7, t_mma, true);
@@ -516,64 +525,94 @@ conv_tcgen05_kernel(const ConvTcParams p) {
   } else {
     // ================================================================ epilogue (warps 0..3)
     int ib = 0, iphase = 0, ab = 0, aphase = 0;
+    const bool affine = p.scale != nullptr || p.shift != nullptr;
+    // One 16-column piece of this thread's row: affine, residual, ReLU, convert, store.
+    auto finish16 = [&](float (&y)[16], int c0, TO* orow, const TO* rrow) {
+      if (affine) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const float4 s4 = *reinterpret_cast<const float4*>(&ctl->sc[c0 + 4 * q]);
+          const float4 h4 = *reinterpret_cast<const float4*>(&ctl->sh[c0 + 4 * q]);
+          y[4 * q + 0] = fmaf(y[4 * q + 0], s4.x, h4.x);
+          y[4 * q + 1] = fmaf(y[4 * q + 1], s4.y, h4.y);
+          y[4 * q + 2] = fmaf(y[4 * q + 2], s4.z, h4.z);
+          y[4 * q + 3] = fmaf(y[4 * q + 3], s4.w, h4.w);
+        }
+      }
+      if (rrow) {
+        float res[16];
+        OutVec<TO>::load(rrow + c0, res);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) y[i] += res[i];
+      }
+      if (p.relu) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) y[i] = fmaxf(y[i], 0.f);
+      }
+      OutVec<TO>::store(orow + c0, y);
+    };
     WCN_T0(t_epi);
     for (int64_t st = blockIdx.x; st < p.supertiles; st += gridDim.x) {
       WCN_T0(t_accf);
       if (ok) ok = mbar_wait(bar(&ctl->info_full[ib]), iphase, p.dev_status, 256);
+      uint32_t gm[MAX_G];
+#pragma unroll
+      for (int g = 0; g < MAX_G; ++g) gm[g] = ok ? ctl->info_mask[ib][g] : 0u;
+      mbar_arrive(bar(&ctl->info_empty[ib]));  // only the masks were needed
+      if (++ib == 2) { ib = 0; iphase ^= 1; }
       if (ok) ok = mbar_wait(bar(&ctl->acc_full[ab]), aphase, p.dev_status, 256);
       WCN_ACC(9, t_accf, tid == 0);
       // tcgen05.ld is warp-collective, so the decision to read must be warp-uniform
       if (!__all_sync(0xFFFFFFFFu, ok)) { ok = false; break; }
       tc_fence_after();
       const int64_t m0 = st * G * BLOCK_M;
-      for (int g = 0; g < G; ++g) {
-        const uint32_t gmask = ctl->info_mask[ib][g];
+#pragma unroll
+      for (int g = 0; g < MAX_G; ++g) {
+        if (g >= G || m0 + (int64_t)g * BLOCK_M >= p.M) break;
+        const uint32_t gmask = gm[g];
         const int64_t slot = m0 + (int64_t)g * BLOCK_M + tid;
-        if (m0 + (int64_t)g * BLOCK_M >= p.M) break;
         // rows past the end keep m >= M and are never stored
         const int64_t m = (p.out_rows && slot < p.M) ? (int64_t)__ldg(&p.out_rows[slot]) : slot;
+        const bool live = slot < p.M;
         const uint32_t trow = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)((ab * G + g) * p.cols);
         TO* orow = reinterpret_cast<TO*>(p.out) + m * p.c_out + n0;
         const TO* rrow = p.residual ? reinterpret_cast<const TO*>(p.residual) + m * p.c_out + n0 : nullptr;
-        for (int c0 = 0; c0 < BN; c0 += 16) {
-          float y[16];
+        int c0 = 0;
+        for (; c0 + 32 <= BN; c0 += 32) {  // two TMEM loads in flight per wait
+          float y0[16], y1[16];
           if (gmask) {
-            uint32_t r[16];
-            tmem_ld16(trow + (uint32_t)c0, r);  // executed by all lanes of the warp
+            uint32_t r0[16], r1[16];
+            tmem_ld16(trow + (uint32_t)c0, r0);  // executed by all lanes of the warp
+            tmem_ld16(trow + (uint32_t)c0 + 16u, r1);
             tmem_ld_wait();
 #pragma unroll
-            for (int i = 0; i < 16; ++i) y[i] = __uint_as_float(r[i]);
+            for (int i = 0; i < 16; ++i) { y0[i] = __uint_as_float(r0[i]); y1[i] = __uint_as_float(r1[i]); }
           } else {
 #pragma unroll
-            for (int i = 0; i < 16; ++i) y[i] = 0.f;
+            for (int i = 0; i < 16; ++i) y0[i] = y1[i] = 0.f;
           }
-          if (m < p.M) {
-            if (p.scale) {
-#pragma unroll
-              for (int i = 0; i < 16; ++i) y[i] *= __ldg(&p.scale[n0 + c0 + i]);
-            }
-            if (p.shift) {
-#pragma unroll
-              for (int i = 0; i < 16; ++i) y[i] += __ldg(&p.shift[n0 + c0 + i]);
-            }
-            if (rrow) {
-              float res[16];
-              OutVec<TO>::load(rrow + c0, res);
-#pragma unroll
-              for (int i = 0; i < 16; ++i) y[i] += res[i];
-            }
-            if (p.relu) {
-#pragma unroll
-              for (int i = 0; i < 16; ++i) y[i] = fmaxf(y[i], 0.f);
-            }
-            OutVec<TO>::store(orow + c0, y);
+          if (live) {
+            finish16(y0, c0, orow, rrow);
+            finish16(y1, c0 + 16, orow, rrow);
           }
+        }
+        if (c0 < BN) {  // BN is a multiple of 16
+          float y0[16];
+          if (gmask) {
+            uint32_t r0[16];
+            tmem_ld16(trow + (uint32_t)c0, r0);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 16; ++i) y0[i] = __uint_as_float(r0[i]);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) y0[i] = 0.f;
+          }
+          if (live) finish16(y0, c0, orow, rrow);
         }
       }
       tc_fence_before();
       mbar_arrive(bar(&ctl->acc_empty[ab]));   // accumulator set may be overwritten
-      mbar_arrive(bar(&ctl->info_empty[ib]));
-      if (++ib == 2) { ib = 0; iphase ^= 1; }
       if (++ab == NBUF) { ab = 0; aphase ^= 1; }
     }
     WCN_ACC(10, t_epi, tid == 0);
@@ -633,7 +672,7 @@ bool plan_launch(ConvTcParams& p, int bk, size_t* smem, dim3* grid) {
   int g = cols >= 128 ? 2 : 4;
   while (g > 1 && ((tiles + g - 1) / g) * split < 2 * (int64_t)sms) g /= 2;
   const size_t a_unit = (size_t)BLOCK_M * bk * 2, b_unit = (size_t)p.block_n * bk * 2;
-  const size_t limit = 224 * 1024;
+  const size_t limit = 226 * 1024;  // the kernels opt in to this much dynamic shared memory
   const int kb_total = p.c_in / bk;
   // Channel slices per ring slot: as many as give a 32 KiB row slot, fewer if the rings would not fit.
   int kbc = (int)((32 * 1024) / a_unit);

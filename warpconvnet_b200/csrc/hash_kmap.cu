@@ -304,7 +304,11 @@ kmap_tile_order_kernel(const int32_t* __restrict__ nbr, int64_t M, int K, int32_
     unsigned long long key = ~0ull;
     if (i < n) {
       unsigned mask = 0;
-      for (int k = 0; k < K; ++k) mask |= (unsigned)(__ldg(&nbr[(int64_t)k * M + base + i]) >= 0) << k;
+      int v[32];  // every load is issued before the first one is consumed
+#pragma unroll
+      for (int k = 0; k < 32; ++k) v[k] = k < K ? __ldg(&nbr[(int64_t)k * M + base + i]) : -1;
+#pragma unroll
+      for (int k = 0; k < 32; ++k) mask |= (unsigned)(v[k] >= 0) << k;
       key = ((unsigned long long)mask << 12) | (unsigned)i;
     }
     keys[i] = key;
@@ -325,10 +329,24 @@ kmap_tile_order_kernel(const int32_t* __restrict__ nbr, int64_t M, int K, int32_
   }
   for (int i = threadIdx.x; i < n; i += kTileOrderThreads)
     out_rows[base + i] = (int32_t)(base + (int64_t)(keys[i] & 4095ull));
+  // permuted copy of the window's table; a thread keeps its four source rows in registers
+  constexpr int kPer = kTileWindow / kTileOrderThreads;
+  int srow[kPer];
+#pragma unroll
+  for (int j = 0; j < kPer; ++j) {
+    const int i = threadIdx.x + j * kTileOrderThreads;
+    srow[j] = i < n ? (int)(keys[i] & 4095ull) : -1;
+  }
+#pragma unroll 4
   for (int k = 0; k < K; ++k) {
     const int32_t* src = nbr + (int64_t)k * M + base;
     int32_t* dst = nbr_tiled + (int64_t)k * M + base;
-    for (int i = threadIdx.x; i < n; i += kTileOrderThreads) dst[i] = __ldg(&src[keys[i] & 4095ull]);
+    int v[kPer];
+#pragma unroll
+    for (int j = 0; j < kPer; ++j) v[j] = srow[j] >= 0 ? __ldg(&src[srow[j]]) : 0;
+#pragma unroll
+    for (int j = 0; j < kPer; ++j)
+      if (srow[j] >= 0) dst[threadIdx.x + j * kTileOrderThreads] = v[j];
   }
 }
 
