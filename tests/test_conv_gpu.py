@@ -165,6 +165,37 @@ def test_tile_order_is_bit_identical(dtype, algo, c_in, c_out):
         assert torch.equal(a, b)
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("K,c_in,c_out", [(27, 3, 32), (1, 3, 32), (27, 4, 64), (8, 6, 16)])
+def test_narrow_input_kernel_matches_fp32_pipe_kernel(dtype, K, c_in, c_out):
+    """Layers with a few input channels take the streaming kernel under `auto`; it accumulates in
+    the order of the FP32-pipe kernel, so the two agree bit for bit (epilogue and tile order on)."""
+    from warpconvnet_b200._native import CONV_AUTO
+    n = 40000
+    coords, _, _ = _layer_case(n, 4, 4, 55, "raster_crop")
+    coords = np.ascontiguousarray(coords[np.argsort(km.morton_code(coords[:, 1:]), kind="stable")])
+    c = torch.from_numpy(coords).to(DEV)
+    g = torch.Generator().manual_seed(K + c_in)
+    if K == 27:
+        kmap, n_out = generate_kernel_map(c, c, (1, 1, 1), (3, 3, 3)), n
+    elif K == 8:
+        coarse, _ = stride_coords(c, (2, 2, 2))
+        kmap, n_out = generate_kernel_map(c, coarse, (2, 2, 2), (2, 2, 2)), len(coarse)
+    else:
+        from warpconvnet_b200.nn.functional.sparse_conv import _identity_map
+        kmap, n_out = _identity_map(n, torch.device(DEV)), n
+    x = torch.randn(n, c_in, generator=g).to(dtype).to(DEV)
+    w = (torch.randn(K, c_in, c_out, generator=g) * 0.3).to(dtype).to(DEV)
+    ep = ConvEpilogue(scale=(torch.rand(c_out, generator=g) + 0.5).to(DEV), shift=torch.randn(c_out, generator=g).to(DEV),
+                      residual=torch.randn(n_out, c_out, generator=g).to(dtype).to(DEV), relu=True)
+    a = sparse_conv_fused(x, w, kmap, n_out, epilogue=ep, algo=CONV_AUTO)
+    b = sparse_conv_fused(x, w, kmap, n_out, epilogue=ep, algo=CONV_SIMT)
+    check_device_status(DEV)
+    assert torch.equal(a, b)
+    plain = sparse_conv_fused(x, w, kmap, n_out, algo=CONV_AUTO)
+    assert torch.equal(plain, sparse_conv_fused(x, w, kmap, n_out, algo=CONV_SIMT))
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
 def test_fused_epilogue_matches_unfused_chain(dtype):
     """conv -> BatchNorm1d(eval) -> + residual -> ReLU in one kernel vs the separate torch ops."""

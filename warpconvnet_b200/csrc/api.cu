@@ -11,6 +11,10 @@ int wcn_conv_simt_fwd(const void* feats, const void* weight, const int32_t* nbr,
 bool wcn_conv_tcgen05_supported(int K, int c_in, int c_out, int dtype, int out_dtype);
 int64_t wcn_conv_tcgen05_packed_bytes(int K, int c_in, int c_out);
 int wcn_conv_tcgen05_pack(const void* weight, int K, int c_in, int c_out, void* packed, cudaStream_t st);
+bool wcn_conv_narrow_supported(int K, int c_in, int c_out, const void* out, const void* residual);
+int wcn_conv_narrow_fwd(const void* feats, const void* weight, const int32_t* nbr, const int32_t* out_rows,
+                        int64_t M, int K, int c_in, int c_out, int dtype, const float* scale, const float* shift,
+                        const void* residual, int relu, void* out, int out_dtype, cudaStream_t st);
 int wcn_conv_tcgen05_fwd(const void* feats, int64_t num_in, const void* packed, const int32_t* nbr,
                          const int32_t* out_rows, int64_t M, int K, int c_in,
                          int c_out, int dtype, const float* scale, const float* shift, const void* residual,
@@ -73,6 +77,12 @@ extern "C" int wcn_conv_fwd(int algo, const void* feats, int64_t num_in, const v
   }
   if (algo != WCN_CONV_SIMT && algo != WCN_CONV_AUTO) return WCN_ERR_INVALID_PARAMETERS;
   if (!weight) return WCN_ERR_INVALID_PARAMETERS;
+  if (algo == WCN_CONV_AUTO && wcn_conv_narrow_supported(num_offsets, c_in, c_out, out, residual)) {
+    // a few input channels: the streaming kernel (same numbers as the FP32-pipe kernel)
+    const int rc = wcn_conv_narrow_fwd(feats, weight, nbr, out_rows, num_out, num_offsets, c_in, c_out, dtype, scale,
+                                       shift, residual, relu, out, out_dtype, st);
+    if (rc != WCN_ERR_UNSUPPORTED_CONFIG) return rc;
+  }
   return wcn_conv_simt_fwd(feats, weight, nbr, out_rows, num_out, num_offsets, c_in, c_out, dtype, scale, shift, residual,
                            relu, out, out_dtype, st);
 }

@@ -102,6 +102,79 @@ int launch_simt(const void* feats, const void* weight, const int32_t* nbr, const
   return cudaGetLastError() == cudaSuccess ? WCN_OK : WCN_ERR_EXECUTION;
 }
 
+
+// ------------------------------------------------------------------ narrow inputs
+//
+// Layers with a handful of input channels (the 3 -> 32 stem of a network) are pure
+// streaming: a few bytes in, a row of c_out values out.  One thread owns 8 output channels of
+// one output row, the whole weight tensor sits in shared memory as fp32, and consecutive
+// threads write consecutive 16-byte (32-byte for fp32) pieces, so the output is written in
+// full lines.  Accumulation order (offset-major, then input channel, fused multiply-add) is
+// the one of conv_simt_kernel, so fp32 results are bit-identical to it.
+constexpr int NARROW_MAX_CIN = 8;
+constexpr int NARROW_MAX_WEIGHTS = 8192;  // floats of shared memory
+
+template <typename T, typename TO>
+__global__ void __launch_bounds__(NT)
+conv_narrow_kernel(const T* __restrict__ feats, const T* __restrict__ weight, const int32_t* __restrict__ nbr,
+                   const int32_t* __restrict__ out_rows, int64_t M, int K, int c_in, int c_out,
+                   const float* __restrict__ scale, const float* __restrict__ shift,
+                   const TO* __restrict__ residual, int relu, TO* __restrict__ out) {
+  __shared__ __align__(16) float w_s[NARROW_MAX_WEIGHTS];
+  for (int i = threadIdx.x; i < K * c_in * c_out; i += NT) w_s[i] = wcn_to_float<T>(weight[i]);
+  __syncthreads();
+  const int groups = c_out >> 3;
+  const int64_t t = (int64_t)blockIdx.x * NT + threadIdx.x;
+  const int64_t slot = t / groups;
+  const int n0 = (int)(t - slot * groups) * 8;
+  if (slot >= M) return;
+  float acc[8] = {};
+  for (int k = 0; k < K; ++k) {
+    const int src = __ldg(&nbr[(int64_t)k * M + slot]);
+    if (src < 0) continue;
+    const T* x = feats + (int64_t)src * c_in;
+    for (int c = 0; c < c_in; ++c) {
+      const float xv = wcn_to_float<T>(x[c]);
+      const float4 w0 = *reinterpret_cast<const float4*>(&w_s[(k * c_in + c) * c_out + n0]);
+      const float4 w1 = *reinterpret_cast<const float4*>(&w_s[(k * c_in + c) * c_out + n0 + 4]);
+      acc[0] = fmaf(xv, w0.x, acc[0]); acc[1] = fmaf(xv, w0.y, acc[1]);
+      acc[2] = fmaf(xv, w0.z, acc[2]); acc[3] = fmaf(xv, w0.w, acc[3]);
+      acc[4] = fmaf(xv, w1.x, acc[4]); acc[5] = fmaf(xv, w1.y, acc[5]);
+      acc[6] = fmaf(xv, w1.z, acc[6]); acc[7] = fmaf(xv, w1.w, acc[7]);
+    }
+  }
+  const int64_t m = out_rows ? (int64_t)__ldg(&out_rows[slot]) : slot;
+  constexpr int VEC = (int)(8 * sizeof(TO) / 16);  // 16-byte pieces of 8 outputs
+  __align__(16) TO tmp[8];
+  if (residual) {
+#pragma unroll
+    for (int v = 0; v < VEC; ++v)
+      reinterpret_cast<uint4*>(tmp)[v] = __ldg(reinterpret_cast<const uint4*>(residual + m * c_out + n0) + v);
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    float y = acc[j];
+    if (scale) y *= scale[n0 + j];
+    if (shift) y += shift[n0 + j];
+    if (residual) y += wcn_to_float<TO>(tmp[j]);
+    if (relu) y = fmaxf(y, 0.f);
+    tmp[j] = wcn_from_float<TO>(y);
+  }
+#pragma unroll
+  for (int v = 0; v < VEC; ++v) reinterpret_cast<uint4*>(out + m * c_out + n0)[v] = reinterpret_cast<uint4*>(tmp)[v];
+}
+
+template <typename T, typename TO>
+int launch_narrow(const void* feats, const void* weight, const int32_t* nbr, const int32_t* out_rows, int64_t M,
+                  int K, int c_in, int c_out, const float* scale, const float* shift, const void* residual,
+                  int relu, void* out, cudaStream_t st) {
+  const int64_t threads = M * (c_out >> 3);
+  conv_narrow_kernel<T, TO><<<(unsigned)((threads + NT - 1) / NT), NT, 0, st>>>(
+      (const T*)feats, (const T*)weight, nbr, out_rows, M, K, c_in, c_out, scale, shift, (const TO*)residual, relu,
+      (TO*)out);
+  return cudaGetLastError() == cudaSuccess ? WCN_OK : WCN_ERR_EXECUTION;
+}
+
 }  // namespace
 
 int wcn_conv_simt_fwd(const void* feats, const void* weight, const int32_t* nbr, const int32_t* out_rows,
@@ -119,5 +192,25 @@ int wcn_conv_simt_fwd(const void* feats, const void* weight, const int32_t* nbr,
   WCN_SIMT_CASE(WCN_F32, float, WCN_F16, __half)
   WCN_SIMT_CASE(WCN_F32, float, WCN_BF16, __nv_bfloat16)
 #undef WCN_SIMT_CASE
+  return WCN_ERR_UNSUPPORTED_CONFIG;
+}
+
+bool wcn_conv_narrow_supported(int K, int c_in, int c_out, const void* out, const void* residual) {
+  return c_in <= NARROW_MAX_CIN && c_out % 8 == 0 && (int64_t)K * c_in * c_out <= NARROW_MAX_WEIGHTS &&
+         (reinterpret_cast<uintptr_t>(out) & 15) == 0 && (reinterpret_cast<uintptr_t>(residual) & 15) == 0;
+}
+
+int wcn_conv_narrow_fwd(const void* feats, const void* weight, const int32_t* nbr, const int32_t* out_rows,
+                        int64_t M, int K, int c_in, int c_out, int dtype, const float* scale, const float* shift,
+                        const void* residual, int relu, void* out, int out_dtype, cudaStream_t st) {
+#define WCN_NARROW_CASE(DT, T, ODT, TO) \
+  if (dtype == DT && out_dtype == ODT) \
+    return launch_narrow<T, TO>(feats, weight, nbr, out_rows, M, K, c_in, c_out, scale, shift, residual, relu, out, st);
+  WCN_NARROW_CASE(WCN_F32, float, WCN_F32, float)
+  WCN_NARROW_CASE(WCN_F16, __half, WCN_F16, __half)
+  WCN_NARROW_CASE(WCN_BF16, __nv_bfloat16, WCN_BF16, __nv_bfloat16)
+  WCN_NARROW_CASE(WCN_F16, __half, WCN_F32, float)
+  WCN_NARROW_CASE(WCN_BF16, __nv_bfloat16, WCN_F32, float)
+#undef WCN_NARROW_CASE
   return WCN_ERR_UNSUPPORTED_CONFIG;
 }

@@ -672,7 +672,11 @@ bool plan_launch(ConvTcParams& p, int bk, size_t* smem, dim3* grid) {
   int g = cols >= 128 ? 2 : 4;
   while (g > 1 && ((tiles + g - 1) / g) * split < 2 * (int64_t)sms) g /= 2;
   const size_t a_unit = (size_t)BLOCK_M * bk * 2, b_unit = (size_t)p.block_n * bk * 2;
+#ifdef WCN_EXP_SMEM_KB  // development builds only: a smaller shared-memory budget
+  const size_t limit = (size_t)WCN_EXP_SMEM_KB * 1024;
+#else
   const size_t limit = 226 * 1024;  // the kernels opt in to this much dynamic shared memory
+#endif
   const int kb_total = p.c_in / bk;
   // Channel slices per ring slot: as many as give a 32 KiB row slot, fewer if the rings would not fit.
   int kbc = (int)((32 * 1024) / a_unit);
