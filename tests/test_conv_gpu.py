@@ -166,10 +166,12 @@ def test_tile_order_is_bit_identical(dtype, algo, c_in, c_out):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
-@pytest.mark.parametrize("K,c_in,c_out", [(27, 3, 32), (1, 3, 32), (27, 4, 64), (8, 6, 16)])
-def test_narrow_input_kernel_matches_fp32_pipe_kernel(dtype, K, c_in, c_out):
-    """Layers with a few input channels take the streaming kernel under `auto`; it accumulates in
-    the order of the FP32-pipe kernel, so the two agree bit for bit (epilogue and tile order on)."""
+@pytest.mark.parametrize("K,c_in,c_out", [(27, 3, 32), (1, 3, 32), (27, 4, 64), (8, 6, 16),
+                                          (1, 96, 20), (1, 64, 8), (8, 32, 24), (1, 128, 31)])
+def test_narrow_kernels_match_fp32_pipe_kernel(dtype, K, c_in, c_out):
+    """Layers with a few input channels (a stem) or a few output channels (a head) take the
+    streaming kernels under `auto`; they accumulate in the order of the FP32-pipe kernel, so the
+    results agree bit for bit (epilogue and tile order on)."""
     from warpconvnet_b200._native import CONV_AUTO
     n = 40000
     coords, _, _ = _layer_case(n, 4, 4, 55, "raster_crop")
@@ -191,9 +193,9 @@ def test_narrow_input_kernel_matches_fp32_pipe_kernel(dtype, K, c_in, c_out):
     a = sparse_conv_fused(x, w, kmap, n_out, epilogue=ep, algo=CONV_AUTO)
     b = sparse_conv_fused(x, w, kmap, n_out, epilogue=ep, algo=CONV_SIMT)
     check_device_status(DEV)
-    assert torch.equal(a, b)
     plain = sparse_conv_fused(x, w, kmap, n_out, algo=CONV_AUTO)
-    assert torch.equal(plain, sparse_conv_fused(x, w, kmap, n_out, algo=CONV_SIMT))
+    assert torch.equal(plain, sparse_conv_fused(x, w, kmap, n_out, algo=CONV_SIMT)), "accumulation differs"
+    assert torch.equal(a, b), "epilogue differs"
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.float16])

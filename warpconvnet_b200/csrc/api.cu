@@ -15,6 +15,11 @@ bool wcn_conv_narrow_supported(int K, int c_in, int c_out, const void* out, cons
 int wcn_conv_narrow_fwd(const void* feats, const void* weight, const int32_t* nbr, const int32_t* out_rows,
                         int64_t M, int K, int c_in, int c_out, int dtype, const float* scale, const float* shift,
                         const void* residual, int relu, void* out, int out_dtype, cudaStream_t st);
+bool wcn_conv_narrow_out_supported(int K, int c_in, int c_out, int dtype, const void* feats);
+int wcn_conv_narrow_out_fwd(const void* feats, const void* weight, const int32_t* nbr, const int32_t* out_rows,
+                            int64_t M, int K, int c_in, int c_out, int dtype, const float* scale,
+                            const float* shift, const void* residual, int relu, void* out, int out_dtype,
+                            cudaStream_t st);
 int wcn_conv_tcgen05_fwd(const void* feats, int64_t num_in, const void* packed, const int32_t* nbr,
                          const int32_t* out_rows, int64_t M, int K, int c_in,
                          int c_out, int dtype, const float* scale, const float* shift, const void* residual,
@@ -81,6 +86,12 @@ extern "C" int wcn_conv_fwd(int algo, const void* feats, int64_t num_in, const v
     // a few input channels: the streaming kernel (same numbers as the FP32-pipe kernel)
     const int rc = wcn_conv_narrow_fwd(feats, weight, nbr, out_rows, num_out, num_offsets, c_in, c_out, dtype, scale,
                                        shift, residual, relu, out, out_dtype, st);
+    if (rc != WCN_ERR_UNSUPPORTED_CONFIG) return rc;
+  }
+  if (algo == WCN_CONV_AUTO && num_in > 0 && wcn_conv_narrow_out_supported(num_offsets, c_in, c_out, dtype, feats)) {
+    // a few output channels (a classification head): one thread per output row
+    const int rc = wcn_conv_narrow_out_fwd(feats, weight, nbr, out_rows, num_out, num_offsets, c_in, c_out, dtype,
+                                           scale, shift, residual, relu, out, out_dtype, st);
     if (rc != WCN_ERR_UNSUPPORTED_CONFIG) return rc;
   }
   return wcn_conv_simt_fwd(feats, weight, nbr, out_rows, num_out, num_offsets, c_in, c_out, dtype, scale, shift, residual,

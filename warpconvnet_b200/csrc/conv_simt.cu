@@ -83,9 +83,8 @@ conv_simt_kernel(const T* __restrict__ feats, const T* __restrict__ weight, cons
       const int n = n0 + tx * 4 + j;
       if (n >= c_out) continue;
       float y = acc[i][j];
-      if (scale) y *= scale[n];
-      if (shift) y += shift[n];
-      if (residual) y += wcn_to_float<TO>(residual[m * c_out + n]);
+      y = wcn_affine(y, scale, shift, n);
+      if (residual) y = __fadd_rn(y, wcn_to_float<TO>(residual[m * c_out + n]));
       if (relu) y = fmaxf(y, 0.f);
       out[m * c_out + n] = wcn_from_float<TO>(y);
     }
@@ -154,9 +153,8 @@ conv_narrow_kernel(const T* __restrict__ feats, const T* __restrict__ weight, co
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
     float y = acc[j];
-    if (scale) y *= scale[n0 + j];
-    if (shift) y += shift[n0 + j];
-    if (residual) y += wcn_to_float<TO>(tmp[j]);
+    y = wcn_affine(y, scale, shift, n0 + j);
+    if (residual) y = __fadd_rn(y, wcn_to_float<TO>(tmp[j]));
     if (relu) y = fmaxf(y, 0.f);
     tmp[j] = wcn_from_float<TO>(y);
   }
@@ -172,6 +170,85 @@ int launch_narrow(const void* feats, const void* weight, const int32_t* nbr, con
   conv_narrow_kernel<T, TO><<<(unsigned)((threads + NT - 1) / NT), NT, 0, st>>>(
       (const T*)feats, (const T*)weight, nbr, out_rows, M, K, c_in, c_out, scale, shift, (const TO*)residual, relu,
       (TO*)out);
+  return cudaGetLastError() == cudaSuccess ? WCN_OK : WCN_ERR_EXECUTION;
+}
+
+// ------------------------------------------------------------------ narrow outputs
+//
+// Layers with at most 32 output channels that the tensor-core kernel does not take (a
+// 96 -> 20 classification head): one thread owns one output row, reads its input rows with
+// 16-byte loads, keeps all outputs in registers and takes the weights (fp32, padded to NP
+// columns) from shared memory, where every lane reads the same address.  Accumulation order
+// is the one of conv_simt_kernel.
+template <typename T, typename TO, int NP>
+__global__ void __launch_bounds__(NT)
+conv_narrow_out_kernel(const T* __restrict__ feats, const T* __restrict__ weight, const int32_t* __restrict__ nbr,
+                       const int32_t* __restrict__ out_rows, int64_t M, int K, int c_in, int c_out,
+                       const float* __restrict__ scale, const float* __restrict__ shift,
+                       const TO* __restrict__ residual, int relu, TO* __restrict__ out) {
+  __shared__ __align__(16) float w_s[NARROW_MAX_WEIGHTS];  // [K][c_in][NP]
+  for (int i = threadIdx.x; i < K * c_in * NP; i += NT) {
+    const int n = i % NP, kc = i / NP;
+    w_s[i] = n < c_out ? wcn_to_float<T>(weight[(int64_t)kc * c_out + n]) : 0.f;
+  }
+  __syncthreads();
+  const int64_t slot = (int64_t)blockIdx.x * NT + threadIdx.x;
+  if (slot >= M) return;
+  constexpr int EPV = 16 / (int)sizeof(T);  // input elements per 16-byte load
+  float acc[NP];
+#pragma unroll
+  for (int j = 0; j < NP; ++j) acc[j] = 0.f;
+  for (int k = 0; k < K; ++k) {
+    const int src = __ldg(&nbr[(int64_t)k * M + slot]);
+    if (src < 0) continue;
+    const uint4* x = reinterpret_cast<const uint4*>(feats + (int64_t)src * c_in);
+    const float* wk = w_s + (int64_t)k * c_in * NP;
+    for (int c0 = 0; c0 < c_in; c0 += EPV) {
+      const uint4 raw = __ldg(x + c0 / EPV);
+      const T* xv = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+      for (int e = 0; e < EPV; ++e) {
+        const float xf = wcn_to_float<T>(xv[e]);
+        const float4* w4 = reinterpret_cast<const float4*>(wk + (c0 + e) * NP);
+#pragma unroll
+        for (int q = 0; q < NP / 4; ++q) {
+          const float4 w = w4[q];
+          acc[4 * q + 0] = fmaf(xf, w.x, acc[4 * q + 0]);
+          acc[4 * q + 1] = fmaf(xf, w.y, acc[4 * q + 1]);
+          acc[4 * q + 2] = fmaf(xf, w.z, acc[4 * q + 2]);
+          acc[4 * q + 3] = fmaf(xf, w.w, acc[4 * q + 3]);
+        }
+      }
+    }
+  }
+  const int64_t m = out_rows ? (int64_t)__ldg(&out_rows[slot]) : slot;
+  TO* orow = out + m * c_out;
+  const TO* rrow = residual ? residual + m * c_out : nullptr;
+#pragma unroll
+  for (int j = 0; j < NP; ++j) {
+    if (j < c_out) {
+      float y = acc[j];
+      y = wcn_affine(y, scale, shift, j);
+      if (rrow) y = __fadd_rn(y, wcn_to_float<TO>(rrow[j]));
+      if (relu) y = fmaxf(y, 0.f);
+      orow[j] = wcn_from_float<TO>(y);
+    }
+  }
+}
+
+template <typename T, typename TO>
+int launch_narrow_out(const void* feats, const void* weight, const int32_t* nbr, const int32_t* out_rows, int64_t M,
+                      int K, int c_in, int c_out, const float* scale, const float* shift, const void* residual,
+                      int relu, void* out, cudaStream_t st) {
+  const unsigned blocks = (unsigned)((M + NT - 1) / NT);
+#define WCN_NOUT(NPV) \
+  conv_narrow_out_kernel<T, TO, NPV><<<blocks, NT, 0, st>>>((const T*)feats, (const T*)weight, nbr, out_rows, M, K, c_in, \
+                                                            c_out, scale, shift, (const TO*)residual, relu, (TO*)out)
+  if (c_out <= 8) WCN_NOUT(8);
+  else if (c_out <= 16) WCN_NOUT(16);
+  else if (c_out <= 24) WCN_NOUT(24);
+  else WCN_NOUT(32);
+#undef WCN_NOUT
   return cudaGetLastError() == cudaSuccess ? WCN_OK : WCN_ERR_EXECUTION;
 }
 
@@ -212,5 +289,27 @@ int wcn_conv_narrow_fwd(const void* feats, const void* weight, const int32_t* nb
   WCN_NARROW_CASE(WCN_F16, __half, WCN_F32, float)
   WCN_NARROW_CASE(WCN_BF16, __nv_bfloat16, WCN_F32, float)
 #undef WCN_NARROW_CASE
+  return WCN_ERR_UNSUPPORTED_CONFIG;
+}
+
+bool wcn_conv_narrow_out_supported(int K, int c_in, int c_out, int dtype, const void* feats) {
+  const int np = (c_out + 7) / 8 * 8;
+  return c_out <= 32 && (int64_t)K * c_in * np <= NARROW_MAX_WEIGHTS && (c_in * wcn_dtype_size(dtype)) % 16 == 0 &&
+         (reinterpret_cast<uintptr_t>(feats) & 15) == 0;
+}
+
+int wcn_conv_narrow_out_fwd(const void* feats, const void* weight, const int32_t* nbr, const int32_t* out_rows,
+                            int64_t M, int K, int c_in, int c_out, int dtype, const float* scale,
+                            const float* shift, const void* residual, int relu, void* out, int out_dtype,
+                            cudaStream_t st) {
+#define WCN_NOUT_CASE(DT, T, ODT, TO) \
+  if (dtype == DT && out_dtype == ODT) \
+    return launch_narrow_out<T, TO>(feats, weight, nbr, out_rows, M, K, c_in, c_out, scale, shift, residual, relu, out, st);
+  WCN_NOUT_CASE(WCN_F32, float, WCN_F32, float)
+  WCN_NOUT_CASE(WCN_F16, __half, WCN_F16, __half)
+  WCN_NOUT_CASE(WCN_BF16, __nv_bfloat16, WCN_BF16, __nv_bfloat16)
+  WCN_NOUT_CASE(WCN_F16, __half, WCN_F32, float)
+  WCN_NOUT_CASE(WCN_BF16, __nv_bfloat16, WCN_F32, float)
+#undef WCN_NOUT_CASE
   return WCN_ERR_UNSUPPORTED_CONFIG;
 }

@@ -98,4 +98,13 @@ template <> __device__ __forceinline__ float wcn_from_float<float>(float v) { re
 template <> __device__ __forceinline__ __half wcn_from_float<__half>(float v) { return __float2half_rn(v); }
 template <> __device__ __forceinline__ __nv_bfloat16 wcn_from_float<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
 
+// Epilogue affine step, written with explicit roundings so that every kernel produces the same
+// bits whatever the compiler would have contracted: fma when both are present.
+__device__ __forceinline__ float wcn_affine(float y, const float* scale, const float* shift, int n) {
+  if (scale && shift) return fmaf(y, scale[n], shift[n]);
+  if (scale) return __fmul_rn(y, scale[n]);
+  if (shift) return __fadd_rn(y, shift[n]);
+  return y;
+}
+
 static inline int wcn_dtype_size(int dtype) { return dtype == WCN_F32 ? 4 : 2; }

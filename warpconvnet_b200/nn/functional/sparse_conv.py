@@ -428,12 +428,14 @@ def spatially_sparse_conv(
     needs_grad = torch.is_grad_enabled() and (feats.requires_grad or weight.requires_grad)
 
     if all(k == 1 for k in _kernel_size) and all(s == 1 for s in _stride):
-        if epilogue is None:
+        native = feats.is_cuda and feats.dtype in (torch.float32, torch.float16, torch.bfloat16)
+        if epilogue is None and (needs_grad or not native):
             out = feats @ weight[0].to(feats.dtype) if weight.dtype != feats.dtype else feats @ weight[0]
             if bias is not None:
                 out = out + bias.to(out.dtype)
             return input_sparse_tensor.replace(batched_features=out)
-        # 1x1x1 with a fused tail: the same kernel over the identity neighbour table
+        # 1x1x1 in inference: the native kernel over the identity neighbour table, bias and any fused
+        # tail in its epilogue
         n = feats.shape[0]
         ident = _identity_map(n, feats.device)
         ep = _merge_bias(epilogue, bias)
