@@ -300,10 +300,7 @@ def run_gpu_arm(args):
     def forward(xyz, feats):
         vox = Voxels(xyz, feats, offsets=offsets)
         ordered = vox.sort(POINT_ORDERING.MORTON_XYZ)
-        out = model(ordered)
-        inv = torch.empty_like(ordered.extra_attributes["perm"])
-        inv[ordered.extra_attributes["perm"]] = torch.arange(n_vox, device=dev)
-        return out.feature_tensor[inv]
+        return model(ordered, restore_order=True)  # logits in the caller's row order
 
     def step_resident():
         flush.zero_()

@@ -198,6 +198,24 @@ def test_narrow_kernels_match_fp32_pipe_kernel(dtype, K, c_in, c_out):
     assert torch.equal(a, b), "epilogue differs"
 
 
+def test_minkunet_restore_order_equals_unpermute():
+    """`restore_order=True` stores the head's rows through the sort permutation: the same
+    numbers as un-permuting the sorted result afterwards."""
+    from warpconvnet_b200 import POINT_ORDERING
+    coords, x, _ = _layer_case(20000, 3, 4, 31, "raster_crop")
+    torch.manual_seed(2)
+    model = MinkUNet18(3, 20).to(DEV).half().eval()
+    randomize_batchnorm_(model)
+    vox = make_voxels(coords, x.half()).sort(POINT_ORDERING.MORTON_XYZ)
+    perm = vox.extra_attributes["perm"]
+    with torch.no_grad():
+        direct = model(vox, restore_order=True)
+        ref = torch.empty_like(direct)
+        ref[perm] = model(vox).feature_tensor
+    check_device_status(DEV)
+    assert torch.equal(direct, ref)
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
 def test_fused_epilogue_matches_unfused_chain(dtype):
     """conv -> BatchNorm1d(eval) -> + residual -> ReLU in one kernel vs the separate torch ops."""

@@ -107,7 +107,11 @@ class MinkUNetBase(nn.Module):
         layers += [BLOCK(out_channels, out_channels) for _ in range(1, blocks)]
         return nn.Sequential(*layers)
 
-    def forward(self, x: Voxels) -> Voxels:
+    def forward(self, x: Voxels, restore_order: bool = False):
+        """``restore_order`` (an addition to the reference signature; inference only): ``x`` is the
+        result of ``Voxels.sort`` and the logits are wanted for the rows as they were before the
+        sort.  The last convolution then stores its rows through the sort permutation and the
+        return value is the ``[N, classes]`` tensor in that order, with no separate un-permute."""
         # all four coarse coordinate sets first: their size read-backs then wait for coordinate
         # kernels only, and the convolutions below queue without a host synchronisation
         prefetch_strided_coordinates(x, [2, 2, 2, 2])
@@ -120,6 +124,10 @@ class MinkUNetBase(nn.Module):
         out = self.block6(cat(self.convtr5(out, out_b2p4), out_b2p4))
         out = self.block7(cat(self.convtr6(out, out_b1p2), out_b1p2))
         out = self.block8(cat(self.convtr7(out, out_p1), out_p1))
+        if restore_order:
+            perm = x.extra_attributes.get("perm")
+            assert perm is not None, "restore_order needs the permutation that Voxels.sort records"
+            return self.final(out, epilogue=ConvEpilogue(out_rows=perm)).feature_tensor
         return self.final(out)
 
 

@@ -64,12 +64,16 @@ class ConvEpilogue:
     ``y = conv * scale + shift; y += residual; y = relu(y)`` (each part optional).
     ``scale``/``shift`` are fp32 ``[C_out]`` (an eval-mode BatchNorm folds to
     exactly this; a bias is a shift); ``residual`` is ``[M, C_out]`` in the
-    output dtype."""
+    output dtype.  ``out_rows`` (a permutation of ``0..M-1``) stores result row
+    ``s`` at row ``out_rows[s]`` of the output, e.g. the ``perm`` of a sorted
+    ``Voxels`` to get the rows back in the order they had before the sort; it
+    cannot be combined with ``residual``."""
 
     scale: Optional[Tensor] = None
     shift: Optional[Tensor] = None
     residual: Optional[Tensor] = None
     relu: bool = False
+    out_rows: Optional[Tensor] = None
 
 
 def _normalize_fwd_algo(algo) -> SPARSE_CONV_FWD_ALGO_MODE:
@@ -196,6 +200,12 @@ def sparse_conv_fused(in_features: Tensor, weight: Tensor, kernel_map: IntSearch
         nbr, out_rows = kernel_map.neighbor_table(num_out_coords), None
     assert nbr.shape[0] == K, f"kernel map has {nbr.shape[0]} offsets, weight has {K}"
     ep = epilogue or ConvEpilogue()
+    if ep.out_rows is not None:
+        assert ep.residual is None, "out_rows cannot be combined with a residual"
+        assert ep.out_rows.shape == (num_out_coords,), "out_rows must have one entry per output row"
+        user_rows = ep.out_rows.to(device=dev, dtype=torch.int32)
+        out_rows = user_rows if out_rows is None else user_rows[out_rows.long()]
+        out_rows = out_rows.contiguous()
     scale = _as_f32_on(ep.scale, dev)
     shift = _as_f32_on(ep.shift, dev)
     residual = None
@@ -512,10 +522,13 @@ def _merge_bias(epilogue: Optional[ConvEpilogue], bias: Optional[Tensor]) -> Opt
     b = bias.detach().float()
     if epilogue is None:
         return ConvEpilogue(shift=b)
+    if epilogue.scale is None and epilogue.shift is None:
+        return ConvEpilogue(shift=b, residual=epilogue.residual, relu=epilogue.relu, out_rows=epilogue.out_rows)
     if epilogue.scale is not None:
         b = b * epilogue.scale.to(b.device).float()
     shift = b if epilogue.shift is None else epilogue.shift.to(b.device).float() + b
-    return ConvEpilogue(scale=epilogue.scale, shift=shift, residual=epilogue.residual, relu=epilogue.relu)
+    return ConvEpilogue(scale=epilogue.scale, shift=shift, residual=epilogue.residual, relu=epilogue.relu,
+                        out_rows=epilogue.out_rows)
 
 
 _identity_maps: dict = {}
