@@ -293,60 +293,123 @@ __global__ void nbr_transpose_kernel(const int32_t* __restrict__ nbr_fwd, int64_
 // keeps the gather footprint of a tile local.
 constexpr int kTileWindow = 4096;
 constexpr int kTileOrderThreads = 1024;
+constexpr int kTileCopyOffsets = 3;  // offsets per block of the permuted copy
+
+// Pass 1: presence mask of every output row (one thread per row, all loads in flight).
+__global__ void kmap_row_mask_kernel(const int32_t* __restrict__ nbr, int64_t M, int K, uint32_t* __restrict__ masks) {
+  const int64_t m = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (m >= M) return;
+  int v[32];
+#pragma unroll
+  for (int k = 0; k < 32; ++k) v[k] = k < K ? __ldg(&nbr[(int64_t)k * M + m]) : -1;
+  uint32_t mask = 0;
+#pragma unroll
+  for (int k = 0; k < 32; ++k) mask |= (uint32_t)(v[k] >= 0) << k;
+  masks[m] = mask;
+}
+
+// Pass 2: one block per window sorts its rows by (mask, row) and replaces the masks by the row
+// order.  Stable least-significant-digit radix sort of the permutation, 7 bits per pass
+// (ceil(K / 7) passes): a warp owns 128 consecutive positions, ranks equal digits with
+// match_any (lane order = position order, so the sort is stable and deterministic), the
+// per-(digit, warp) counts are scanned digit-major by the block, and rows scatter to their place.
+constexpr int kDigitBits = 7, kDigits = 1 << kDigitBits;
 
 __global__ void __launch_bounds__(kTileOrderThreads)
-kmap_tile_order_kernel(const int32_t* __restrict__ nbr, int64_t M, int K, int32_t* __restrict__ out_rows,
-                       int32_t* __restrict__ nbr_tiled) {
-  __shared__ unsigned long long keys[kTileWindow];
+kmap_window_sort_kernel(int32_t* __restrict__ rows_io, int64_t M, int K) {
+  __shared__ uint32_t mask_s[kTileWindow];             // mask of local row r (never moves)
+  __shared__ uint16_t perm_s[2][kTileWindow];          // local rows in the current / next order
+  __shared__ uint16_t cnt[kDigits * 32];               // [digit][warp] counts, then start positions
+  __shared__ uint32_t warp_sums[32];
   const int64_t base = (int64_t)blockIdx.x * kTileWindow;
   const int n = (int)min((int64_t)kTileWindow, M - base);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   for (int i = threadIdx.x; i < kTileWindow; i += kTileOrderThreads) {
-    unsigned long long key = ~0ull;
-    if (i < n) {
-      unsigned mask = 0;
-      int v[32];  // every load is issued before the first one is consumed
-#pragma unroll
-      for (int k = 0; k < 32; ++k) v[k] = k < K ? __ldg(&nbr[(int64_t)k * M + base + i]) : -1;
-#pragma unroll
-      for (int k = 0; k < 32; ++k) mask |= (unsigned)(v[k] >= 0) << k;
-      key = ((unsigned long long)mask << 12) | (unsigned)i;
-    }
-    keys[i] = key;
+    mask_s[i] = i < n ? (uint32_t)rows_io[base + i] : 0xFFFFFFFFu;  // padding sorts last (ties: stable)
+    perm_s[0][i] = (uint16_t)i;
   }
-  __syncthreads();
-  // bitonic sort, ascending; keys are distinct (the low 12 bits are the row)
-  for (int size = 2; size <= kTileWindow; size <<= 1) {
-    for (int stride = size >> 1; stride > 0; stride >>= 1) {
-      for (int t = threadIdx.x; t < kTileWindow / 2; t += kTileOrderThreads) {
-        const int lo = 2 * t - (t & (stride - 1));
-        const int hi = lo + stride;
-        const bool up = (lo & size) == 0;
-        const unsigned long long a = keys[lo], b = keys[hi];
-        if ((a > b) == up) { keys[lo] = b; keys[hi] = a; }
+  int cur = 0;
+  const int passes = (K + kDigitBits - 1) / kDigitBits;
+  for (int pass = 0; pass < passes; ++pass) {
+    const int shift = pass * kDigitBits;
+    for (int i = threadIdx.x; i < kDigits * 32; i += kTileOrderThreads) cnt[i] = 0;
+    __syncthreads();
+    // rank inside (warp, digit); positions of a warp: warp*128 + batch*32 + lane
+    uint16_t row[4];
+    int dig[4], rank[4];
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+      row[b] = perm_s[cur][warp * 128 + b * 32 + lane];
+      dig[b] = (int)((mask_s[row[b]] >> shift) & (kDigits - 1));
+      const unsigned same = __match_any_sync(0xFFFFFFFFu, dig[b]);
+      const int r = __popc(same & ((1u << lane) - 1u));
+      const int leader = __ffs(same) - 1;
+      int before = 0;
+      if (r == 0) {  // the first lane of each digit updates the warp's count
+        before = cnt[dig[b] * 32 + warp];
+        cnt[dig[b] * 32 + warp] = (uint16_t)(before + __popc(same));
+      }
+      before = __shfl_sync(0xFFFFFFFFu, before, leader);
+      rank[b] = before + r;
+      __syncwarp();  // the next batch reads the counts written here
+    }
+    __syncthreads();
+    // exclusive scan of the counts in (digit, warp) order: 4 consecutive entries per thread
+    {
+      constexpr int kPer = kDigits * 32 / kTileOrderThreads;
+      uint32_t v[kPer], sum = 0;
+#pragma unroll
+      for (int j = 0; j < kPer; ++j) { v[j] = cnt[threadIdx.x * kPer + j]; sum += v[j]; }
+      uint32_t incl = sum;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const uint32_t o = __shfl_up_sync(0xFFFFFFFFu, incl, d);
+        if (lane >= d) incl += o;
+      }
+      if (lane == 31) warp_sums[warp] = incl;
+      __syncthreads();
+      if (warp == 0) {
+        const uint32_t w = warp_sums[lane];
+        uint32_t wi = w;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+          const uint32_t o = __shfl_up_sync(0xFFFFFFFFu, wi, d);
+          if (lane >= d) wi += o;
+        }
+        warp_sums[lane] = wi - w;
       }
       __syncthreads();
-    }
-  }
-  for (int i = threadIdx.x; i < n; i += kTileOrderThreads)
-    out_rows[base + i] = (int32_t)(base + (int64_t)(keys[i] & 4095ull));
-  // permuted copy of the window's table; a thread keeps its four source rows in registers
-  constexpr int kPer = kTileWindow / kTileOrderThreads;
-  int srow[kPer];
+      uint32_t run = warp_sums[warp] + incl - sum;
 #pragma unroll
-  for (int j = 0; j < kPer; ++j) {
-    const int i = threadIdx.x + j * kTileOrderThreads;
-    srow[j] = i < n ? (int)(keys[i] & 4095ull) : -1;
+      for (int j = 0; j < kPer; ++j) { cnt[threadIdx.x * kPer + j] = (uint16_t)run; run += v[j]; }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int b = 0; b < 4; ++b) perm_s[cur ^ 1][cnt[dig[b] * 32 + warp] + rank[b]] = row[b];
+    cur ^= 1;
+    __syncthreads();
   }
-#pragma unroll 4
-  for (int k = 0; k < K; ++k) {
+  for (int i = threadIdx.x; i < n; i += kTileOrderThreads) rows_io[base + i] = (int32_t)(base + perm_s[cur][i]);
+}
+
+// Pass 3: nbr_tiled[k][s] = nbr[k][out_rows[s]]; a block stages one window of one offset in
+// shared memory, so global memory is read and written in full lines.
+__global__ void __launch_bounds__(kTileOrderThreads)
+kmap_permute_kernel(const int32_t* __restrict__ nbr, const int32_t* __restrict__ out_rows, int64_t M, int K,
+                    int32_t* __restrict__ nbr_tiled) {
+  __shared__ uint16_t perm[kTileWindow];
+  __shared__ int32_t stage[kTileWindow];
+  const int64_t base = (int64_t)blockIdx.x * kTileWindow;
+  const int n = (int)min((int64_t)kTileWindow, M - base);
+  for (int i = threadIdx.x; i < n; i += kTileOrderThreads) perm[i] = (uint16_t)(out_rows[base + i] - base);
+  const int k0 = blockIdx.y * kTileCopyOffsets;
+  for (int k = k0; k < min(K, k0 + kTileCopyOffsets); ++k) {
     const int32_t* src = nbr + (int64_t)k * M + base;
     int32_t* dst = nbr_tiled + (int64_t)k * M + base;
-    int v[kPer];
-#pragma unroll
-    for (int j = 0; j < kPer; ++j) v[j] = srow[j] >= 0 ? __ldg(&src[srow[j]]) : 0;
-#pragma unroll
-    for (int j = 0; j < kPer; ++j)
-      if (srow[j] >= 0) dst[threadIdx.x + j * kTileOrderThreads] = v[j];
+    __syncthreads();  // perm written / previous offset's stage fully read
+    for (int i = threadIdx.x; i < n; i += kTileOrderThreads) stage[i] = __ldg(&src[i]);
+    __syncthreads();
+    for (int i = threadIdx.x; i < n; i += kTileOrderThreads) dst[i] = stage[perm[i]];
   }
 }
 
@@ -628,9 +691,13 @@ extern "C" int wcn_kmap_tile_order(const int32_t* nbr, int64_t num_out, int32_t 
   if (num_offsets <= 0 || num_offsets > 32 || num_out < 0 || num_out >= 0x7FFFFFFFll) return WCN_ERR_INVALID_PARAMETERS;
   if (num_out == 0) return WCN_OK;
   if (!nbr || !out_rows || !nbr_tiled || nbr == nbr_tiled) return WCN_ERR_INVALID_PARAMETERS;
-  const unsigned blocks = (unsigned)((num_out + kTileWindow - 1) / kTileWindow);
-  kmap_tile_order_kernel<<<blocks, kTileOrderThreads, 0, wcn_stream(stream)>>>(nbr, num_out, num_offsets, out_rows,
-                                                                              nbr_tiled);
+  cudaStream_t st = wcn_stream(stream);
+  const unsigned windows = (unsigned)((num_out + kTileWindow - 1) / kTileWindow);
+  // out_rows first holds the masks, then (window by window) the order
+  kmap_row_mask_kernel<<<grid_for(num_out), kThreads, 0, st>>>(nbr, num_out, num_offsets, (uint32_t*)out_rows);
+  kmap_window_sort_kernel<<<windows, kTileOrderThreads, 0, st>>>(out_rows, num_out, num_offsets);
+  dim3 grid(windows, (unsigned)((num_offsets + kTileCopyOffsets - 1) / kTileCopyOffsets));
+  kmap_permute_kernel<<<grid, kTileOrderThreads, 0, st>>>(nbr, out_rows, num_out, num_offsets, nbr_tiled);
   WCN_CHECK_LAUNCH();
   return WCN_OK;
 }
