@@ -65,7 +65,8 @@ const char* wcn_status_string(int status);
 
 /* ------------------------------------------------------------------ hash table */
 
-/* Bytes of the table buffer for `capacity` slots (16-byte key + 4-byte value per slot).
+/* Bytes of the table buffer for `capacity` slots (16-byte key + 4-byte value per slot, and a
+ * 16-byte tail whose first word records whether a key was inserted twice).
  * Replaces the `[capacity, 2] int32` allocation in TorchHashTable.insert
  * (warpconvnet/geometry/coords/search/torch_hashmap.py:142). */
 int wcn_hash_table_bytes(int64_t capacity, int64_t* bytes);
@@ -114,7 +115,8 @@ int wcn_kmap_workspace_bytes(int64_t num_queries, int32_t num_offsets, int64_t* 
 
 /* nbr[k*M + m] = row of (b, x*sx + i - cx, y*sy + j - cy, z*sz + l - cz) in the table or
  * -1, for k = (i*ky + j)*kz + l and c = size/2 for odd sizes, 0 for even sizes; also the
- * per-block hit counts in `workspace`.  num_offsets limits k to the first num_offsets
+ * per-block hit counts in `workspace` (NULL: no counts; wcn_kmap_count makes them later if a
+ * compact map is ever asked for).  num_offsets limits k to the first num_offsets
  * positions (the reference's skip_symmetric mode passes K/2).
  * Replaces kernel_map_size_4d_{fnv1a,city,murmur}
  * (warpconvnet/csrc/discrete_kernels.cu:264-334, 339-370). */
@@ -176,6 +178,25 @@ int wcn_nbr_from_maps(const int32_t* in_maps, const int32_t* out_maps, const int
  * of transposed convolutions (warpconvnet/nn/functional/sparse_conv.py:1934-1938, 1953-1957). */
 int wcn_nbr_transpose(const int32_t* nbr_fwd, int32_t num_offsets, int64_t num_out, int64_t num_in,
                       int32_t* nbr_t, void* stream);
+
+/* Kernel map of a coordinate set onto itself: `keys` are the rows the table was built from
+ * (same order), the window is odd and the stride 1, so nbr is [K, num_keys] with
+ * K = kx*ky*kz.  Same result as wcn_kmap_search on those arguments.  When the keys are
+ * distinct (the table records whether they are) the map is symmetric, nbr[k][m] = i exactly
+ * when nbr[K-1-k][i] = m, and only the first half of the offsets and the centre are probed.
+ * Leaves no hit counts.
+ * Replaces kernel_map_size_4d_* for the submanifold case, i.e. what the reference's
+ * skip_symmetric_kernel_map flag hints at (warpconvnet/geometry/coords/search/torch_discrete.py:291-296)
+ * but never completes into the full map. */
+int wcn_kmap_search_self(const void* table, int64_t capacity, int hash_method, const int32_t* keys,
+                         int64_t num_keys, const int32_t* kernel_size, int32_t* nbr, void* stream);
+
+/* Per-block hit counts of a dense neighbour table into `workspace`, exactly what
+ * wcn_kmap_search leaves there; for maps that were searched without counts.
+ * Replaces the `found >= 0` pass of map_found_indices_to_maps_cuda
+ * (warpconvnet/csrc/discrete_kernels.cu:183-213). */
+int wcn_kmap_count(const int32_t* nbr, int64_t num_queries, int32_t num_offsets, void* workspace,
+                   void* stream);
 
 /* Tile order of a neighbour table: within each window of 4096 consecutive output rows the
  * rows are sorted by their neighbour-presence mask (bit k set when nbr[k][m] >= 0; ties by

@@ -52,7 +52,7 @@ def test_status_strings_and_version(lib):
 
 def test_host_side_argument_checks_need_no_gpu(lib):
     out = ctypes.c_int64(0)
-    assert lib.wcn_hash_table_bytes(ctypes.c_int64(1000), ctypes.byref(out)) == 0 and out.value == 20000
+    assert lib.wcn_hash_table_bytes(ctypes.c_int64(1000), ctypes.byref(out)) == 0 and out.value == 20016
     assert lib.wcn_hash_table_bytes(ctypes.c_int64(0), ctypes.byref(out)) == -5
     assert lib.wcn_kmap_workspace_bytes(ctypes.c_int64(1000), 27, ctypes.byref(out)) == 0 and out.value >= 27 * 4 * 4
     assert lib.wcn_conv_packed_weight_bytes(0, 27, 64, 64, 1, ctypes.byref(out)) == 0 and out.value == 27 * 64 * 64 * 2

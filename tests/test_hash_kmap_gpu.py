@@ -235,3 +235,29 @@ def test_tile_order_matches_oracle(n, ksize, stride):
         assert np.array_equal(np.sort(want_rows), np.arange(m))
         assert np.array_equal(want_rows // 4096, np.arange(m) // 4096)  # no row leaves its window
     check_device_status(DEV)
+
+
+@pytest.mark.parametrize("method", list(HashMethod))
+def test_self_map_with_repeated_rows_matches_oracle(method):
+    """A coordinate set searched against itself takes the mirrored search when its rows are
+    distinct and the full search when they are not (the table records which); both equal the
+    oracle, compact form included."""
+    rng = np.random.default_rng(17)
+    distinct = np.unique(rng.integers(0, 24, size=(6000, 4)).astype(np.int32), axis=0)
+    distinct[:, 0] %= 2
+    distinct = np.unique(distinct, axis=0)
+    rng.shuffle(distinct)
+    repeated = np.concatenate([distinct, distinct[:500]], axis=0)
+    for coords in (distinct, repeated):
+        c = dev(coords)
+        res = generate_kernel_map(c, c, (1, 1, 1), (3, 3, 3), hash_method=method)
+        i, o, f, iden = km.generate_kernel_map(coords, coords, (1, 1, 1), (3, 3, 3))
+        assert np.array_equal(res.neighbor_table(len(coords)).cpu().numpy(),
+                              km.kernel_map_found(coords, coords, (1, 1, 1), (3, 3, 3)))
+        assert_map_equal(res, i, o, f)
+    # a 3x1x5 window: mirrored offsets with unequal extents
+    c = dev(distinct)
+    res = generate_kernel_map(c, c, (1, 1, 1), (3, 1, 5), hash_method=method)
+    assert np.array_equal(res.neighbor_table(len(distinct)).cpu().numpy(),
+                          km.kernel_map_found(distinct, distinct, (1, 1, 1), (3, 1, 5)))
+    check_device_status(DEV)

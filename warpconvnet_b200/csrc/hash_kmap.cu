@@ -46,12 +46,15 @@ __device__ __forceinline__ int4 load_key(const int32_t* __restrict__ keys, int64
 
 // ------------------------------------------------------------------ table build / search
 
+// The table buffer ends with one flag word behind the values: tvals[cap] != 0 when a key was
+// inserted more than once.
 __global__ void hash_clear_kernel(int4* tkeys, int* tvals, int64_t cap) {
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i < cap) {
     tkeys[i] = make_int4(WCN_EMPTY_BATCH, 0, 0, 0);
     tvals[i] = INT_MAX;
   }
+  if (i == 0) tvals[cap] = 0;
 }
 
 template <int METHOD>
@@ -64,9 +67,14 @@ __global__ void hash_insert_kernel(const int32_t* __restrict__ keys, int64_t n, 
   uint32_t slot = wcn_slot(wcn_hash4<METHOD>(key), cap);
   for (uint32_t p = 0; p < cap; ++p) {
     int4 cur = __ldcg(&tkeys[slot]);
-    if (cur.x == WCN_EMPTY_BATCH) cur = cas128(&tkeys[slot], empty, key);
-    if (cur.x == WCN_EMPTY_BATCH || wcn_key_eq(cur, key)) {
+    bool claimed = false;
+    if (cur.x == WCN_EMPTY_BATCH) {
+      cur = cas128(&tkeys[slot], empty, key);
+      claimed = cur.x == WCN_EMPTY_BATCH;
+    }
+    if (claimed || wcn_key_eq(cur, key)) {
       atomicMin(&tvals[slot], (int)i);  // smallest row index wins: deterministic
+      if (!claimed) tvals[cap] = 1;     // the key was there already: the keys are not distinct
       return;
     }
     slot = (slot + 1 == cap) ? 0u : slot + 1;
@@ -221,8 +229,9 @@ struct KernelGeom {
 };
 
 // One thread per (query m, offset k); m runs along the warp so the query load
-// and the nbr store are coalesced.  grid = (ceil(M/256), K).
-template <int METHOD>
+// and the nbr store are coalesced.  grid = (ceil(M/256), K).  COUNT: also leave the number
+// of hits of every block for the compaction.
+template <int METHOD, bool COUNT>
 __global__ void kmap_search_kernel(const int4* __restrict__ tkeys, const int* __restrict__ tvals,
                                    uint32_t cap, const int32_t* __restrict__ queries, int64_t M,
                                    KernelGeom g, int32_t* __restrict__ nbr,
@@ -239,7 +248,42 @@ __global__ void kmap_search_kernel(const int4* __restrict__ tkeys, const int* __
     found = wcn_lookup<METHOD>(tkeys, tvals, cap, q);
     nbr[(int64_t)k * M + m] = found;
   }
-  const int c = __syncthreads_count(found >= 0);
+  if (COUNT) {
+    const int c = __syncthreads_count(found >= 0);
+    if (threadIdx.x == 0) block_counts[(int64_t)k * gridDim.x + blockIdx.x] = c;
+  }
+}
+
+// Map of a coordinate set onto itself (the queries are the table's own keys, in row order;
+// stride 1, odd window).  When the keys are distinct the map is symmetric: row m sees row i at
+// offset k exactly when row i sees row m at the mirrored offset K-1-k.  Only the first half of
+// the offsets and the centre are probed; a hit also fills the mirrored entry, whose rows were
+// set to -1 beforehand.  With repeated keys (flag behind the table values) every offset is
+// probed as in kmap_search_kernel.
+template <int METHOD>
+__global__ void kmap_search_self_kernel(const int4* __restrict__ tkeys, const int* __restrict__ tvals,
+                                        uint32_t cap, const int32_t* __restrict__ queries, int64_t M,
+                                        KernelGeom g, int K, int32_t* __restrict__ nbr) {
+  const int k = blockIdx.y;
+  const bool distinct = __ldg(&tvals[cap]) == 0;
+  if (distinct && k > K / 2) return;
+  const int64_t m = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (m >= M) return;
+  int4 q = __ldg(reinterpret_cast<const int4*>(queries) + m);
+  const int l = k % g.kz, j = (k / g.kz) % g.ky, i = k / (g.kz * g.ky);
+  q.y += i - g.cx;
+  q.z += j - g.cy;
+  q.w += l - g.cz;
+  const int found = wcn_lookup<METHOD>(tkeys, tvals, cap, q);
+  nbr[(int64_t)k * M + m] = found;
+  if (distinct && k < K / 2 && found >= 0) nbr[(int64_t)(K - 1 - k) * M + found] = (int32_t)m;
+}
+
+// Per-block hit counts of a dense neighbour table, in the layout kmap_search_kernel<.., true> leaves.
+__global__ void kmap_count_kernel(const int32_t* __restrict__ nbr, int64_t M, int* __restrict__ block_counts) {
+  const int k = blockIdx.y;
+  const int64_t m = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int c = __syncthreads_count(m < M && __ldg(&nbr[(int64_t)k * M + m]) >= 0);
   if (threadIdx.x == 0) block_counts[(int64_t)k * gridDim.x + blockIdx.x] = c;
 }
 
@@ -446,7 +490,7 @@ inline unsigned grid_for(int64_t n) { return (unsigned)((n + kThreads - 1) / kTh
 
 extern "C" int wcn_hash_table_bytes(int64_t capacity, int64_t* bytes) {
   if (capacity <= 0 || !bytes) return WCN_ERR_INVALID_PARAMETERS;
-  *bytes = capacity * 20;
+  *bytes = capacity * 20 + 16;  // keys, values, duplicate flag
   return WCN_OK;
 }
 
@@ -556,7 +600,7 @@ extern "C" int wcn_kmap_search(const void* table, int64_t capacity, int hash_met
                                int64_t num_queries, const int32_t* stride, const int32_t* kernel_size,
                                int32_t num_offsets, int32_t* nbr, void* workspace, void* stream) {
   KernelGeom g;
-  if (!table || !kernel_size || !workspace || capacity <= 0 || capacity > 0x7FFFFFFFll || num_queries < 0 ||
+  if (!table || !kernel_size || capacity <= 0 || capacity > 0x7FFFFFFFll || num_queries < 0 ||
       !parse_stride(stride, &g.sx, &g.sy, &g.sz))
     return WCN_ERR_INVALID_PARAMETERS;
   g.kx = kernel_size[0]; g.ky = kernel_size[1]; g.kz = kernel_size[2];
@@ -571,9 +615,51 @@ extern "C" int wcn_kmap_search(const void* table, int64_t capacity, int hash_met
   const int4* tkeys = reinterpret_cast<const int4*>(table);
   const int* tvals = reinterpret_cast<const int*>(tkeys + capacity);
   dim3 grid(grid_for(num_queries), (unsigned)num_offsets);
-  WCN_DISPATCH_HASH(hash_method, (kmap_search_kernel<HM><<<grid, kThreads, 0, wcn_stream(stream)>>>(
-                                     tkeys, tvals, (uint32_t)capacity, queries, num_queries, g, nbr,
-                                     reinterpret_cast<int*>(workspace))));
+  if (workspace) {
+    WCN_DISPATCH_HASH(hash_method, (kmap_search_kernel<HM, true><<<grid, kThreads, 0, wcn_stream(stream)>>>(
+                                       tkeys, tvals, (uint32_t)capacity, queries, num_queries, g, nbr,
+                                       reinterpret_cast<int*>(workspace))));
+  } else {
+    WCN_DISPATCH_HASH(hash_method, (kmap_search_kernel<HM, false><<<grid, kThreads, 0, wcn_stream(stream)>>>(
+                                       tkeys, tvals, (uint32_t)capacity, queries, num_queries, g, nbr, nullptr)));
+  }
+  WCN_CHECK_LAUNCH();
+  return WCN_OK;
+}
+
+extern "C" int wcn_kmap_search_self(const void* table, int64_t capacity, int hash_method, const int32_t* keys,
+                                    int64_t num_keys, const int32_t* kernel_size, int32_t* nbr, void* stream) {
+  KernelGeom g;
+  if (!table || !kernel_size || capacity <= 0 || capacity > 0x7FFFFFFFll || num_keys < 0 || num_keys >= 0x7FFFFFFFll)
+    return WCN_ERR_INVALID_PARAMETERS;
+  g.sx = g.sy = g.sz = 1;
+  g.kx = kernel_size[0]; g.ky = kernel_size[1]; g.kz = kernel_size[2];
+  if (g.kx <= 0 || g.ky <= 0 || g.kz <= 0 || !(g.kx & 1) || !(g.ky & 1) || !(g.kz & 1)) return WCN_ERR_INVALID_PARAMETERS;
+  const int K = g.kx * g.ky * g.kz;
+  if (K > 65535) return WCN_ERR_INVALID_PARAMETERS;
+  g.cx = g.kx / 2; g.cy = g.ky / 2; g.cz = g.kz / 2;
+  if (num_keys == 0) return WCN_OK;
+  if (!keys || !nbr || (reinterpret_cast<uintptr_t>(keys) & 15)) return WCN_ERR_INVALID_PARAMETERS;
+  cudaStream_t st = wcn_stream(stream);
+  const int4* tkeys = reinterpret_cast<const int4*>(table);
+  const int* tvals = reinterpret_cast<const int*>(tkeys + capacity);
+  // rows of the mirrored half that nobody points at stay -1
+  if (K > 1)
+    cudaMemsetAsync(nbr + (int64_t)(K / 2 + 1) * num_keys, 0xFF, sizeof(int32_t) * (size_t)(K / 2) * (size_t)num_keys, st);
+  dim3 grid(grid_for(num_keys), (unsigned)K);
+  WCN_DISPATCH_HASH(hash_method, (kmap_search_self_kernel<HM><<<grid, kThreads, 0, st>>>(
+                                     tkeys, tvals, (uint32_t)capacity, keys, num_keys, g, K, nbr)));
+  WCN_CHECK_LAUNCH();
+  return WCN_OK;
+}
+
+extern "C" int wcn_kmap_count(const int32_t* nbr, int64_t num_queries, int32_t num_offsets, void* workspace,
+                              void* stream) {
+  if (num_queries < 0 || num_offsets <= 0 || num_offsets > 65535 || !workspace) return WCN_ERR_INVALID_PARAMETERS;
+  if (num_queries == 0) return WCN_OK;
+  if (!nbr) return WCN_ERR_INVALID_PARAMETERS;
+  dim3 grid(grid_for(num_queries), (unsigned)num_offsets);
+  kmap_count_kernel<<<grid, kThreads, 0, wcn_stream(stream)>>>(nbr, num_queries, reinterpret_cast<int*>(workspace));
   WCN_CHECK_LAUNCH();
   return WCN_OK;
 }

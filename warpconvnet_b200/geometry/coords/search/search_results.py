@@ -18,7 +18,7 @@ from typing import List, Literal, Optional, Tuple
 import torch
 from torch import Tensor
 
-from ...._native import check, lib, ptr, stream_ptr
+from ...._native import check, lib, ptr, query_bytes, stream_ptr
 
 
 class IntSearchResult:
@@ -60,13 +60,14 @@ class IntSearchResult:
         nbr, K, M = self._nbr, self._num_offsets, self._num_out
         dev = nbr.device
         ws = self._workspace
-        if ws is None:
-            if self._forward is None:
-                raise RuntimeError("dense kernel map without hit counts cannot be compacted")
+        if ws is None and self._forward is not None:
             # transposed view: the compact form is the forward map's with in/out exchanged
             fwd = self._forward
             self._in_maps, self._out_maps, self._offsets = fwd.out_maps, fwd.in_maps, fwd.offsets
             return
+        if ws is None:  # searched without hit counts: count now
+            ws = torch.empty(query_bytes("wcn_kmap_workspace_bytes", M, K), dtype=torch.uint8, device=dev)
+            check(lib().wcn_kmap_count(ptr(nbr), M, K, ptr(ws), stream_ptr(dev)), "wcn_kmap_count")
         offsets = torch.empty(K + 1, dtype=torch.int32, device=dev)
         check(lib().wcn_kmap_scan(ptr(ws), M, K, ptr(offsets), stream_ptr(dev)), "wcn_kmap_scan")
         offsets_cpu = offsets.cpu()  # the one host synchronisation of a compact map

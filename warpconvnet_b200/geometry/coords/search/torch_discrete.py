@@ -45,12 +45,15 @@ def _kernel_map_from_size(hashtable: TorchHashTable, batched_query_coords: Tenso
                           kernel_sizes: Tuple[int, ...], identity_map_index: Optional[int] = None,
                           return_type: Literal["indices", "offsets"] = "offsets",
                           skip_symmetric_kernel_map: bool = False,
-                          query_stride: Optional[Tuple[int, ...]] = None, num_in: Optional[int] = None):
+                          query_stride: Optional[Tuple[int, ...]] = None, num_in: Optional[int] = None,
+                          self_map: bool = False):
     """Search every position of a ``kernel_sizes`` window around each query.
 
     ``return_type="indices"`` returns ``found[K, M]`` (-1 = absent), "offsets" an
     :class:`IntSearchResult`.  With ``skip_symmetric_kernel_map`` only the first
-    K//2 positions are searched (torch_discrete.py:291-296).
+    K//2 positions are searched (torch_discrete.py:291-296).  ``self_map``: the queries are the
+    rows the table was built from, in the same order (odd window, stride 1); the native call
+    then probes half of the offsets and mirrors the rest when the rows are distinct.
     """
     dev = hashtable.device
     assert str(dev) == str(batched_query_coords.device)
@@ -68,12 +71,20 @@ def _kernel_map_from_size(hashtable: TorchHashTable, batched_query_coords: Tenso
     q = batched_query_coords.contiguous()
     M = q.shape[0]
     nbr = torch.empty((K, M), dtype=torch.int32, device=dev)
-    ws = torch.empty(query_bytes("wcn_kmap_workspace_bytes", M, K), dtype=torch.uint8, device=dev)
     ksz = (ctypes.c_int32 * 3)(*[int(k) for k in kernel_sizes])
     strd = (ctypes.c_int32 * 3)(*[int(s) for s in (query_stride or (1, 1, 1))])
-    check(lib().wcn_kmap_search(ptr(hashtable._table), hashtable.capacity, hashtable.hash_method.value, ptr(q), M,
-                                ctypes.addressof(strd), ctypes.addressof(ksz), K, ptr(nbr), ptr(ws), stream_ptr(dev)),
-          "wcn_kmap_search")
+    # hit counts are only needed by the compact form; IntSearchResult makes them on demand
+    ws = None
+    if (self_map and not skip_symmetric_kernel_map and all(k % 2 == 1 for k in kernel_sizes)
+            and all(int(s) == 1 for s in (query_stride or (1, 1, 1)))):
+        assert M == len(hashtable.vector_keys), "self_map needs the table's own rows as queries"
+        check(lib().wcn_kmap_search_self(ptr(hashtable._table), hashtable.capacity, hashtable.hash_method.value,
+                                         ptr(q), M, ctypes.addressof(ksz), ptr(nbr), stream_ptr(dev)),
+              "wcn_kmap_search_self")
+    else:
+        check(lib().wcn_kmap_search(ptr(hashtable._table), hashtable.capacity, hashtable.hash_method.value, ptr(q),
+                                    M, ctypes.addressof(strd), ctypes.addressof(ksz), K, ptr(nbr), None,
+                                    stream_ptr(dev)), "wcn_kmap_search")
     if return_type == "indices":
         return nbr
     assert return_type == "offsets"
@@ -127,4 +138,7 @@ def generate_kernel_map(batch_indexed_in_coords: Tensor, batch_indexed_out_coord
     return _kernel_map_from_size(hashtable, batch_indexed_out_coords, kernel_size,
                                  identity_map_index=identity_map_index, return_type="offsets",
                                  skip_symmetric_kernel_map=skip_symmetric_kernel_map, query_stride=stride,
-                                 num_in=batch_indexed_in_coords.shape[0])
+                                 num_in=batch_indexed_in_coords.shape[0],
+                                 self_map=(batch_indexed_out_coords.data_ptr() == batch_indexed_in_coords.data_ptr()
+                                           and batch_indexed_out_coords.shape == batch_indexed_in_coords.shape
+                                           and batch_indexed_in_coords.is_contiguous()))
