@@ -95,6 +95,15 @@ def main():
     down = generate_kernel_map(fine, coarse, (2, 2, 2), (2, 2, 2))
     ms = time_ms(lambda: down.swapped(num_in=n).neighbor_table(n), args.iters, flush)
     report("transposed_from_forward", ms, n, 4.0 * 8 * (m2 + n))
+    # tile order of the 3x3x3 table: read it twice (masks, copy), write it once, plus the row order
+    km3 = generate_kernel_map(fine, fine, (1, 1, 1), (3, 3, 3))
+
+    def tile_order():
+        km3._tiled = None
+        return km3.tiled_neighbor_table(n)
+
+    ms = time_ms(tile_order, args.iters, flush)
+    report("tile_order_3x3x3", ms, n, 4.0 * 27 * n * 3 + 8.0 * n)
     check_device_status(dev)
 
 
