@@ -127,6 +127,20 @@ class Geometry:
             feats = to_batched_features(feats, coords.offsets)
         return self.__class__(coords, feats, **{**self._extra_attributes, **kwargs})
 
+    def _derive(self, features: Tensor, coords: Optional[Coords] = None) -> "Geometry":
+        """Same kind of object with ``features`` (``[N, C]`` for the rows of ``coords``, default this
+        object's coordinates) and the same extra attributes.  For results whose row count is already
+        guaranteed by the kernel that made them; unlike ``replace`` it checks and converts nothing."""
+        new = object.__new__(self.__class__)
+        c = coords if coords is not None else self.batched_coordinates
+        f = object.__new__(CatFeatures)
+        f.batched_tensor = features
+        f.offsets = c.offsets
+        new.batched_coordinates = c
+        new.batched_features = f
+        new._extra_attributes = dict(self._extra_attributes)
+        return new
+
     def _apply_feature_transform(self, fn):
         return self.replace(batched_features=fn(self.feature_tensor))
 

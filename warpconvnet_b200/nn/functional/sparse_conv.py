@@ -450,7 +450,7 @@ def spatially_sparse_conv(
         ident = _identity_map(n, feats.device)
         ep = _merge_bias(epilogue, bias)
         out = _implicit_gemm_forward_logic(feats, weight, ident, n, compute_dtype, epilogue=ep)
-        return input_sparse_tensor.replace(batched_features=out)
+        return input_sparse_tensor._derive(out)
 
     in_tensor_stride = input_sparse_tensor.tensor_stride
     if in_tensor_stride is None:
@@ -494,21 +494,26 @@ def spatially_sparse_conv(
             out = _implicit_gemm_forward_logic(feats, weight, kernel_map, num_out, effective_compute_dtype,
                                                epilogue=ep)
 
-    # Output coordinates: the input's own coordinate object when they are unchanged, the
-    # target's for a transposed convolution, else a new one that already knows its
-    # batch-indexed form (so nothing is rebuilt layer after layer).
-    if output_spatially_sparse_tensor is not None and order == POINT_ORDERING.RANDOM:
-        src = output_spatially_sparse_tensor.batched_coordinates
-        out_ic = IntCoords(src.batched_tensor, offsets=src.offsets).share_derived(src)
-    elif all(s == 1 for s in _stride) and order == POINT_ORDERING.RANDOM:
-        src = input_sparse_tensor.batched_coordinates
-        out_ic = IntCoords(src.batched_tensor, offsets=src.offsets).share_derived(src)
-    elif order == POINT_ORDERING.RANDOM:
-        src = strided_coordinates(input_sparse_tensor.batched_coordinates, _stride)
-        out_ic = IntCoords(src.batched_tensor, offsets=src.offsets).share_derived(src)
-    else:
-        out_ic = IntCoords(out_coords[:, 1:], offsets=out_offsets if out_offsets.device.type == "cpu" else out_offsets.cpu())
-        out_ic._bcoords = out_coords
+    # Output coordinates: the input's own coordinate object when they are unchanged, the target's for
+    # a transposed convolution, the cached strided set otherwise; all of them already know their
+    # batch-indexed form and hash table, so nothing is rebuilt layer after layer.
+    if order == POINT_ORDERING.RANDOM:
+        own = False
+        if output_spatially_sparse_tensor is not None:
+            out_ic = output_spatially_sparse_tensor.batched_coordinates
+        elif all(s == 1 for s in _stride):
+            out_ic = input_sparse_tensor.batched_coordinates
+        else:
+            out_ic, own = strided_coordinates(input_sparse_tensor.batched_coordinates, _stride), True
+        if out_ic.tensor_stride != out_tensor_stride:
+            if own and out_ic.tensor_stride is None:
+                out_ic.tensor_stride = out_tensor_stride  # the cached set is labelled once
+            else:  # same rows under another stride label: a view that shares the derived data
+                out_ic = IntCoords(out_ic.batched_tensor, offsets=out_ic.offsets,
+                                   tensor_stride=out_tensor_stride).share_derived(out_ic)
+        return input_sparse_tensor._derive(out, out_ic)
+    out_ic = IntCoords(out_coords[:, 1:], offsets=out_offsets if out_offsets.device.type == "cpu" else out_offsets.cpu())
+    out_ic._bcoords = out_coords
     return input_sparse_tensor.replace(batched_coordinates=out_ic, batched_features=out,
                                        tensor_stride=out_tensor_stride)
 
