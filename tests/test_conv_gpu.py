@@ -266,14 +266,55 @@ def test_backward_matches_explicit_formulas():
         yr = yr.index_add(0, torch.from_numpy(o[s:e]).long(), xr[torch.from_numpy(i[s:e]).long()] @ wr[k])
     go = torch.randn(n, 12, generator=torch.Generator().manual_seed(2))
     yr.backward(go)
-    for algo in (ALGO.EXPLICIT_GEMM, ALGO.IMPLICIT_GEMM):
+    from warpconvnet_b200 import SPARSE_CONV_BWD_ALGO_MODE as BWD
+    for algo, bwd in ((ALGO.EXPLICIT_GEMM, BWD.EXPLICIT_GEMM), (ALGO.IMPLICIT_GEMM, BWD.EXPLICIT_GEMM),
+                      (ALGO.IMPLICIT_GEMM, BWD.IMPLICIT_GEMM), (ALGO.AUTO, [BWD.EXPLICIT_GEMM, BWD.CUTLASS_IMPLICIT_GEMM])):
         xg = x.clone().to(DEV).requires_grad_(True)
         wg = w.clone().to(DEV).requires_grad_(True)
         vox = make_voxels(coords, xg)
-        y = spatially_sparse_conv(vox, wg, 3, fwd_algo=algo)
+        y = spatially_sparse_conv(vox, wg, 3, fwd_algo=algo, bwd_algo=bwd)
         y.feature_tensor.backward(go.to(DEV))
         assert rel_l2(xg.grad.cpu().numpy(), xr.grad.numpy()) < 1e-4
         assert rel_l2(wg.grad.cpu().numpy(), wr.grad.numpy()) < 1e-4
+
+
+def test_backward_native_dx_strided_and_transposed_fp16():
+    """dX of a stride-2 convolution and of its transposed counterpart through the forward kernel on
+    the swapped table (tensor-core path, fp16) against autograd over the explicit formulas in fp32."""
+    from warpconvnet_b200 import SPARSE_CONV_BWD_ALGO_MODE as BWD
+    n, c_in, c_out = 20000, 32, 64
+    coords, x, _ = _layer_case(n, c_in, c_out, 21, "raster_crop")
+    g = torch.Generator().manual_seed(4)
+    w = torch.randn(8, c_in, c_out, generator=g) * 0.1
+    xq, wq = x.half(), w.half()
+    xg = xq.clone().to(DEV).requires_grad_(True)
+    vox = make_voxels(coords, xg)
+    down = spatially_sparse_conv(vox, wq.to(DEV), 2, stride=2, fwd_algo=ALGO.IMPLICIT_GEMM, bwd_algo=BWD.IMPLICIT_GEMM)
+    go = torch.randn(down.feature_tensor.shape, generator=g).half()
+    down.feature_tensor.backward(go.to(DEV))
+    # reference: the same map from the oracle, explicit formulas in fp32
+    out_c, _ = km.stride_coords(coords, (2, 2, 2))
+    i, o, f, _ = km.generate_kernel_map(coords, out_c, (2, 2, 2), (2, 2, 2))
+    # the product's strided rows are in first-occurrence order, as the oracle's: same row numbering
+    ref = torch.zeros(n, c_in)
+    for k in range(8):
+        s, e = int(f[k]), int(f[k + 1])
+        ref.index_add_(0, torch.from_numpy(i[s:e]).long(), go.float()[torch.from_numpy(o[s:e]).long()] @ wq.float()[k].T)
+    assert rel_l2(xg.grad.float().cpu().numpy(), ref.numpy()) < 1e-2
+    # transposed convolution back up: its dX reads the forward (down) table
+    wt = (torch.randn(8, c_out, c_in, generator=g) * 0.1).half()
+    cg = down.feature_tensor.detach().clone().requires_grad_(True)
+    up = spatially_sparse_conv(down.replace(batched_features=cg), wt.to(DEV), 2, stride=2, transposed=True,
+                               output_spatially_sparse_tensor=vox, fwd_algo=ALGO.IMPLICIT_GEMM,
+                               bwd_algo=BWD.IMPLICIT_GEMM)
+    gu = torch.randn(n, c_in, generator=g).half()
+    up.feature_tensor.backward(gu.to(DEV))
+    ref2 = torch.zeros(len(out_c), c_out)
+    for k in range(8):  # up[i] += coarse[o] @ wt[k]  =>  d coarse[o] += d up[i] @ wt[k]^T
+        s, e = int(f[k]), int(f[k + 1])
+        ref2.index_add_(0, torch.from_numpy(o[s:e]).long(), gu.float()[torch.from_numpy(i[s:e]).long()] @ wt.float()[k].T)
+    assert rel_l2(cg.grad.float().cpu().numpy(), ref2.numpy()) < 1e-2
+    check_device_status(DEV)
 
 
 def test_surface_errors_and_shortcuts():

@@ -359,15 +359,30 @@ def _cached_table(voxels: Optional[Voxels], coords: Tensor):
 # --------------------------------------------------------------------------- autograd
 
 
+def _normalize_bwd_algo(algo) -> SPARSE_CONV_BWD_ALGO_MODE:
+    """Enum | str | list of either -> one algorithm; with a list the first native entry wins
+    (no tuner), as for the forward algorithm."""
+    items = list(algo) if isinstance(algo, (list, tuple)) else [algo]
+    items = [SPARSE_CONV_BWD_ALGO_MODE(a.lower()) if isinstance(a, str) else a for a in items]
+    for a in items:
+        if a != SPARSE_CONV_BWD_ALGO_MODE.EXPLICIT_GEMM:
+            return a
+    return items[0]
+
+
 class _SparseConvFunction(torch.autograd.Function):
-    """Forward through the native kernels; backward with the explicit-GEMM
-    formulas (reference :314-355) on the compact map: dX[in_k] += dY[out_k] @ W_k^T,
-    dW_k = X[in_k]^T @ dY[out_k]."""
+    """Forward through the native kernels.  Backward: dW_k = X[in_k]^T @ dY[out_k] per offset
+    (reference :314-355, explicit formulas on the compact map); dX either by the same explicit
+    formulas, dX[in_k] += dY[out_k] @ W_k^T, or — for the implicit backward algorithms, the
+    reference's AD gather-scatter with the maps swapped and W^T (:472-480, 591-604) — as ONE
+    launch of the forward kernel over the transposed neighbour table with the weights transposed."""
 
     @staticmethod
-    def forward(ctx, in_features, weight, kernel_map, num_out_coords, algo, compute_dtype, epilogue):
+    def forward(ctx, in_features, weight, kernel_map, num_out_coords, algo, compute_dtype, epilogue,
+                bwd_algo=SPARSE_CONV_BWD_ALGO_MODE.EXPLICIT_GEMM):
         ctx.kernel_map = kernel_map
         ctx.compute_dtype = compute_dtype
+        ctx.bwd_algo = bwd_algo
         ctx.save_for_backward(in_features, weight)
         if algo == SPARSE_CONV_FWD_ALGO_MODE.EXPLICIT_GEMM:
             return _explicit_gemm_forward_logic(in_features, weight, kernel_map, num_out_coords, compute_dtype)
@@ -380,18 +395,30 @@ class _SparseConvFunction(torch.autograd.Function):
         km = ctx.kernel_map
         dt = ctx.compute_dtype if ctx.compute_dtype is not None else x.dtype
         xc, wc, gc = x.to(dt), w.to(dt), grad_output.contiguous().to(dt)
-        gx = torch.zeros_like(xc)
-        gw = torch.zeros_like(wc)
-        offsets, in_maps, out_maps = km.offsets, km.in_maps, km.out_maps
-        for k in range(len(km)):
-            s, e = int(offsets[k]), int(offsets[k + 1])
-            if e == s:
-                continue
-            go = _gather_rows(gc, out_maps[s:e])
-            xi = _gather_rows(xc, in_maps[s:e])
-            _scatter_add_rows(torch.matmul(go, wc[k].T), in_maps[s:e], gx)
-            gw[k] = torch.matmul(xi.T, go)
-        return gx.to(x.dtype), gw.to(w.dtype), None, None, None, None, None
+        need_gx, need_gw = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
+        native_dx = (need_gx and ctx.bwd_algo != SPARSE_CONV_BWD_ALGO_MODE.EXPLICIT_GEMM and gc.is_cuda
+                     and dt in (torch.float32, torch.float16, torch.bfloat16) and x.shape[0] > 0)
+        gx = None
+        if native_dx:
+            with torch.no_grad():
+                wt = wc.detach().transpose(1, 2).contiguous()  # [K, C_out, C_in]
+                gx = sparse_conv_fused(gc.detach(), wt, km.swapped(num_in=x.shape[0]), x.shape[0])
+        elif need_gx:
+            gx = torch.zeros_like(xc)
+        gw = torch.zeros_like(wc) if need_gw else None
+        if need_gw or (need_gx and not native_dx):
+            offsets, in_maps, out_maps = km.offsets, km.in_maps, km.out_maps
+            for k in range(len(km)):
+                s, e = int(offsets[k]), int(offsets[k + 1])
+                if e == s:
+                    continue
+                go = _gather_rows(gc, out_maps[s:e])
+                if need_gx and not native_dx:
+                    _scatter_add_rows(torch.matmul(go, wc[k].T), in_maps[s:e], gx)
+                if need_gw:
+                    gw[k] = torch.matmul(_gather_rows(xc, in_maps[s:e]).T, go)
+        return (gx.to(x.dtype) if gx is not None else None, gw.to(w.dtype) if gw is not None else None,
+                None, None, None, None, None, None)
 
 
 # --------------------------------------------------------------------------- entry point
@@ -478,7 +505,8 @@ def spatially_sparse_conv(
 
     if algo == SPARSE_CONV_FWD_ALGO_MODE.EXPLICIT_GEMM and epilogue is None:
         if needs_grad:
-            out = _SparseConvFunction.apply(feats, weight, kernel_map, num_out, algo, effective_compute_dtype, None)
+            out = _SparseConvFunction.apply(feats, weight, kernel_map, num_out, algo, effective_compute_dtype, None,
+                                            _normalize_bwd_algo(bwd_algo))
         else:
             out = _explicit_gemm_forward_logic(feats, weight, kernel_map, num_out, effective_compute_dtype)
         if bias is not None:
@@ -489,7 +517,8 @@ def spatially_sparse_conv(
             if epilogue is not None:
                 raise RuntimeError("a fused epilogue is an inference feature; run under torch.no_grad()")
             out = _SparseConvFunction.apply(feats, weight, kernel_map, num_out,
-                                            SPARSE_CONV_FWD_ALGO_MODE.IMPLICIT_GEMM, effective_compute_dtype, ep)
+                                            SPARSE_CONV_FWD_ALGO_MODE.IMPLICIT_GEMM, effective_compute_dtype, ep,
+                                            _normalize_bwd_algo(bwd_algo))
         else:
             out = _implicit_gemm_forward_logic(feats, weight, kernel_map, num_out, effective_compute_dtype,
                                                epilogue=ep)
