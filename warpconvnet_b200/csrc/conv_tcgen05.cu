@@ -238,6 +238,22 @@ __device__ __forceinline__ uint32_t subtiles_at(uint32_t m0, uint32_t m1, uint32
   return ((m0 >> k) & 1u) | (((m1 >> k) & 1u) << 1) | (((m2 >> k) & 1u) << 2) | (((m3 >> k) & 1u) << 3);
 }
 
+// Up to N active offsets taken from the low end of `rest` (bit k = offset k still to do);
+// ku[u] = -1 beyond the last one.  Returns how many were taken.
+template <int N> __device__ __forceinline__ int pop_offsets(uint32_t& rest, int (&ku)[N]) {
+  int n = 0;
+#pragma unroll
+  for (int u = 0; u < N; ++u) {
+    ku[u] = -1;
+    if (rest) {
+      ku[u] = __ffs(rest) - 1;
+      rest &= rest - 1;
+      n = u + 1;
+    }
+  }
+  return n;
+}
+
 // Ring cursor: slot index and the parity of the phase the slot is in.
 struct Ring {
   int slot, phase, depth;
@@ -368,6 +384,22 @@ conv_tcgen05_kernel(const ConvTcParams p) {
         uint32_t rest = ctl->info_mask[ib][0] | ctl->info_mask[ib][1] | ctl->info_mask[ib][2] | ctl->info_mask[ib][3];
         mbar_arrive(bar(&ctl->info_empty[ib]));  // only the masks were needed
         if (++ib == 2) { ib = 0; iphase ^= 1; }
+        // One channel slice per offset (KB == 1) and KBC > 1: a ring slot spans KBC consecutive
+        // ACTIVE OFFSETS instead of KBC channel slices of one offset, so narrow layers get the same
+        // fat slots as wide ones.  All roles take the offsets off the mask in the same groups.
+        while (KBC > 1 && KB == 1 && rest && ok) {
+          int ku[KBC];
+          const int nu = pop_offsets<KBC>(rest, ku);
+          if (!mbar_wait(bar(&ctl->b_empty[rb.slot]), rb.phase ^ 1, p.dev_status)) { ok = false; break; }
+          const uint32_t fullb = bar(&ctl->b_full[rb.slot]);
+          mbar_expect_tx(fullb, (uint32_t)(nu * B_BYTES));
+#pragma unroll
+          for (int u = 0; u < KBC; ++u)
+            if (ku[u] >= 0)
+              bulk_copy_g2s(b_base + rb.slot * B_SLOT + u * B_BYTES,
+                            p.wpacked + ((int64_t)ku[u] * p.c_out + n0) * RB, (uint32_t)B_BYTES, fullb);
+          rb.advance();
+        }
         while (rest && ok) {
           const int k = __ffs(rest) - 1;
           rest &= rest - 1;
@@ -409,6 +441,39 @@ conv_tcgen05_kernel(const ConvTcParams p) {
       const uint32_t mk2 = ctl->info_mask[ib][2], mk3 = ctl->info_mask[ib][3];
       const int32_t* tab = rows_idx + ib * IDX_INTS + gwarp * ROWS_PER_WARP + sub_row;
       uint32_t rest = mk0 | mk1 | mk2 | mk3;
+      while (KBC > 1 && KB == 1 && rest && ok) {  // slots that span offsets (see the weight loader)
+        int ku[KBC];
+        pop_offsets<KBC>(rest, ku);
+        uint32_t gbu[KBC], gany = 0;
+#pragma unroll
+        for (int u = 0; u < KBC; ++u) {
+          gbu[u] = ku[u] >= 0 ? subtiles_at(mk0, mk1, mk2, mk3, ku[u]) : 0u;
+          gany |= gbu[u];
+        }
+        for (uint32_t gb = gany; gb; gb &= gb - 1) {
+          const int g = __ffs(gb) - 1;
+          if (!mbar_wait(bar(&ctl->a_empty[ra.slot]), ra.phase ^ 1, p.dev_status)) { ok = false; break; }
+          const uint32_t a_dst = a_base + ra.slot * A_SLOT;
+          const char* fbase = p.feats + chunk * 16;
+#pragma unroll
+          for (int u = 0; u < KBC; ++u) {
+            if ((gbu[u] >> g) & 1u) {  // sub-tiles of offsets this row block does not have stay unused
+              const int32_t* rk = tab + (g * K + ku[u]) * BLOCK_M;
+              int src[NJ];
+#pragma unroll
+              for (int j = 0; j < NJ; ++j) src[j] = rk[j * RPI];
+#pragma unroll
+              for (int j = 0; j < NJ; ++j) {
+                const bool have = src[j] >= 0;
+                cp_async16(a_dst + u * A_BYTES + aoff[j], have ? fbase + (int64_t)src[j] * p.c_in * 2 : p.feats,
+                           have ? 16u : 0u);
+              }
+            }
+          }
+          cp_async_arrive(bar(&ctl->a_full[ra.slot]));
+          ra.advance();
+        }
+      }
       while (rest && ok) {
         const int k = __ffs(rest) - 1;
         rest &= rest - 1;
@@ -472,6 +537,48 @@ conv_tcgen05_kernel(const ConvTcParams p) {
         tc_fence_after();
         uint32_t started = 0;
         uint32_t rest = uni;
+        while (KBC > 1 && KB == 1 && rest && ok) {  // slots that span offsets (see the weight loader)
+          int ku[KBC];
+          pop_offsets<KBC>(rest, ku);
+          uint32_t gbu[KBC], gany = 0;
+#pragma unroll
+          for (int u = 0; u < KBC; ++u) {
+            gbu[u] = ku[u] >= 0 ? subtiles_at(mk0, mk1, mk2, mk3, ku[u]) : 0u;
+            gany |= gbu[u];
+          }
+          if (!mbar_wait(bar(&ctl->b_full[rb.slot]), rb.phase, p.dev_status)) { ok = false; break; }
+          const uint32_t b_slot = b_base + rb.slot * B_SLOT;
+          for (uint32_t gb = gany; gb; gb &= gb - 1) {
+            const int g = __ffs(gb) - 1;
+            if (!mbar_wait(bar(&ctl->a_full[ra.slot]), ra.phase, p.dev_status)) { ok = false; break; }
+            if (((uint32_t)g & 1u) != issuer) {  // the other issuer's slot
+              mbar_arrive(bar(&ctl->a_empty[ra.slot]));
+              ra.advance();
+              continue;
+            }
+            tc_fence_after();
+            const uint32_t a_slot = a_base + ra.slot * A_SLOT;
+            const uint32_t d = tmem_base + (uint32_t)((ab * G + g) * p.cols);
+            uint32_t acc = (started >> g) & 1u;
+#pragma unroll
+            for (int u = 0; u < KBC; ++u) {
+              if ((gbu[u] >> g) & 1u) {
+                const uint64_t adesc = smem_desc<RB>(a_slot + u * A_BYTES);
+                const uint64_t bdesc = smem_desc<RB>(b_slot + u * B_BYTES);
+#pragma unroll
+                for (int kk = 0; kk < BK / 16; ++kk)
+                  umma_f16(d, adesc + (uint64_t)(kk * 2), bdesc + (uint64_t)(kk * 2), idesc,
+                           (acc | (uint32_t)kk) ? 1u : 0u);
+                acc = 1u;
+              }
+            }
+            started |= 1u << g;
+            umma_commit(bar(&ctl->a_empty[ra.slot]));
+            ra.advance();
+          }
+          umma_commit(bar(&ctl->b_empty[rb.slot]));
+          rb.advance();
+        }
         while (rest && ok) {
           const int k = __ffs(rest) - 1;
           rest &= rest - 1;
@@ -679,11 +786,13 @@ bool plan_launch(ConvTcParams& p, int bk, size_t* smem, dim3* grid) {
 #endif
   const int kb_total = p.c_in / bk;
   // Channel slices per ring slot: as many as give a 32 KiB row slot, fewer if the rings would not fit.
+  // (with a single slice per offset the slot spans that many active offsets instead)
   int kbc = (int)((32 * 1024) / a_unit);
-  if (kbc > kb_total) kbc = kb_total;
+  if (kb_total > 1 && kbc > kb_total) kbc = kb_total;
+  if (kb_total == 1 && kbc > p.K) kbc = p.K;
   if (kbc > 4) kbc = 4;
   if (kbc < 1) kbc = 1;
-  while (kb_total % kbc != 0) --kbc;
+  while (kb_total > 1 && kb_total % kbc != 0) --kbc;
   size_t fixed = 0, a_stage = 0, b_stage = 0;
   for (;;) {  // two staged neighbour tables + a few row slots and 2 weight slots must fit
     fixed = 1024 + sizeof(Control) + 2 * (size_t)g * p.K * BLOCK_M * 4 + 128;
@@ -691,7 +800,7 @@ bool plan_launch(ConvTcParams& p, int bk, size_t* smem, dim3* grid) {
     b_stage = kbc * b_unit;
     if (fixed + (kbc > 1 ? 3 : 4) * a_stage + 2 * b_stage <= limit) break;
     if (kbc > 1) {
-      do { --kbc; } while (kb_total % kbc != 0);
+      do { --kbc; } while (kb_total > 1 && kb_total % kbc != 0);
       continue;
     }
     if (g == 1) return false;
