@@ -272,6 +272,20 @@ int wcn_conv_fwd(int algo, const void* feats, int64_t num_in, const void* weight
                  const float* shift, const void* residual, int relu, void* out, int out_dtype,
                  int32_t* dev_status, void* stream);
 
+/* Weight gradient of the convolution above, accumulated into grad_weight[K, c_in, c_out] (fp32; the
+ * caller zeroes it):
+ *   grad_weight[k] += feats[nbr[k*M + m], :]^T (outer) grad_out[m, :]   over rows m with nbr >= 0
+ * feats / grad_out share `dtype` (f16 or bf16), fp32 accumulation on the tensor cores; the partial
+ * sums of different row ranges are added with atomics, so the last bits vary from run to run.
+ * Needs c_in % 32 == 0, c_out % 32 == 0, c_out <= 256; else WCN_ERR_UNSUPPORTED_CONFIG (callers fall
+ * back to a GEMM per offset).  `nbr` is the plain (not tiled) neighbour table of the forward pass.
+ * Replaces cutlass_gemm_trAB_gather (warpconvnet/csrc/warpconvnet_pybind.cpp:511-624) and
+ * split_k_implicit_gemm (warpconvnet/csrc/implicit_gemm_split_k.cu:63-393) with the per-offset loop
+ * around them (warpconvnet/nn/functional/sparse_conv.py:591-604). */
+int wcn_conv_wgrad(const void* feats, int64_t num_in, const void* grad_out, const int32_t* nbr,
+                   int64_t num_out, int32_t num_offsets, int32_t c_in, int32_t c_out, int dtype,
+                   float* grad_weight, int32_t* dev_status, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

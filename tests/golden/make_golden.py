@@ -1,7 +1,7 @@
 """Generate the golden fixtures in this folder FROM THE REFERENCE ITSELF.
 
-Run on a machine that has the reference tree (``WCN_REFERENCE_ROOT``, default
-``/root/reference``):
+Run on a machine that has the reference tree (its location is taken from the
+environment variable ``WCN_REFERENCE_ROOT``):
 
     python tests/golden/make_golden.py
 

@@ -278,6 +278,39 @@ def test_backward_matches_explicit_formulas():
         assert rel_l2(wg.grad.cpu().numpy(), wr.grad.numpy()) < 1e-4
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("K,c_in,c_out,n", [(27, 64, 64, 30000), (27, 128, 128, 20000), (27, 32, 32, 30000),
+                                            (27, 96, 96, 20000), (27, 256, 256, 6000), (27, 128, 96, 20000),
+                                            (8, 64, 128, 30000), (27, 32, 64, 300)])
+def test_wgrad_tcgen05_matches_explicit_formulas(dtype, K, c_in, c_out, n):
+    """dW on the tensor cores (operands read as MN-major tiles, units of 64 or 32 channels grouped on
+    the M side, fp32 accumulation, split over row ranges) against a per-offset fp32 GEMM on the same
+    quantised operands."""
+    from warpconvnet_b200.nn.functional.sparse_conv import sparse_conv_wgrad
+    coords, _, _ = _layer_case(n, 4, 4, 91, "raster_crop")
+    coords = np.ascontiguousarray(coords[np.argsort(km.morton_code(coords[:, 1:]), kind="stable")])
+    c = torch.from_numpy(coords).to(DEV)
+    g = torch.Generator().manual_seed(K * c_in + c_out)
+    if K == 27:
+        kmap, n_out = generate_kernel_map(c, c, (1, 1, 1), (3, 3, 3)), n
+        i, o, f, _ = km.generate_kernel_map(coords, coords, (1, 1, 1), (3, 3, 3))
+    else:
+        coarse, _ = stride_coords(c, (2, 2, 2))
+        kmap, n_out = generate_kernel_map(c, coarse, (2, 2, 2), (2, 2, 2)), len(coarse)
+        i, o, f, _ = km.generate_kernel_map(coords, coarse.cpu().numpy(), (2, 2, 2), (2, 2, 2))
+    x = torch.randn(n, c_in, generator=g).to(dtype)
+    go = torch.randn(n_out, c_out, generator=g).to(dtype)
+    gw = sparse_conv_wgrad(x.to(DEV), go.to(DEV), kmap, n_out)
+    check_device_status(DEV)
+    assert gw is not None and gw.dtype == torch.float32 and tuple(gw.shape) == (K, c_in, c_out)
+    ref = torch.zeros(K, c_in, c_out)
+    for k in range(K):
+        s, e = int(f[k]), int(f[k + 1])
+        if e > s:
+            ref[k] = x.float()[torch.from_numpy(i[s:e]).long()].T @ go.float()[torch.from_numpy(o[s:e]).long()]
+    assert rel_l2(gw.cpu().numpy(), ref.numpy()) < 1e-4  # fp32 accumulation of exact products
+
+
 def test_backward_native_dx_strided_and_transposed_fp16():
     """dX of a stride-2 convolution and of its transposed counterpart through the forward kernel on
     the swapped table (tensor-core path, fp16) against autograd over the explicit formulas in fp32."""

@@ -20,7 +20,7 @@ import torch
 from .. import POINT_ORDERING, Voxels, generate_kernel_map, stride_coords
 from .._native import CONV_AUTO, CONV_SIMT, CONV_TCGEN05, check_device_status
 from ..datasets import synthetic
-from ..nn.functional.sparse_conv import sparse_conv_fused
+from ..nn.functional.sparse_conv import sparse_conv_fused, sparse_conv_wgrad
 
 DT = {"fp16": torch.float16, "bf16": torch.bfloat16, "fp32": torch.float32}
 ALGOS = {"auto": CONV_AUTO, "simt": CONV_SIMT, "tcgen05": CONV_TCGEN05}
@@ -58,7 +58,8 @@ def main():
     ap.add_argument("--mode", default="raster_crop")
     ap.add_argument("--channels", default="32,64,128,256")
     ap.add_argument("--dtypes", default="fp16,bf16")
-    ap.add_argument("--kinds", default="conv3,down2,up2")
+    ap.add_argument("--kinds", default="conv3,down2,up2",
+                    help="conv3, down2, up2 (forward); append :dx or :dw for the two backward launches, e.g. conv3:dw")
     ap.add_argument("--algo", default="auto", choices=list(ALGOS))
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--no-sort", action="store_true", help="keep the generator's random row order")
@@ -81,7 +82,8 @@ def main():
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     g = torch.Generator(device="cpu").manual_seed(0)
 
-    for kind in args.kinds.split(","):
+    for kind_arg in args.kinds.split(","):
+        kind, _, which = kind_arg.partition(":")
         kmap, n_in, n_out = maps[kind]
         nbr = kmap.neighbor_table(n_out)
         pairs = int((nbr >= 0).sum().item())
@@ -92,7 +94,15 @@ def main():
                 x = torch.randn(n_in, c, generator=g).to(dev, dt)
                 bound = (3.0 / (K * c)) ** 0.5 * 1.73
                 w = ((torch.rand(K, c, c, generator=g) * 2 - 1) * bound).to(dev, dt)
-                fn = lambda: sparse_conv_fused(x, w, kmap, n_out, algo=ALGOS[args.algo])
+                if which == "dw":    # weight gradient: X^T dY over the rows, one launch
+                    gy = torch.randn(n_out, c, generator=g).to(dev, dt)
+                    fn = lambda: sparse_conv_wgrad(x, gy, kmap, n_out)
+                elif which == "dx":  # input gradient: the forward kernel over the transposed table
+                    gy = torch.randn(n_out, c, generator=g).to(dev, dt)
+                    wt, kt = w.transpose(1, 2).contiguous(), kmap.swapped(num_in=n_in)
+                    fn = lambda: sparse_conv_fused(gy, wt, kt, n_in, algo=ALGOS[args.algo])
+                else:
+                    fn = lambda: sparse_conv_fused(x, w, kmap, n_out, algo=ALGOS[args.algo])
                 ms = time_ms(fn, args.iters, flush)
                 check_device_status(dev)
                 es = 4 if dt == torch.float32 else 2
@@ -100,7 +110,7 @@ def main():
                 byts = es * (n_in * c + n_out * c + K * c * c) + 4.0 * n_out * K
                 t_tc, t_hbm = flop / (tflops * 1e12), byts / (hbm * 1e9)
                 print(json.dumps({
-                    "kind": kind, "c": c, "dtype": dname, "voxels_in": n_in, "voxels_out": n_out, "pairs": pairs,
+                    "kind": kind_arg, "c": c, "dtype": dname, "voxels_in": n_in, "voxels_out": n_out, "pairs": pairs,
                     "pairs_per_out": pairs / n_out, "ms": ms, "useful_tflops": flop / ms / 1e9,
                     "alg_gbs": byts / ms / 1e6, "bound": "tensor" if t_tc > t_hbm else "hbm",
                     "roofline_frac": max(t_tc, t_hbm) / (ms * 1e-3), "peaks": src,

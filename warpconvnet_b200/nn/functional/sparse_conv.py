@@ -359,6 +359,26 @@ def _cached_table(voxels: Optional[Voxels], coords: Tensor):
 # --------------------------------------------------------------------------- autograd
 
 
+def sparse_conv_wgrad(in_features: Tensor, grad_output: Tensor, kernel_map: IntSearchResult,
+                      num_out_coords: int) -> Optional[Tensor]:
+    """``dW[k] = X[in_k]^T @ dY[out_k]`` for every kernel offset in one launch on the tensor cores
+    (fp16 / bf16 operands, fp32 result ``[K, C_in, C_out]``), or None when the shape is not one the
+    native kernel takes (the caller then uses a GEMM per offset)."""
+    require_cuda(in_features, "in_features")
+    x, g = in_features.contiguous(), grad_output.contiguous()
+    K, c_in, c_out = len(kernel_map), x.shape[1], g.shape[1]
+    if (x.dtype not in (torch.float16, torch.bfloat16) or g.dtype != x.dtype or c_in % 32 or c_out % 32
+            or c_out > 256 or K > 32 or x.shape[0] == 0 or num_out_coords == 0):
+        return None
+    dev = x.device
+    nbr = kernel_map.neighbor_table(num_out_coords)
+    gw = torch.zeros((K, c_in, c_out), dtype=torch.float32, device=dev)
+    check(lib().wcn_conv_wgrad(ptr(x), x.shape[0], ptr(g), ptr(nbr), num_out_coords, K, c_in, c_out,
+                               dtype_code(x.dtype), ptr(gw), ptr(device_status(dev)), stream_ptr(dev)),
+          "wcn_conv_wgrad")
+    return gw
+
+
 def _normalize_bwd_algo(algo) -> SPARSE_CONV_BWD_ALGO_MODE:
     """Enum | str | list of either -> one algorithm; with a list the first native entry wins
     (no tuner), as for the forward algorithm."""
@@ -371,11 +391,13 @@ def _normalize_bwd_algo(algo) -> SPARSE_CONV_BWD_ALGO_MODE:
 
 
 class _SparseConvFunction(torch.autograd.Function):
-    """Forward through the native kernels.  Backward: dW_k = X[in_k]^T @ dY[out_k] per offset
-    (reference :314-355, explicit formulas on the compact map); dX either by the same explicit
-    formulas, dX[in_k] += dY[out_k] @ W_k^T, or — for the implicit backward algorithms, the
-    reference's AD gather-scatter with the maps swapped and W^T (:472-480, 591-604) — as ONE
-    launch of the forward kernel over the transposed neighbour table with the weights transposed."""
+    """Forward through the native kernels.  Backward with the explicit algorithm: the reference's
+    formulas on the compact map (:314-355), dX[in_k] += dY[out_k] @ W_k^T and
+    dW_k = X[in_k]^T @ dY[out_k], a GEMM per offset.  With the implicit algorithms (the reference's
+    AD gather-scatter with the maps swapped and W^T, and its trAB gather / split-K kernels,
+    :472-480, 591-604): dX is ONE launch of the forward kernel over the transposed neighbour table
+    with the weights transposed, dW ONE launch of the tensor-core weight-gradient kernel (shapes it
+    does not take fall back to the per-offset GEMMs)."""
 
     @staticmethod
     def forward(ctx, in_features, weight, kernel_map, num_out_coords, algo, compute_dtype, epilogue,
@@ -405,7 +427,14 @@ class _SparseConvFunction(torch.autograd.Function):
                 gx = sparse_conv_fused(gc.detach(), wt, km.swapped(num_in=x.shape[0]), x.shape[0])
         elif need_gx:
             gx = torch.zeros_like(xc)
-        gw = torch.zeros_like(wc) if need_gw else None
+        gw = None
+        if need_gw and native_dx:  # the implicit algorithms: one tensor-core launch when the shape allows
+            with torch.no_grad():
+                gw = sparse_conv_wgrad(xc.detach(), gc.detach(), km, gc.shape[0])
+        native_dw = gw is not None
+        if need_gw and not native_dw:
+            gw = torch.zeros_like(wc)
+        need_gw = need_gw and not native_dw
         if need_gw or (need_gx and not native_dx):
             offsets, in_maps, out_maps = km.offsets, km.in_maps, km.out_maps
             for k in range(len(km)):
