@@ -53,6 +53,9 @@ enum wcn_dtype { WCN_F32 = 0, WCN_F16 = 1, WCN_BF16 = 2 };
  * (warpconvnet/geometry/coords/search/torch_hashmap.py:17-32). */
 enum wcn_hash_method { WCN_HASH_FNV1A = 0, WCN_HASH_CITY = 1, WCN_HASH_MURMUR = 2 };
 
+/* Reductions of wcn_row_reduce, the native part of REDUCTIONS (warpconvnet/ops/reductions.py:13-21). */
+enum wcn_reduce_op { WCN_REDUCE_MIN = 0, WCN_REDUCE_MAX = 1, WCN_REDUCE_SUM = 2, WCN_REDUCE_MEAN = 3, WCN_REDUCE_MUL = 4 };
+
 /* Convolution kernels selectable through wcn_conv_fwd's `algo`. */
 enum wcn_conv_algo { WCN_CONV_AUTO = 0, WCN_CONV_SIMT = 1, WCN_CONV_TCGEN05 = 2 };
 
@@ -271,6 +274,16 @@ int wcn_conv_fwd(int algo, const void* feats, int64_t num_in, const void* weight
                  int64_t num_out, int32_t num_offsets, int32_t c_in, int32_t c_out, int dtype, const float* scale,
                  const float* shift, const void* residual, int relu, void* out, int out_dtype,
                  int32_t* dev_status, void* stream);
+
+/* Pooling over a kernel map: out[m, :] = op over the offsets k with nbr[k*M + m] >= 0 of
+ * feats[nbr[k*M + m], :] (fp32 accumulation, offsets in ascending order; rows without a neighbour
+ * become 0; mean divides by the number of neighbours).  With the transposed table of a
+ * non-overlapping pooling it is the un-pooling gather.
+ * Replaces kernel_map.to_csr() + row_reduction / torch_scatter.segment_csr of sparse_reduce
+ * (warpconvnet/nn/functional/sparse_pool.py:87-92, warpconvnet/ops/reductions.py:36-70) and the
+ * argsort + gather of sparse_unpool (sparse_pool.py:168-172). */
+int wcn_row_reduce(const void* feats, const int32_t* nbr, int64_t num_out, int32_t num_offsets,
+                   int32_t channels, int dtype, int op, void* out, void* stream);
 
 /* Weight gradient of the convolution above, accumulated into grad_weight[K, c_in, c_out] (fp32; the
  * caller zeroes it):

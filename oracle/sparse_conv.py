@@ -156,3 +156,37 @@ def minkunet_forward(state_dict: Dict[str, torch.Tensor], coords: np.ndarray, fe
     out = up("convtr6", "block7", out, out_b1p2, layers[6])
     out = up("convtr7", "block8", out, out_p1, layers[7])
     return out.feats @ sd["final.weight"][0] + sd["final.bias"]
+
+
+def window_reduce(feats: np.ndarray, in_maps: np.ndarray, out_maps: np.ndarray, num_out: int,
+                  reduction: str) -> np.ndarray:
+    """Restates ``sparse_reduce`` (warpconvnet/nn/functional/sparse_pool.py:87-107): the rows
+    ``feats[in_maps]`` grouped by ``out_maps`` and reduced per group as ``row_reduction`` /
+    ``segment_csr`` do (warpconvnet/ops/reductions.py:36-70); output rows without any input are 0."""
+    feats = np.asarray(feats, dtype=np.float64)
+    out = np.zeros((num_out, feats.shape[1]), dtype=np.float64)
+    order = np.argsort(out_maps, kind="stable")
+    o, i = np.asarray(out_maps)[order], np.asarray(in_maps)[order]
+    bounds = np.flatnonzero(np.diff(o)) + 1
+    starts = np.concatenate([[0], bounds]) if len(o) else np.zeros(0, dtype=np.int64)
+    ends = np.concatenate([bounds, [len(o)]]) if len(o) else np.zeros(0, dtype=np.int64)
+    for s, e in zip(starts, ends):
+        rows = feats[i[s:e]]
+        if reduction == "max":
+            r = rows.max(0)
+        elif reduction == "min":
+            r = rows.min(0)
+        elif reduction == "sum":
+            r = rows.sum(0)
+        elif reduction == "mean":
+            r = rows.mean(0)
+        elif reduction == "mul":
+            r = rows.prod(0)
+        elif reduction == "var":
+            r = (rows ** 2).mean(0) - rows.mean(0) ** 2
+        elif reduction == "std":
+            r = np.sqrt((rows ** 2).mean(0) - rows.mean(0) ** 2 + 1e-6)
+        else:
+            raise ValueError(reduction)
+        out[o[s]] = r
+    return out

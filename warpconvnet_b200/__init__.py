@@ -17,10 +17,13 @@ from .geometry.features.cat import CatFeatures
 from .geometry.types.voxels import Voxels
 from .nn.functional.sparse_conv import (SPARSE_CONV_BWD_ALGO_MODE, SPARSE_CONV_FWD_ALGO_MODE, STRIDED_CONV_MODE,
                                         ConvEpilogue, spatially_sparse_conv)
+from .nn.functional.sparse_pool import sparse_avg_pool, sparse_max_pool, sparse_reduce, sparse_unpool
 from .nn.functional.transforms import cat
 from .nn.modules.activations import ReLU
 from .nn.modules.normalizations import BatchNorm
 from .nn.modules.sequential import Sequential
 from .nn.modules.sparse_conv import SparseConv2d, SparseConv3d, SpatiallySparseConv
+from .nn.modules.sparse_pool import SparseMaxPool, SparseMinPool, SparsePool, SparseUnpool
+from .ops.reductions import REDUCTIONS
 
 __version__ = "0.1.0"

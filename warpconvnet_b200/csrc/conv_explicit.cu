@@ -81,3 +81,96 @@ extern "C" int wcn_scatter_add_rows(const void* src, const int32_t* idx, void* d
   WCN_CHECK_LAUNCH();
   return WCN_OK;
 }
+
+// ------------------------------------------------------------------ pooling
+
+namespace {
+
+// out[m, :] = reduce over the offsets k that have a neighbour (nbr[k*M + m] >= 0) of
+// feats[nbr[k*M + m], :]; rows without any neighbour become 0.  One thread owns VEC consecutive
+// channels of one output row, walks the offsets in order and accumulates in fp32.
+template <typename T, int VEC>
+__global__ void row_reduce_kernel(const T* __restrict__ feats, const int32_t* __restrict__ nbr, int64_t M, int K,
+                                  int channels, int op, T* __restrict__ out) {
+  const int vpr = channels / VEC;
+  const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t m = t / vpr;
+  if (m >= M) return;
+  const int c0 = (int)(t - m * vpr) * VEC;
+  float acc[VEC];
+  int count = 0;
+  for (int k = 0; k < K; ++k) {
+    const int src = __ldg(&nbr[(int64_t)k * M + m]);
+    if (src < 0) continue;
+    __align__(16) T v[VEC];
+    if (VEC > 1) {
+      constexpr int PIECES = (int)(VEC * sizeof(T) / 16);
+#pragma unroll
+      for (int q = 0; q < PIECES; ++q)
+        reinterpret_cast<uint4*>(v)[q] = __ldg(reinterpret_cast<const uint4*>(feats + (int64_t)src * channels + c0) + q);
+    } else {
+      v[0] = feats[(int64_t)src * channels + c0];
+    }
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) {
+      const float x = wcn_to_float<T>(v[i]);
+      if (count == 0) acc[i] = x;
+      else if (op == WCN_REDUCE_MIN) acc[i] = fminf(acc[i], x);
+      else if (op == WCN_REDUCE_MAX) acc[i] = fmaxf(acc[i], x);
+      else if (op == WCN_REDUCE_MUL) acc[i] = __fmul_rn(acc[i], x);
+      else acc[i] = __fadd_rn(acc[i], x);  // sum, mean
+    }
+    ++count;
+  }
+  __align__(16) T o[VEC];
+#pragma unroll
+  for (int i = 0; i < VEC; ++i) {
+    float y = count ? acc[i] : 0.f;
+    if (op == WCN_REDUCE_MEAN && count) y = __fdiv_rn(y, (float)count);
+    o[i] = wcn_from_float<T>(y);
+  }
+  if (VEC > 1) {
+    constexpr int PIECES = (int)(VEC * sizeof(T) / 16);
+#pragma unroll
+    for (int q = 0; q < PIECES; ++q)
+      reinterpret_cast<uint4*>(out + m * channels + c0)[q] = reinterpret_cast<uint4*>(o)[q];
+  } else {
+    out[m * channels + c0] = o[0];
+  }
+}
+
+template <typename T>
+int launch_row_reduce(const void* feats, const int32_t* nbr, int64_t M, int K, int channels, int op, void* out,
+                      cudaStream_t st) {
+  constexpr int VEC = (int)(16 / sizeof(T));
+  const bool vec = channels % VEC == 0 && !(reinterpret_cast<uintptr_t>(feats) & 15) &&
+                   !(reinterpret_cast<uintptr_t>(out) & 15);
+  if (vec) {
+    const int64_t total = M * (channels / VEC);
+    row_reduce_kernel<T, VEC><<<(unsigned)((total + 255) / 256), 256, 0, st>>>((const T*)feats, nbr, M, K, channels, op,
+                                                                              (T*)out);
+  } else {
+    const int64_t total = M * channels;
+    row_reduce_kernel<T, 1><<<(unsigned)((total + 255) / 256), 256, 0, st>>>((const T*)feats, nbr, M, K, channels, op,
+                                                                            (T*)out);
+  }
+  return cudaGetLastError() == cudaSuccess ? WCN_OK : WCN_ERR_EXECUTION;
+}
+
+}  // namespace
+
+extern "C" int wcn_row_reduce(const void* feats, const int32_t* nbr, int64_t num_out, int32_t num_offsets,
+                              int32_t channels, int dtype, int op, void* out, void* stream) {
+  if (num_out < 0 || num_offsets <= 0 || channels <= 0 || op < WCN_REDUCE_MIN || op > WCN_REDUCE_MUL)
+    return WCN_ERR_INVALID_PARAMETERS;
+  if (num_out == 0) return WCN_OK;
+  if (!nbr || !out) return WCN_ERR_INVALID_PARAMETERS;
+  if ((int64_t)num_out * channels >= (int64_t)0x7FFFFFFF * 256) return WCN_ERR_INVALID_PARAMETERS;
+  cudaStream_t st = wcn_stream(stream);
+  switch (dtype) {
+    case WCN_F32: return launch_row_reduce<float>(feats, nbr, num_out, num_offsets, channels, op, out, st);
+    case WCN_F16: return launch_row_reduce<__half>(feats, nbr, num_out, num_offsets, channels, op, out, st);
+    case WCN_BF16: return launch_row_reduce<__nv_bfloat16>(feats, nbr, num_out, num_offsets, channels, op, out, st);
+    default: return WCN_ERR_INVALID_PARAMETERS;
+  }
+}

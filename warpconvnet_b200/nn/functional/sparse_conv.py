@@ -257,7 +257,7 @@ def generate_output_coords_and_kernel_map(input_sparse_tensor: Voxels, kernel_si
     if generative:
         raise NotImplementedError("generative convolution is outside the supported path")
     if stride_mode != STRIDED_CONV_MODE.STRIDE_ONLY and any(s != 1 for s in stride):
-        raise NotImplementedError("stride_mode=reduce_and_stride is outside the supported path")
+        raise ValueError("with stride_mode=reduce_and_stride the caller pools first and passes stride 1")
     in_coords = input_sparse_tensor.batch_indexed_coordinates
     if in_coords.dtype != torch.int32:
         in_coords = in_coords.to(torch.int32)
@@ -523,6 +523,16 @@ def spatially_sparse_conv(
             out_tensor_stride = ntuple(1, ndim=nd)
         assert any(o < i for o, i in zip(out_tensor_stride, in_tensor_stride)), \
             "Output stride is larger than input stride"
+
+    if stride_mode == STRIDED_CONV_MODE.REDUCE_AND_STRIDE and any(s != 1 for s in _stride) and not transposed:
+        # pool the stride window first, then convolve at stride 1 on the pooled tensor (:1753-1767)
+        if needs_grad:
+            raise NotImplementedError("stride_mode=reduce_and_stride is an inference path here")
+        from .sparse_pool import sparse_reduce
+        input_sparse_tensor = sparse_reduce(input_sparse_tensor, kernel_size=_stride, stride=_stride,
+                                            reduction=stride_reduce)
+        feats = input_sparse_tensor.feature_tensor
+        _stride = ntuple(1, ndim=nd)
 
     effective_compute_dtype = compute_dtype if compute_dtype is not None else feats.dtype
 
