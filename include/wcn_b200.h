@@ -134,6 +134,15 @@ int wcn_kmap_search(const void* table, int64_t capacity, int hash_method, const 
 int wcn_kmap_scan(void* workspace, int64_t num_queries, int32_t num_offsets, int32_t* offsets,
                   void* stream);
 
+/* wcn_kmap_search with dilated windows: position (i, j, l) of the window probes
+ * x*sx + (i - cx)*dx and so on; `dilation` NULL means 1.
+ * Replaces kernel_offsets_from_size with a kernel_dilation and the offset-list search
+ * _kernel_map_from_offsets (warpconvnet/geometry/coords/search/torch_discrete.py:44-77, 160-241). */
+int wcn_kmap_search_dilated(const void* table, int64_t capacity, int hash_method, const int32_t* queries,
+                            int64_t num_queries, const int32_t* stride, const int32_t* kernel_size,
+                            const int32_t* dilation, int32_t num_offsets, int32_t* nbr, void* workspace,
+                            void* stream);
+
 /* wcn_kmap_search followed by wcn_kmap_scan, for callers that must not allocate device
  * memory.  Some hosts of this library cannot call cudaMalloc around it: plugins that are
  * handed a fixed arena by their framework and own no allocator, serving loops whose latency
@@ -183,7 +192,7 @@ int wcn_nbr_transpose(const int32_t* nbr_fwd, int32_t num_offsets, int64_t num_o
                       int32_t* nbr_t, void* stream);
 
 /* Kernel map of a coordinate set onto itself: `keys` are the rows the table was built from
- * (same order), the window is odd and the stride 1, so nbr is [K, num_keys] with
+ * (same order), the window is odd (dilated by `dilation`, NULL = 1) and the stride 1, so nbr is [K, num_keys] with
  * K = kx*ky*kz.  Same result as wcn_kmap_search on those arguments.  When the keys are
  * distinct (the table records whether they are) the map is symmetric, nbr[k][m] = i exactly
  * when nbr[K-1-k][i] = m, and only the first half of the offsets and the centre are probed.
@@ -192,7 +201,8 @@ int wcn_nbr_transpose(const int32_t* nbr_fwd, int32_t num_offsets, int64_t num_o
  * skip_symmetric_kernel_map flag hints at (warpconvnet/geometry/coords/search/torch_discrete.py:291-296)
  * but never completes into the full map. */
 int wcn_kmap_search_self(const void* table, int64_t capacity, int hash_method, const int32_t* keys,
-                         int64_t num_keys, const int32_t* kernel_size, int32_t* nbr, void* stream);
+                         int64_t num_keys, const int32_t* kernel_size, const int32_t* dilation, int32_t* nbr,
+                         void* stream);
 
 /* Per-block hit counts of a dense neighbour table into `workspace`, exactly what
  * wcn_kmap_search leaves there; for maps that were searched without counts.

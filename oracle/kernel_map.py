@@ -122,9 +122,11 @@ def identity_map_index(kernel_size: Sequence[int], n_in: int, n_out: int) -> Opt
 
 
 def kernel_map_found(
-    in_coords: np.ndarray, out_coords: np.ndarray, stride: Sequence[int], kernel_size: Sequence[int]
+    in_coords: np.ndarray, out_coords: np.ndarray, stride: Sequence[int], kernel_size: Sequence[int],
+    kernel_dilation: Optional[Sequence[int]] = None
 ) -> np.ndarray:
-    """found[K, M]: input row matching ``out*stride + offset[k]`` or -1.
+    """found[K, M]: input row matching ``out*stride + offset[k]`` or -1 (offsets scaled by the
+    dilation, torch_discrete.py:60-77).
 
     Restates ``kernel_map_size_4d_templated``
     (warpconvnet/csrc/discrete_kernels.cu:264-334) with the stride product of
@@ -132,7 +134,7 @@ def kernel_map_found(
     """
     in_coords = np.ascontiguousarray(in_coords, dtype=np.int32)
     out_coords = np.ascontiguousarray(out_coords, dtype=np.int32)
-    offs = kernel_offsets_from_size(kernel_size)
+    offs = kernel_offsets_from_size(kernel_size, kernel_dilation)
     K, M = len(offs), len(out_coords)
     svec = np.array([1, *stride], dtype=np.int32)
     q0 = out_coords * svec
@@ -160,10 +162,10 @@ def compact_found(found: np.ndarray) -> Tuple[np.ndarray, np.ndarray, np.ndarray
     return found[kk, mm].astype(np.int32), mm.astype(np.int32), offsets
 
 
-def generate_kernel_map(in_coords, out_coords, stride, kernel_size):
+def generate_kernel_map(in_coords, out_coords, stride, kernel_size, kernel_dilation=None):
     """Full map as the reference's ``generate_kernel_map`` (torch_discrete.py:365-466,
     method="size") returns it: in_maps, out_maps, offsets, identity_map_index."""
-    found = kernel_map_found(in_coords, out_coords, stride, kernel_size)
+    found = kernel_map_found(in_coords, out_coords, stride, kernel_size, kernel_dilation)
     in_maps, out_maps, offsets = compact_found(found)
     return in_maps, out_maps, offsets, identity_map_index(kernel_size, len(in_coords), len(out_coords))
 
@@ -177,6 +179,19 @@ def transposed_kernel_map(in_coords_coarse, out_coords_fine, stride, kernel_size
     """
     fin, fout, offsets, _ = generate_kernel_map(out_coords_fine, in_coords_coarse, stride, kernel_size)
     return fout, fin, offsets, None
+
+
+def expand_coords(coords: np.ndarray, kernel_size: Sequence[int], kernel_dilation: Optional[Sequence[int]] = None):
+    """Set of coordinates a kernel window reaches from ``coords`` (the reference's ``expand_coords``,
+    warpconvnet/geometry/coords/ops/expand.py:17-64, whose row order depends on hash slots): returned
+    in lexicographic order with its batch offsets."""
+    coords = np.ascontiguousarray(coords, dtype=np.int32)
+    offs = kernel_offsets_from_size(kernel_size, kernel_dilation)
+    cand = (coords[None, :, :] + offs[:, None, :]).reshape(-1, coords.shape[1])
+    out = canonical_coords(np.unique(np.concatenate([coords, cand], axis=0), axis=0))
+    nb = int(out[:, 0].max()) + 1 if len(out) else 0
+    counts = np.bincount(out[:, 0], minlength=nb)
+    return out, np.concatenate([[0], np.cumsum(counts)]).astype(np.int64)
 
 
 # --------------------------------------------------------------------------- stride

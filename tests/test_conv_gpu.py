@@ -198,6 +198,32 @@ def test_narrow_kernels_match_fp32_pipe_kernel(dtype, K, c_in, c_out):
     assert torch.equal(a, b), "epilogue differs"
 
 
+@pytest.mark.parametrize("stride", [1, 2])
+def test_generative_and_dilated_convolution(stride):
+    """generative=True grows the output support by the kernel window (after the stride, if any);
+    dilation spaces the window.  Output rows are compared with the oracle's after sorting both
+    coordinate sets (the reference defines the set, not the order)."""
+    n, c_in, c_out = 4000, 8, 12
+    coords, x, _ = _layer_case(n, c_in, c_out, 71, "sample")
+    g = torch.Generator().manual_seed(5)
+    w = torch.randn(27, c_in, c_out, generator=g) * 0.2
+    vox = make_voxels(coords, x)
+    dil = (1, 2, 1)
+    with torch.no_grad():
+        y = spatially_sparse_conv(vox, w.to(DEV), 3, stride=stride, kernel_dilation=dil, generative=True,
+                                  fwd_algo=ALGO.IMPLICIT_GEMM)
+    base = coords if stride == 1 else km.stride_coords(coords, (stride,) * 3)[0]
+    out_c, out_off = km.expand_coords(base, (3, 3, 3), dil)
+    i, o, f, iden = km.generate_kernel_map(coords, out_c, (stride,) * 3, (3, 3, 3), dil)
+    want = osc.explicit_gemm_forward(x, w, i, o, f, iden, len(out_c)).numpy()
+    got_c = y.batch_indexed_coordinates.cpu().numpy()
+    assert len(got_c) == len(out_c) and np.array_equal(y.offsets.numpy(), out_off)
+    order = np.lexsort(tuple(got_c[:, d] for d in reversed(range(4))))
+    assert np.array_equal(got_c[order], out_c)
+    assert rel_l2(y.feature_tensor.cpu().numpy()[order], want) < 1e-4
+    check_device_status(DEV)
+
+
 def test_minkunet_restore_order_equals_unpermute():
     """`restore_order=True` stores the head's rows through the sort permutation: the same
     numbers as un-permuting the sorted result afterwards."""

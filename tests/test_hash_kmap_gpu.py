@@ -146,7 +146,7 @@ def test_kernel_map_edge_cases():
     with pytest.raises(AssertionError):
         generate_kernel_map(dev(c).long(), dev(c), (1, 1, 1), (3, 3, 3))
     with pytest.raises(AssertionError):
-        generate_kernel_map(dev(c), dev(c), (1, 1, 1), (3, 3, 3), kernel_dilation=(2, 2, 2))
+        generate_kernel_map(dev(c), dev(c), (1, 1, 1), (3, 3, 3), kernel_center_offset=(0, 0, 0))
 
 
 def test_stride_coords(golden):
@@ -260,4 +260,39 @@ def test_self_map_with_repeated_rows_matches_oracle(method):
     res = generate_kernel_map(c, c, (1, 1, 1), (3, 1, 5), hash_method=method)
     assert np.array_equal(res.neighbor_table(len(distinct)).cpu().numpy(),
                           km.kernel_map_found(distinct, distinct, (1, 1, 1), (3, 1, 5)))
+    check_device_status(DEV)
+
+
+@pytest.mark.parametrize("dilation", [(2, 2, 2), (1, 3, 2)])
+def test_dilated_kernel_maps_match_oracle(dilation):
+    """Dilated windows: the self map (mirrored search) and a strided map against the oracle."""
+    rng = np.random.default_rng(23)
+    coords = np.unique(rng.integers(-9, 9, size=(5000, 4)).astype(np.int32), axis=0)
+    coords[:, 0] = np.abs(coords[:, 0]) % 2
+    coords = np.unique(coords, axis=0)
+    rng.shuffle(coords)
+    c = dev(coords)
+    res = generate_kernel_map(c, c, (1, 1, 1), (3, 3, 3), kernel_dilation=dilation)
+    assert np.array_equal(res.neighbor_table(len(coords)).cpu().numpy(),
+                          km.kernel_map_found(coords, coords, (1, 1, 1), (3, 3, 3), dilation))
+    i, o, f, _ = km.generate_kernel_map(coords, coords, (1, 1, 1), (3, 3, 3), dilation)
+    assert_map_equal(res, i, o, f)
+    coarse, _ = km.stride_coords(coords, (2, 2, 2))
+    res2 = generate_kernel_map(c, dev(coarse), (2, 2, 2), (2, 2, 2), kernel_dilation=dilation)
+    assert np.array_equal(res2.neighbor_table(len(coarse)).cpu().numpy(),
+                          km.kernel_map_found(coords, coarse, (2, 2, 2), (2, 2, 2), dilation))
+    check_device_status(DEV)
+
+
+def test_expand_coords_matches_oracle_set():
+    from warpconvnet_b200.geometry.coords.ops.expand import expand_coords
+    scenes = [synthetic.room_scene(3000, 0.05, 700 + i, "sample") - 11 for i in range(2)]
+    coords, offsets = synthetic.batch_scenes(scenes)
+    for ks, dil in (((3, 3, 3), (1, 1, 1)), ((2, 2, 2), (1, 1, 1)), ((3, 1, 3), (2, 1, 1))):
+        rows, offs = expand_coords(dev(coords.astype(np.int32)), ks, dil)
+        want, want_off = km.expand_coords(coords, ks, dil)
+        got = rows.cpu().numpy()
+        assert np.array_equal(km.canonical_coords(got), want)
+        assert np.array_equal(offs.numpy(), want_off)
+        assert np.all(np.diff(got[:, 0]) >= 0)  # batch-sorted
     check_device_status(DEV)

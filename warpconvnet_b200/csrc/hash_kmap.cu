@@ -226,6 +226,7 @@ struct KernelGeom {
   int sx, sy, sz;  // multiply output coordinates by this
   int kx, ky, kz;
   int cx, cy, cz;  // centre: size/2 for odd sizes, 0 for even
+  int dx, dy, dz;  // dilation: spacing of the window positions
 };
 
 // One thread per (query m, offset k); m runs along the warp so the query load
@@ -242,9 +243,9 @@ __global__ void kmap_search_kernel(const int4* __restrict__ tkeys, const int* __
   if (m < M) {
     int4 q = __ldg(reinterpret_cast<const int4*>(queries) + m);
     const int l = k % g.kz, j = (k / g.kz) % g.ky, i = k / (g.kz * g.ky);
-    q.y = q.y * g.sx + i - g.cx;
-    q.z = q.z * g.sy + j - g.cy;
-    q.w = q.w * g.sz + l - g.cz;
+    q.y = q.y * g.sx + (i - g.cx) * g.dx;
+    q.z = q.z * g.sy + (j - g.cy) * g.dy;
+    q.w = q.w * g.sz + (l - g.cz) * g.dz;
     found = wcn_lookup<METHOD>(tkeys, tvals, cap, q);
     nbr[(int64_t)k * M + m] = found;
   }
@@ -271,9 +272,9 @@ __global__ void kmap_search_self_kernel(const int4* __restrict__ tkeys, const in
   if (m >= M) return;
   int4 q = __ldg(reinterpret_cast<const int4*>(queries) + m);
   const int l = k % g.kz, j = (k / g.kz) % g.ky, i = k / (g.kz * g.ky);
-  q.y += i - g.cx;
-  q.z += j - g.cy;
-  q.w += l - g.cz;
+  q.y += (i - g.cx) * g.dx;
+  q.z += (j - g.cy) * g.dy;
+  q.w += (l - g.cz) * g.dz;
   const int found = wcn_lookup<METHOD>(tkeys, tvals, cap, q);
   nbr[(int64_t)k * M + m] = found;
   if (distinct && k < K / 2 && found >= 0) nbr[(int64_t)(K - 1 - k) * M + found] = (int32_t)m;
@@ -596,12 +597,13 @@ extern "C" int wcn_kmap_workspace_bytes(int64_t num_queries, int32_t num_offsets
   return WCN_OK;
 }
 
-extern "C" int wcn_kmap_search(const void* table, int64_t capacity, int hash_method, const int32_t* queries,
-                               int64_t num_queries, const int32_t* stride, const int32_t* kernel_size,
-                               int32_t num_offsets, int32_t* nbr, void* workspace, void* stream) {
+extern "C" int wcn_kmap_search_dilated(const void* table, int64_t capacity, int hash_method,
+                                       const int32_t* queries, int64_t num_queries, const int32_t* stride,
+                                       const int32_t* kernel_size, const int32_t* dilation, int32_t num_offsets,
+                                       int32_t* nbr, void* workspace, void* stream) {
   KernelGeom g;
   if (!table || !kernel_size || capacity <= 0 || capacity > 0x7FFFFFFFll || num_queries < 0 ||
-      !parse_stride(stride, &g.sx, &g.sy, &g.sz))
+      !parse_stride(stride, &g.sx, &g.sy, &g.sz) || !parse_stride(dilation, &g.dx, &g.dy, &g.dz))
     return WCN_ERR_INVALID_PARAMETERS;
   g.kx = kernel_size[0]; g.ky = kernel_size[1]; g.kz = kernel_size[2];
   if (g.kx <= 0 || g.ky <= 0 || g.kz <= 0) return WCN_ERR_INVALID_PARAMETERS;
@@ -627,10 +629,19 @@ extern "C" int wcn_kmap_search(const void* table, int64_t capacity, int hash_met
   return WCN_OK;
 }
 
+extern "C" int wcn_kmap_search(const void* table, int64_t capacity, int hash_method, const int32_t* queries,
+                               int64_t num_queries, const int32_t* stride, const int32_t* kernel_size,
+                               int32_t num_offsets, int32_t* nbr, void* workspace, void* stream) {
+  return wcn_kmap_search_dilated(table, capacity, hash_method, queries, num_queries, stride, kernel_size, nullptr,
+                                 num_offsets, nbr, workspace, stream);
+}
+
 extern "C" int wcn_kmap_search_self(const void* table, int64_t capacity, int hash_method, const int32_t* keys,
-                                    int64_t num_keys, const int32_t* kernel_size, int32_t* nbr, void* stream) {
+                                    int64_t num_keys, const int32_t* kernel_size, const int32_t* dilation,
+                                    int32_t* nbr, void* stream) {
   KernelGeom g;
-  if (!table || !kernel_size || capacity <= 0 || capacity > 0x7FFFFFFFll || num_keys < 0 || num_keys >= 0x7FFFFFFFll)
+  if (!table || !kernel_size || capacity <= 0 || capacity > 0x7FFFFFFFll || num_keys < 0 || num_keys >= 0x7FFFFFFFll ||
+      !parse_stride(dilation, &g.dx, &g.dy, &g.dz))
     return WCN_ERR_INVALID_PARAMETERS;
   g.sx = g.sy = g.sz = 1;
   g.kx = kernel_size[0]; g.ky = kernel_size[1]; g.kz = kernel_size[2];

@@ -46,7 +46,7 @@ def _kernel_map_from_size(hashtable: TorchHashTable, batched_query_coords: Tenso
                           return_type: Literal["indices", "offsets"] = "offsets",
                           skip_symmetric_kernel_map: bool = False,
                           query_stride: Optional[Tuple[int, ...]] = None, num_in: Optional[int] = None,
-                          self_map: bool = False):
+                          self_map: bool = False, kernel_dilation: Optional[Tuple[int, ...]] = None):
     """Search every position of a ``kernel_sizes`` window around each query.
 
     ``return_type="indices"`` returns ``found[K, M]`` (-1 = absent), "offsets" an
@@ -73,18 +73,20 @@ def _kernel_map_from_size(hashtable: TorchHashTable, batched_query_coords: Tenso
     nbr = torch.empty((K, M), dtype=torch.int32, device=dev)
     ksz = (ctypes.c_int32 * 3)(*[int(k) for k in kernel_sizes])
     strd = (ctypes.c_int32 * 3)(*[int(s) for s in (query_stride or (1, 1, 1))])
+    dil = (ctypes.c_int32 * 3)(*[int(d) for d in (kernel_dilation or (1, 1, 1))])
     # hit counts are only needed by the compact form; IntSearchResult makes them on demand
     ws = None
     if (self_map and not skip_symmetric_kernel_map and all(k % 2 == 1 for k in kernel_sizes)
             and all(int(s) == 1 for s in (query_stride or (1, 1, 1)))):
         assert M == len(hashtable.vector_keys), "self_map needs the table's own rows as queries"
         check(lib().wcn_kmap_search_self(ptr(hashtable._table), hashtable.capacity, hashtable.hash_method.value,
-                                         ptr(q), M, ctypes.addressof(ksz), ptr(nbr), stream_ptr(dev)),
-              "wcn_kmap_search_self")
+                                         ptr(q), M, ctypes.addressof(ksz), ctypes.addressof(dil), ptr(nbr),
+                                         stream_ptr(dev)), "wcn_kmap_search_self")
     else:
-        check(lib().wcn_kmap_search(ptr(hashtable._table), hashtable.capacity, hashtable.hash_method.value, ptr(q),
-                                    M, ctypes.addressof(strd), ctypes.addressof(ksz), K, ptr(nbr), None,
-                                    stream_ptr(dev)), "wcn_kmap_search")
+        check(lib().wcn_kmap_search_dilated(ptr(hashtable._table), hashtable.capacity, hashtable.hash_method.value,
+                                            ptr(q), M, ctypes.addressof(strd), ctypes.addressof(ksz),
+                                            ctypes.addressof(dil), K, ptr(nbr), None, stream_ptr(dev)),
+              "wcn_kmap_search_dilated")
     if return_type == "indices":
         return nbr
     assert return_type == "offsets"
@@ -125,10 +127,8 @@ def generate_kernel_map(batch_indexed_in_coords: Tensor, batch_indexed_out_coord
 
     if method not in ("size", "offset"):
         raise ValueError(f"Invalid method: {method}. Choose 'query', 'offset', or 'size'.")
-    # Both methods reduce to the window search; a dilation or a custom centre is
-    # not expressible by it (the reference asserts the same for method="size").
-    assert kernel_dilation is None or all(s == 1 for s in kernel_dilation), \
-        "Kernel dilation is not supported."
+    # Both methods reduce to the window search (dilated when asked); a custom centre is not
+    # expressible by it.
     assert kernel_center_offset is None, "Custom kernel_center_offset is not supported."
 
     if hashtable is None or hashtable.hash_method != hash_method:
@@ -139,6 +139,7 @@ def generate_kernel_map(batch_indexed_in_coords: Tensor, batch_indexed_out_coord
                                  identity_map_index=identity_map_index, return_type="offsets",
                                  skip_symmetric_kernel_map=skip_symmetric_kernel_map, query_stride=stride,
                                  num_in=batch_indexed_in_coords.shape[0],
+                                 kernel_dilation=(tuple(int(d) for d in kernel_dilation) if kernel_dilation else None),
                                  self_map=(batch_indexed_out_coords.data_ptr() == batch_indexed_in_coords.data_ptr()
                                            and batch_indexed_out_coords.shape == batch_indexed_in_coords.shape
                                            and batch_indexed_in_coords.is_contiguous()))

@@ -30,6 +30,7 @@ from ..._native import (CONV_AUTO, CONV_SIMT, CONV_TCGEN05, check, device_status
                         query_bytes, require_cuda, stream_ptr)
 from ...geometry.coords.integer import IntCoords
 from ...geometry.coords.ops.serialization import POINT_ORDERING, encode
+from ...geometry.coords.ops.expand import expand_coords
 from ...geometry.coords.ops.stride import stride_coords
 from ...geometry.coords.search.cache import IntSearchCache, IntSearchCacheKey
 from ...geometry.coords.search.search_results import IntSearchResult
@@ -254,8 +255,6 @@ def generate_output_coords_and_kernel_map(input_sparse_tensor: Voxels, kernel_si
                                           order: POINT_ORDERING = POINT_ORDERING.RANDOM):
     """(batch-indexed output coords, output offsets, kernel map); maps are cached on
     the input's shared cache and a transposed map reuses the forward one."""
-    if generative:
-        raise NotImplementedError("generative convolution is outside the supported path")
     if stride_mode != STRIDED_CONV_MODE.STRIDE_ONLY and any(s != 1 for s in stride):
         raise ValueError("with stride_mode=reduce_and_stride the caller pools first and passes stride 1")
     in_coords = input_sparse_tensor.batch_indexed_coordinates
@@ -263,13 +262,20 @@ def generate_output_coords_and_kernel_map(input_sparse_tensor: Voxels, kernel_si
         in_coords = in_coords.to(torch.int32)
 
     if output_spatially_sparse_tensor is not None:
+        assert not generative, "Output spatially sparse tensor is not supported with generative convolution"
         out_coords = output_spatially_sparse_tensor.batch_indexed_coordinates
         if out_coords.dtype != torch.int32:
             out_coords = out_coords.to(torch.int32)
         out_offsets = output_spatially_sparse_tensor.offsets
     elif any(s != 1 for s in stride):
         down = strided_coordinates(input_sparse_tensor.batched_coordinates, stride)
+        if generative:  # the strided set grown by the kernel window (reference :1861-1866)
+            down = expanded_coordinates(down, kernel_size, kernel_dilation)
         out_coords, out_offsets = down.batch_indexed_coordinates, down.offsets
+    elif generative:
+        assert not transposed, "Transposed and generative convolution is not supported yet"
+        grown = expanded_coordinates(input_sparse_tensor.batched_coordinates, kernel_size, kernel_dilation)
+        out_coords, out_offsets = grown.batch_indexed_coordinates, grown.offsets
     else:
         out_coords, out_offsets = in_coords, input_sparse_tensor.offsets
 
@@ -295,11 +301,11 @@ def generate_output_coords_and_kernel_map(input_sparse_tensor: Voxels, kernel_si
             fwd = cache.get(key_for(False, out_offsets, input_sparse_tensor.offsets))
         if fwd is None:
             # forward map: table on the (fine) output coordinates, (coarse) inputs * stride as queries
-            fwd = generate_kernel_map(out_coords, in_coords, stride, kernel_size, None,
+            fwd = generate_kernel_map(out_coords, in_coords, stride, kernel_size, kernel_dilation,
                                       hashtable=_cached_table(output_spatially_sparse_tensor, out_coords))
         kernel_map = fwd.swapped(num_in=out_coords.shape[0])
     else:
-        kernel_map = generate_kernel_map(in_coords, out_coords, stride, kernel_size, None,
+        kernel_map = generate_kernel_map(in_coords, out_coords, stride, kernel_size, kernel_dilation,
                                          hashtable=_cached_table(input_sparse_tensor, in_coords))
 
     if input_sparse_tensor.cache is None:
@@ -323,6 +329,20 @@ def strided_coordinates(coords: IntCoords, stride: Tuple[int, ...]) -> IntCoords
         out_coords, out_offsets = stride_coords(bc, stride, in_offsets=coords.offsets)
         hit = IntCoords(out_coords[:, 1:], offsets=out_offsets)
         hit._bcoords = out_coords
+        coords._shared[key] = hit
+    return hit
+
+
+def expanded_coordinates(coords: IntCoords, kernel_size: Tuple[int, ...], kernel_dilation: Tuple[int, ...]) -> IntCoords:
+    """The coordinates a kernel window reaches from ``coords`` (the output support of a generative
+    convolution), computed once per (coordinate set, window) and kept with the coordinate set."""
+    key = ("expanded", tuple(int(k) for k in kernel_size), tuple(int(d) for d in kernel_dilation))
+    hit = coords._shared.get(key)
+    if hit is None:
+        bc = coords.batch_indexed_coordinates
+        rows, offsets = expand_coords(bc if bc.dtype == torch.int32 else bc.to(torch.int32), key[1], key[2])
+        hit = IntCoords(rows[:, 1:], offsets=offsets, tensor_stride=coords.tensor_stride)
+        hit._bcoords = rows
         coords._shared[key] = hit
     return hit
 
@@ -573,6 +593,8 @@ def spatially_sparse_conv(
             out_ic = input_sparse_tensor.batched_coordinates
         else:
             out_ic, own = strided_coordinates(input_sparse_tensor.batched_coordinates, _stride), True
+        if generative:
+            out_ic, own = expanded_coordinates(out_ic, _kernel_size, _kernel_dilation), True
         if out_ic.tensor_stride != out_tensor_stride:
             if own and out_ic.tensor_stride is None:
                 out_ic.tensor_stride = out_tensor_stride  # the cached set is labelled once
