@@ -224,14 +224,28 @@ conv_narrow_out_kernel(const T* __restrict__ feats, const T* __restrict__ weight
   const int64_t m = out_rows ? (int64_t)__ldg(&out_rows[slot]) : slot;
   TO* orow = out + m * c_out;
   const TO* rrow = residual ? residual + m * c_out : nullptr;
+  constexpr int PER8 = (int)(8 / sizeof(TO));  // outputs per 8-byte store
+  const bool wide = (c_out % PER8) == 0 && (reinterpret_cast<uintptr_t>(out) & 7) == 0;  // rows start 8-byte aligned
 #pragma unroll
-  for (int j = 0; j < NP; ++j) {
-    if (j < c_out) {
+  for (int j0 = 0; j0 < NP; j0 += PER8) {
+    __align__(8) TO o[PER8];
+#pragma unroll
+    for (int i = 0; i < PER8; ++i) {
+      const int j = j0 + i;
       float y = acc[j];
-      y = wcn_affine(y, scale, shift, j);
-      if (rrow) y = __fadd_rn(y, wcn_to_float<TO>(rrow[j]));
-      if (relu) y = fmaxf(y, 0.f);
-      orow[j] = wcn_from_float<TO>(y);
+      if (j < c_out) {
+        y = wcn_affine(y, scale, shift, j);
+        if (rrow) y = __fadd_rn(y, wcn_to_float<TO>(rrow[j]));
+        if (relu) y = fmaxf(y, 0.f);
+      }
+      o[i] = wcn_from_float<TO>(y);
+    }
+    if (wide) {
+      if (j0 < c_out) *reinterpret_cast<uint2*>(orow + j0) = *reinterpret_cast<const uint2*>(o);
+    } else {
+#pragma unroll
+      for (int i = 0; i < PER8; ++i)
+        if (j0 + i < c_out) orow[j0 + i] = o[i];
     }
   }
 }
