@@ -49,7 +49,8 @@ SIGNATURES = {
     "wcn_conv_pack_weight": [_c_i32, _c_vp, _c_i32, _c_i32, _c_i32, _c_i32, _c_vp, _c_vp],
     "wcn_kmap_tile_order": [_c_vp, _c_i64, _c_i32, _c_vp, _c_vp, _c_vp],
     "wcn_row_reduce": [_c_vp, _c_vp, _c_i64, _c_i32, _c_i32, _c_i32, _c_i32, _c_vp, _c_vp],
-    "wcn_conv_wgrad": [_c_vp, _c_i64, _c_vp, _c_vp, _c_i64, _c_i32, _c_i32, _c_i32, _c_i32, _c_vp, _c_vp, _c_vp],
+    "wcn_kmap_tile_masks": [_c_vp, _c_i64, _c_i32, _c_vp, _c_vp],
+    "wcn_conv_wgrad": [_c_vp, _c_i64, _c_vp, _c_vp, _c_vp, _c_i64, _c_i32, _c_i32, _c_i32, _c_i32, _c_vp, _c_vp, _c_vp],
     "wcn_conv_fwd": [_c_i32, _c_vp, _c_i64, _c_vp, _c_vp, _c_vp, _c_vp, _c_i64, _c_i32, _c_i32, _c_i32, _c_i32,
                      _c_vp, _c_vp, _c_vp, _c_i32, _c_vp, _c_i32, _c_vp, _c_vp],
 }
@@ -61,7 +62,7 @@ _lib = None
 KERNELS_PER_CALL = {
     "wcn_hash_build": 2, "wcn_hash_search": 1, "wcn_unique_mark": 3, "wcn_unique_emit": 2, "wcn_kmap_search": 1, "wcn_kmap_search_static": 3,
     "wcn_kmap_scan": 2, "wcn_kmap_compact": 1, "wcn_nbr_from_maps": 1, "wcn_nbr_transpose": 1, "wcn_morton20": 1,
-    "wcn_kmap_tile_order": 3, "wcn_conv_wgrad": 1, "wcn_row_reduce": 1, "wcn_kmap_search_self": 1, "wcn_kmap_search_dilated": 1, "wcn_kmap_count": 1,
+    "wcn_kmap_tile_order": 3, "wcn_conv_wgrad": 1, "wcn_kmap_tile_masks": 1, "wcn_row_reduce": 1, "wcn_kmap_search_self": 1, "wcn_kmap_search_dilated": 1, "wcn_kmap_count": 1,
     "wcn_gather_rows": 1, "wcn_scatter_add_rows": 1, "wcn_conv_pack_weight": 1, "wcn_conv_fwd": 1,
 }
 LAUNCH_COUNTS: Counter = Counter()

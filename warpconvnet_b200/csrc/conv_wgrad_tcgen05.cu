@@ -36,6 +36,7 @@ struct WgradParams {
   const char* feats;     // [num_in, c_in]
   const char* gout;      // [M, c_out]
   const int32_t* nbr;    // [K][M]
+  const uint32_t* tile_masks;  // per 128-row step: offsets with any neighbour (null: every step is processed)
   float* gw;             // [K][c_in][c_out] fp32, accumulated into
   int64_t M, num_in;
   int K, c_in, c_out;
@@ -50,6 +51,7 @@ struct WgradControl {
   uint64_t acc_full;
   uint32_t tmem_holder;
   int skip;
+  int any;  // the accumulator received at least one step
 };
 
 template <int RBA, int RBB, bool BF16>
@@ -81,7 +83,8 @@ conv_wgrad_tcgen05_kernel(const WgradParams p) {
 
   if (tid == 0) {
     for (int s = 0; s < p.stages; ++s) { mbar_init(bar(&ctl->full[s]), WG_PROD_THREADS); mbar_init(bar(&ctl->empty[s]), 1); }
-    mbar_init(bar(&ctl->acc_full), 1);
+    mbar_init(bar(&ctl->acc_full), 2);  // the commit of the last MMAs and the issuer's own arrival
+    ctl->any = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == WG_MMA_WARP) tmem_alloc(smem_u32(&ctl->tmem_holder), (uint32_t)p.cols);
@@ -94,6 +97,11 @@ conv_wgrad_tcgen05_kernel(const WgradParams p) {
   const int64_t step0 = (int64_t)blockIdx.x * p.steps_per_cta;
   const int64_t step1 = min(total_steps, step0 + p.steps_per_cta);
   bool ok = true;
+  // offsets this group gathers through; a step none of whose rows has a neighbour at any of them
+  // contributes nothing and is skipped by every role alike
+  uint32_t gmask = 0;
+  for (int u = 0; u < GU; ++u)
+    if (unit0 + u < total_units) gmask |= 1u << ((unit0 + u) / UA);
 
   if (warp >= WG_PROD_WARP0 && warp < WG_MMA_WARP) {
     // ================================================================ producers
@@ -108,6 +116,7 @@ conv_wgrad_tcgen05_kernel(const WgradParams p) {
     const int b_iters = WG_ROWS * PR / WG_PROD_THREADS;
     int slot = 0, phase = 0;
     for (int64_t st = step0; st < step1 && ok; ++st) {
+      if (p.tile_masks && !(__ldg(&p.tile_masks[st]) & gmask)) continue;
       const int64_t m0 = st * WG_ROWS;
       // the neighbour indices of this thread's rows, for every unit of the group, before the wait
       int src[GU][NJ];
@@ -156,6 +165,7 @@ conv_wgrad_tcgen05_kernel(const WgradParams p) {
       int slot = 0, phase = 0;
       bool any = false;
       for (int64_t st = step0; st < step1 && ok; ++st) {
+        if (p.tile_masks && !(__ldg(&p.tile_masks[st]) & gmask)) continue;
         if (!mbar_wait(bar(&ctl->full[slot]), phase, p.dev_status)) { ok = false; break; }
         tc_fence_after();
         const uint32_t a_slot = base + slot * STAGE;
@@ -170,14 +180,15 @@ conv_wgrad_tcgen05_kernel(const WgradParams p) {
         umma_commit(bar(&ctl->empty[slot]));  // the stage is free once these MMAs have read it
         if (++slot == p.stages) { slot = 0; phase ^= 1; }
       }
-      if (any && ok) umma_commit(bar(&ctl->acc_full));
-      else mbar_arrive(bar(&ctl->acc_full));
+      umma_commit(bar(&ctl->acc_full));  // arrives when every MMA above has completed (at once if there were none)
+      ctl->any = (any && ok) ? 1 : 0;
+      mbar_arrive(bar(&ctl->acc_full));  // publishes `any`
     }
     __syncwarp();
   } else {
     // ================================================================ epilogue (warps 0..3)
     ok = mbar_wait(bar(&ctl->acc_full), 0, p.dev_status, 256);
-    if (__all_sync(0xFFFFFFFFu, ok) && step1 > step0) {
+    if (__all_sync(0xFFFFFFFFu, ok) && ctl->any) {
       tc_fence_after();
       const int row = warp * 32 + lane;            // TMEM lane = position on the M side
       const int unit = unit0 + row / CWA;
@@ -246,15 +257,15 @@ bool wcn_conv_wgrad_tcgen05_supported(int K, int c_in, int c_out, int dtype) {
          c_out % 32 == 0 && c_out <= 256 && (int64_t)K * c_in <= 65535ll * 32;
 }
 
-int wcn_conv_wgrad_tcgen05(const void* feats, int64_t num_in, const void* grad_out, const int32_t* nbr, int64_t M,
-                           int K, int c_in, int c_out, int dtype, float* grad_weight, int32_t* dev_status,
-                           cudaStream_t st) {
+int wcn_conv_wgrad_tcgen05(const void* feats, int64_t num_in, const void* grad_out, const int32_t* nbr,
+                           const uint32_t* tile_masks, int64_t M, int K, int c_in, int c_out, int dtype,
+                           float* grad_weight, int32_t* dev_status, cudaStream_t st) {
   if (!wcn_conv_wgrad_tcgen05_supported(K, c_in, c_out, dtype)) return WCN_ERR_UNSUPPORTED_CONFIG;
   if (!dev_status || !grad_weight || num_in <= 0 || num_in >= 0x7FFFFFFFll) return WCN_ERR_INVALID_PARAMETERS;
   if ((reinterpret_cast<uintptr_t>(feats) & 15) || (reinterpret_cast<uintptr_t>(grad_out) & 15))
     return WCN_ERR_INVALID_PARAMETERS;
   WgradParams p;
-  p.feats = (const char*)feats; p.gout = (const char*)grad_out; p.nbr = nbr; p.gw = grad_weight;
+  p.feats = (const char*)feats; p.gout = (const char*)grad_out; p.nbr = nbr; p.tile_masks = K <= 32 ? tile_masks : nullptr; p.gw = grad_weight;
   p.M = M; p.num_in = num_in; p.K = K; p.c_in = c_in; p.c_out = c_out; p.dev_status = dev_status;
   const bool a128 = c_in % 64 == 0, b128 = c_out % 64 == 0, bf = dtype == WCN_BF16;
 #define WCN_WG_CASE(A, B, F) if (a128 == (A == 128) && b128 == (B == 128) && bf == F) return launch_wgrad<A, B, F>(p, st);

@@ -353,6 +353,25 @@ __global__ void kmap_row_mask_kernel(const int32_t* __restrict__ nbr, int64_t M,
   masks[m] = mask;
 }
 
+// Offsets with any neighbour among 128 consecutive rows of the table (one block per 128 rows):
+// what a kernel that walks the table in 128-row steps may skip.
+__global__ void kmap_tile_mask_kernel(const int32_t* __restrict__ nbr, int64_t M, int K, uint32_t* __restrict__ masks) {
+  __shared__ uint32_t part[4];
+  const int64_t m = (int64_t)blockIdx.x * 128 + threadIdx.x;
+  uint32_t mask = 0;
+  if (m < M) {
+    int v[32];
+#pragma unroll
+    for (int k = 0; k < 32; ++k) v[k] = k < K ? __ldg(&nbr[(int64_t)k * M + m]) : -1;
+#pragma unroll
+    for (int k = 0; k < 32; ++k) mask |= (uint32_t)(v[k] >= 0) << k;
+  }
+  mask = __reduce_or_sync(0xFFFFFFFFu, mask);
+  if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = mask;
+  __syncthreads();
+  if (threadIdx.x == 0) masks[blockIdx.x] = part[0] | part[1] | part[2] | part[3];
+}
+
 // Pass 2: one block per window sorts its rows by (mask, row) and replaces the masks by the row
 // order.  Stable least-significant-digit radix sort of the permutation, 7 bits per pass
 // (ceil(K / 7) passes): a warp owns 128 consecutive positions, ranks equal digits with
@@ -795,6 +814,17 @@ extern "C" int wcn_kmap_tile_order(const int32_t* nbr, int64_t num_out, int32_t 
   kmap_window_sort_kernel<<<windows, kTileOrderThreads, 0, st>>>(out_rows, num_out, num_offsets);
   dim3 grid(windows, (unsigned)((num_offsets + kTileCopyOffsets - 1) / kTileCopyOffsets));
   kmap_permute_kernel<<<grid, kTileOrderThreads, 0, st>>>(nbr, out_rows, num_out, num_offsets, nbr_tiled);
+  WCN_CHECK_LAUNCH();
+  return WCN_OK;
+}
+
+extern "C" int wcn_kmap_tile_masks(const int32_t* nbr, int64_t num_out, int32_t num_offsets, uint32_t* masks,
+                                   void* stream) {
+  if (num_offsets <= 0 || num_offsets > 32 || num_out < 0) return WCN_ERR_INVALID_PARAMETERS;
+  if (num_out == 0) return WCN_OK;
+  if (!nbr || !masks) return WCN_ERR_INVALID_PARAMETERS;
+  kmap_tile_mask_kernel<<<(unsigned)((num_out + 127) / 128), 128, 0, wcn_stream(stream)>>>(nbr, num_out, num_offsets,
+                                                                                          masks);
   WCN_CHECK_LAUNCH();
   return WCN_OK;
 }

@@ -392,8 +392,9 @@ def sparse_conv_wgrad(in_features: Tensor, grad_output: Tensor, kernel_map: IntS
         return None
     dev = x.device
     nbr = kernel_map.neighbor_table(num_out_coords)
+    masks = kernel_map.tile_masks(num_out_coords) if K > 1 else None  # steps without neighbours are skipped
     gw = torch.zeros((K, c_in, c_out), dtype=torch.float32, device=dev)
-    check(lib().wcn_conv_wgrad(ptr(x), x.shape[0], ptr(g), ptr(nbr), num_out_coords, K, c_in, c_out,
+    check(lib().wcn_conv_wgrad(ptr(x), x.shape[0], ptr(g), ptr(nbr), ptr(masks), num_out_coords, K, c_in, c_out,
                                dtype_code(x.dtype), ptr(gw), ptr(device_status(dev)), stream_ptr(dev)),
           "wcn_conv_wgrad")
     return gw
