@@ -307,14 +307,15 @@ int wcn_row_reduce(const void* feats, const int32_t* nbr, int64_t num_out, int32
  * feats / grad_out share `dtype` (f16 or bf16), fp32 accumulation on the tensor cores; the partial
  * sums of different row ranges are added with atomics, so the last bits vary from run to run.
  * Needs c_in % 32 == 0, c_out % 32 == 0, c_out <= 256; else WCN_ERR_UNSUPPORTED_CONFIG (callers fall
- * back to a GEMM per offset).  `nbr` is the plain (not tiled) neighbour table of the forward pass;
+ * back to a GEMM per offset).  (`nbr`, `out_rows`) is the pair wcn_conv_fwd takes: the plain table
+ * with out_rows NULL, or the tiled one with its row order (grad_out is then read at out_rows[s]);
  * `tile_masks` (from wcn_kmap_tile_masks on the same table, or NULL) lets the kernel skip the 128-row
  * steps in which the offsets of a CTA have no neighbour.
  * Replaces cutlass_gemm_trAB_gather (warpconvnet/csrc/warpconvnet_pybind.cpp:511-624) and
  * split_k_implicit_gemm (warpconvnet/csrc/implicit_gemm_split_k.cu:63-393) with the per-offset loop
  * around them (warpconvnet/nn/functional/sparse_conv.py:591-604). */
 int wcn_conv_wgrad(const void* feats, int64_t num_in, const void* grad_out, const int32_t* nbr,
-                   const uint32_t* tile_masks, int64_t num_out, int32_t num_offsets, int32_t c_in, int32_t c_out, int dtype,
+                   const int32_t* out_rows, const uint32_t* tile_masks, int64_t num_out, int32_t num_offsets, int32_t c_in, int32_t c_out, int dtype,
                    float* grad_weight, int32_t* dev_status, void* stream);
 
 #ifdef __cplusplus

@@ -335,6 +335,10 @@ def test_wgrad_tcgen05_matches_explicit_formulas(dtype, K, c_in, c_out, n):
         if e > s:
             ref[k] = x.float()[torch.from_numpy(i[s:e]).long()].T @ go.float()[torch.from_numpy(o[s:e]).long()]
     assert rel_l2(gw.cpu().numpy(), ref.numpy()) < 1e-4  # fp32 accumulation of exact products
+    # the same through the tiled table (dY rows read through the row order)
+    gt = sparse_conv_wgrad(x.to(DEV), go.to(DEV), kmap, n_out, tile_order=True)
+    check_device_status(DEV)
+    assert rel_l2(gt.cpu().numpy(), ref.numpy()) < 1e-4
 
 
 def test_backward_native_dx_strided_and_transposed_fp16():

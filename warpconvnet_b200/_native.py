@@ -50,7 +50,7 @@ SIGNATURES = {
     "wcn_kmap_tile_order": [_c_vp, _c_i64, _c_i32, _c_vp, _c_vp, _c_vp],
     "wcn_row_reduce": [_c_vp, _c_vp, _c_i64, _c_i32, _c_i32, _c_i32, _c_i32, _c_vp, _c_vp],
     "wcn_kmap_tile_masks": [_c_vp, _c_i64, _c_i32, _c_vp, _c_vp],
-    "wcn_conv_wgrad": [_c_vp, _c_i64, _c_vp, _c_vp, _c_vp, _c_i64, _c_i32, _c_i32, _c_i32, _c_i32, _c_vp, _c_vp, _c_vp],
+    "wcn_conv_wgrad": [_c_vp, _c_i64, _c_vp, _c_vp, _c_vp, _c_vp, _c_i64, _c_i32, _c_i32, _c_i32, _c_i32, _c_vp, _c_vp, _c_vp],
     "wcn_conv_fwd": [_c_i32, _c_vp, _c_i64, _c_vp, _c_vp, _c_vp, _c_vp, _c_i64, _c_i32, _c_i32, _c_i32, _c_i32,
                      _c_vp, _c_vp, _c_vp, _c_i32, _c_vp, _c_i32, _c_vp, _c_vp],
 }

@@ -22,7 +22,7 @@ int wcn_conv_narrow_out_fwd(const void* feats, const void* weight, const int32_t
                             cudaStream_t st);
 bool wcn_conv_wgrad_tcgen05_supported(int K, int c_in, int c_out, int dtype);
 int wcn_conv_wgrad_tcgen05(const void* feats, int64_t num_in, const void* grad_out, const int32_t* nbr,
-                           const uint32_t* tile_masks, int64_t M, int K, int c_in, int c_out, int dtype,
+                           const int32_t* out_rows, const uint32_t* tile_masks, int64_t M, int K, int c_in, int c_out, int dtype,
                            float* grad_weight, int32_t* dev_status, cudaStream_t st);
 int wcn_conv_tcgen05_fwd(const void* feats, int64_t num_in, const void* packed, const int32_t* nbr,
                          const int32_t* out_rows, int64_t M, int K, int c_in,
@@ -103,12 +103,12 @@ extern "C" int wcn_conv_fwd(int algo, const void* feats, int64_t num_in, const v
 }
 
 extern "C" int wcn_conv_wgrad(const void* feats, int64_t num_in, const void* grad_out, const int32_t* nbr,
-                              const uint32_t* tile_masks, int64_t num_out, int32_t num_offsets, int32_t c_in, int32_t c_out, int dtype,
+                              const int32_t* out_rows, const uint32_t* tile_masks, int64_t num_out, int32_t num_offsets, int32_t c_in, int32_t c_out, int dtype,
                               float* grad_weight, int32_t* dev_status, void* stream) {
   if (num_in < 0 || num_out < 0 || num_offsets <= 0 || c_in <= 0 || c_out <= 0) return WCN_ERR_INVALID_PARAMETERS;
   if (!wcn_conv_wgrad_tcgen05_supported(num_offsets, c_in, c_out, dtype)) return WCN_ERR_UNSUPPORTED_CONFIG;
   if (num_out == 0 || num_in == 0) return WCN_OK;
   if (!feats || !grad_out || !nbr || !grad_weight || !dev_status) return WCN_ERR_INVALID_PARAMETERS;
-  return wcn_conv_wgrad_tcgen05(feats, num_in, grad_out, nbr, tile_masks, num_out, num_offsets, c_in, c_out, dtype, grad_weight,
+  return wcn_conv_wgrad_tcgen05(feats, num_in, grad_out, nbr, out_rows, tile_masks, num_out, num_offsets, c_in, c_out, dtype, grad_weight,
                                 dev_status, wcn_stream(stream));
 }

@@ -36,6 +36,7 @@ struct WgradParams {
   const char* feats;     // [num_in, c_in]
   const char* gout;      // [M, c_out]
   const int32_t* nbr;    // [K][M]
+  const int32_t* out_rows;     // slot -> row of gout (tiled table), or null for the identity
   const uint32_t* tile_masks;  // per 128-row step: offsets with any neighbour (null: every step is processed)
   float* gw;             // [K][c_in][c_out] fp32, accumulated into
   int64_t M, num_in;
@@ -149,8 +150,10 @@ conv_wgrad_tcgen05_kernel(const WgradParams p) {
         const int q = pt + i * WG_PROD_THREADS;
         const int row = q / PR, piece = q - row * PR;
         const bool have = m0 + row < p.M;
+        int64_t grow = m0 + row;
+        if (have && p.out_rows) grow = __ldg(&p.out_rows[grow]);
         cp_async16(b_dst + (piece / CHB) * B_TILE + tile_offset<RBB>(row, piece % CHB),
-                   have ? p.gout + ((m0 + row) * p.c_out) * 2 + piece * 16 : p.gout, have ? 16u : 0u);
+                   have ? p.gout + (grow * p.c_out) * 2 + piece * 16 : p.gout, have ? 16u : 0u);
       }
       cp_async_arrive(bar(&ctl->full[slot]));  // hardware arrives when this thread's copies land
       if (++slot == p.stages) { slot = 0; phase ^= 1; }
@@ -258,14 +261,14 @@ bool wcn_conv_wgrad_tcgen05_supported(int K, int c_in, int c_out, int dtype) {
 }
 
 int wcn_conv_wgrad_tcgen05(const void* feats, int64_t num_in, const void* grad_out, const int32_t* nbr,
-                           const uint32_t* tile_masks, int64_t M, int K, int c_in, int c_out, int dtype,
+                           const int32_t* out_rows, const uint32_t* tile_masks, int64_t M, int K, int c_in, int c_out, int dtype,
                            float* grad_weight, int32_t* dev_status, cudaStream_t st) {
   if (!wcn_conv_wgrad_tcgen05_supported(K, c_in, c_out, dtype)) return WCN_ERR_UNSUPPORTED_CONFIG;
   if (!dev_status || !grad_weight || num_in <= 0 || num_in >= 0x7FFFFFFFll) return WCN_ERR_INVALID_PARAMETERS;
   if ((reinterpret_cast<uintptr_t>(feats) & 15) || (reinterpret_cast<uintptr_t>(grad_out) & 15))
     return WCN_ERR_INVALID_PARAMETERS;
   WgradParams p;
-  p.feats = (const char*)feats; p.gout = (const char*)grad_out; p.nbr = nbr; p.tile_masks = K <= 32 ? tile_masks : nullptr; p.gw = grad_weight;
+  p.feats = (const char*)feats; p.gout = (const char*)grad_out; p.nbr = nbr; p.out_rows = out_rows; p.tile_masks = K <= 32 ? tile_masks : nullptr; p.gw = grad_weight;
   p.M = M; p.num_in = num_in; p.K = K; p.c_in = c_in; p.c_out = c_out; p.dev_status = dev_status;
   const bool a128 = c_in % 64 == 0, b128 = c_out % 64 == 0, bf = dtype == WCN_BF16;
 #define WCN_WG_CASE(A, B, F) if (a128 == (A == 128) && b128 == (B == 128) && bf == F) return launch_wgrad<A, B, F>(p, st);

@@ -127,16 +127,17 @@ class IntSearchResult:
         assert self._tiled[0].shape[1] == num_out
         return self._tiled
 
-    def tile_masks(self, num_out: int) -> Tensor:
-        """Per 128 consecutive output rows, the set of offsets (bit k) that have any neighbour there;
-        ``int32 [ceil(num_out / 128)]``, built once per map."""
-        if getattr(self, "_tile_masks", None) is None:
-            nbr = self.neighbor_table(num_out)
+    def tile_masks(self, num_out: int, tiled: bool = False) -> Tensor:
+        """Per 128 consecutive rows of the neighbour table (the tiled one with ``tiled``), the set of
+        offsets (bit k) that have any neighbour there; ``int32 [ceil(num_out / 128)]``, built once."""
+        store = self.__dict__.setdefault("_tile_masks", {})
+        if tiled not in store:
+            nbr = self.tiled_neighbor_table(num_out)[0] if tiled else self.neighbor_table(num_out)
             masks = torch.empty((num_out + 127) // 128, dtype=torch.int32, device=nbr.device)
             check(lib().wcn_kmap_tile_masks(ptr(nbr), num_out, self._num_offsets, ptr(masks), stream_ptr(nbr.device)),
                   "wcn_kmap_tile_masks")
-            self._tile_masks = masks
-        return self._tile_masks
+            store[tiled] = masks
+        return store[tiled]
 
     def swapped(self, num_in: Optional[int] = None) -> "IntSearchResult":
         """The map with inputs and outputs exchanged (transposed convolution,

@@ -380,7 +380,7 @@ def _cached_table(voxels: Optional[Voxels], coords: Tensor):
 
 
 def sparse_conv_wgrad(in_features: Tensor, grad_output: Tensor, kernel_map: IntSearchResult,
-                      num_out_coords: int) -> Optional[Tensor]:
+                      num_out_coords: int, tile_order: bool = False) -> Optional[Tensor]:
     """``dW[k] = X[in_k]^T @ dY[out_k]`` for every kernel offset in one launch on the tensor cores
     (fp16 / bf16 operands, fp32 result ``[K, C_in, C_out]``), or None when the shape is not one the
     native kernel takes (the caller then uses a GEMM per offset)."""
@@ -391,10 +391,15 @@ def sparse_conv_wgrad(in_features: Tensor, grad_output: Tensor, kernel_map: IntS
             or c_out > 256 or K > 32 or x.shape[0] == 0 or num_out_coords == 0):
         return None
     dev = x.device
-    nbr = kernel_map.neighbor_table(num_out_coords)
-    masks = kernel_map.tile_masks(num_out_coords) if K > 1 else None  # steps without neighbours are skipped
+    tiled = bool(tile_order)
+    if tiled:
+        nbr, out_rows = kernel_map.tiled_neighbor_table(num_out_coords)
+    else:
+        nbr, out_rows = kernel_map.neighbor_table(num_out_coords), None
+    masks = kernel_map.tile_masks(num_out_coords, tiled) if K > 1 else None  # steps without neighbours are skipped
     gw = torch.zeros((K, c_in, c_out), dtype=torch.float32, device=dev)
-    check(lib().wcn_conv_wgrad(ptr(x), x.shape[0], ptr(g), ptr(nbr), ptr(masks), num_out_coords, K, c_in, c_out,
+    check(lib().wcn_conv_wgrad(ptr(x), x.shape[0], ptr(g), ptr(nbr), ptr(out_rows), ptr(masks), num_out_coords, K,
+                               c_in, c_out,
                                dtype_code(x.dtype), ptr(gw), ptr(device_status(dev)), stream_ptr(dev)),
           "wcn_conv_wgrad")
     return gw
