@@ -172,8 +172,10 @@ def _as_f32_on(t: Optional[Tensor], dev: torch.device) -> Optional[Tensor]:
     return t if t.is_contiguous() else t.contiguous()
 
 
-# Kernel maps with at least this many output rows (and 2..32 offsets) are run in tile order.
+# Kernel maps with at least this many output rows and this many offsets (at most 32) are run in tile
+# order; for 2x2x2 maps building the order costs about what it saves.
 TILE_ORDER_MIN_ROWS = 1024
+TILE_ORDER_MIN_OFFSETS = 9
 
 
 def sparse_conv_fused(in_features: Tensor, weight: Tensor, kernel_map: IntSearchResult, num_out_coords: int,
@@ -194,7 +196,7 @@ def sparse_conv_fused(in_features: Tensor, weight: Tensor, kernel_map: IntSearch
     if num_out_coords == 0:
         return out
     if tile_order is None:
-        tile_order = 1 < K <= 32 and num_out_coords >= TILE_ORDER_MIN_ROWS
+        tile_order = TILE_ORDER_MIN_OFFSETS <= K <= 32 and num_out_coords >= TILE_ORDER_MIN_ROWS
     if tile_order:
         nbr, out_rows = kernel_map.tiled_neighbor_table(num_out_coords)
     else:
