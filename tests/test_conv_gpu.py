@@ -224,6 +224,33 @@ def test_generative_and_dilated_convolution(stride):
     check_device_status(DEV)
 
 
+def test_minkunet34_is_bit_identical_with_and_without_tile_order(monkeypatch):
+    """The whole network (fused epilogues, offset-spanning slots, stem and head kernels) gives the same
+    bits whether the 3x3x3 layers run in tile order or in row order, and the same bits twice."""
+    import warpconvnet_b200.nn.functional.sparse_conv as F
+    from warpconvnet_b200 import POINT_ORDERING
+    from warpconvnet_b200.examples.mink_unet import MinkUNet34
+    scenes = [synthetic.room_scene(30000, 0.02, 800 + i, "raster_crop") for i in range(2)]
+    coords, offsets = synthetic.batch_scenes(scenes)
+    torch.manual_seed(7)
+    model = MinkUNet34(3, 20).to(DEV).half().eval()
+    randomize_batchnorm_(model)
+    x = torch.rand(len(coords), 3, generator=torch.Generator().manual_seed(1)).half()
+
+    def run():
+        vox = Voxels(torch.from_numpy(coords[:, 1:].copy()).to(DEV), x.to(DEV), offsets=torch.from_numpy(offsets))
+        with torch.no_grad():
+            return model(vox.sort(POINT_ORDERING.MORTON_XYZ), restore_order=True)
+
+    a = run()
+    b = run()
+    monkeypatch.setattr(F, "TILE_ORDER_MIN_ROWS", 1 << 60)
+    c = run()
+    check_device_status(DEV)
+    assert torch.isfinite(a.float()).all() and float(a.float().abs().max()) > 0
+    assert torch.equal(a, b) and torch.equal(a, c)
+
+
 def test_minkunet_restore_order_equals_unpermute():
     """`restore_order=True` stores the head's rows through the sort permutation: the same
     numbers as un-permuting the sorted result afterwards."""
