@@ -26,11 +26,12 @@ namespace {
 
 constexpr int WG_ROWS = 128;          // rows per step (K extent of 8 instructions)
 constexpr int WG_MAX_STAGES = 4;
-constexpr int WG_EPI_THREADS = 128;   // warps 0..3
+constexpr int WG_EPI_WARPS = 4;        // warps 0..3
 constexpr int WG_PROD_WARP0 = 4;      // warps 4..11
 constexpr int WG_PROD_THREADS = 256;
 constexpr int WG_MMA_WARP = 12;
 constexpr int WG_THREADS = 416;
+static_assert(WG_PROD_WARP0 == WG_EPI_WARPS && WG_THREADS == (WG_MMA_WARP + 1) * 32, "role layout");
 
 struct WgradParams {
   const char* feats;     // [num_in, c_in]
