@@ -12,9 +12,15 @@
  *  - `stream` is a cudaStream_t passed as void*; work is enqueued on it and the call
  *    returns without synchronising.
  *  - conditions that can only be detected on the device (hash-table overflow, a bounded
- *    wait that ran out) are reported through `dev_status`, a device int32 the caller
- *    zeroes beforehand and reads back when it wants to check; kernels only ever store a
- *    negative wcn_status code into it.
+ *    wait that ran out, an index that names no row) are reported through `dev_status`, a
+ *    device int32 the caller zeroes beforehand and must read back (poll) when it wants to
+ *    know: kernels only ever store a negative wcn_status code into it, the most negative
+ *    one wins, and it stays set until the caller zeroes it again.  While it is set the
+ *    tensor-core kernels do no work: a convolution fills the rows it was asked for with
+ *    NaN, a weight gradient adds nothing.  An out-of-range index itself is never followed:
+ *    the access is skipped (the neighbour counts as absent) and WCN_ERR_BOUNDS is stored.
+ *  - the device the stream belongs to must be the current device of the calling thread
+ *    (launch geometry is taken from the current device's properties).
  *  - coordinates are int32 rows (batch, x, y, z).  The batch value INT32_MIN is reserved
  *    (it marks an empty hash slot).
  *
@@ -134,14 +140,15 @@ int wcn_kmap_search(const void* table, int64_t capacity, int hash_method, const 
 int wcn_kmap_scan(void* workspace, int64_t num_queries, int32_t num_offsets, int32_t* offsets,
                   void* stream);
 
-/* wcn_kmap_search with dilated windows: position (i, j, l) of the window probes
- * x*sx + (i - cx)*dx and so on; `dilation` NULL means 1.
- * Replaces kernel_offsets_from_size with a kernel_dilation and the offset-list search
- * _kernel_map_from_offsets (warpconvnet/geometry/coords/search/torch_discrete.py:44-77, 160-241). */
+/* wcn_kmap_search with dilated windows and a free window centre: position (i, j, l) of the
+ * window probes x*sx + (i - cx)*dx and so on; `dilation` NULL means 1, `center` = {cx,cy,cz}
+ * NULL means the default centre (size/2 for odd sizes, 0 for even sizes).
+ * Replaces kernel_offsets_from_size with a kernel_dilation / center_offset and the offset-list
+ * search _kernel_map_from_offsets (warpconvnet/geometry/coords/search/torch_discrete.py:44-77, 160-241). */
 int wcn_kmap_search_dilated(const void* table, int64_t capacity, int hash_method, const int32_t* queries,
                             int64_t num_queries, const int32_t* stride, const int32_t* kernel_size,
-                            const int32_t* dilation, int32_t num_offsets, int32_t* nbr, void* workspace,
-                            void* stream);
+                            const int32_t* dilation, const int32_t* center, int32_t num_offsets, int32_t* nbr,
+                            void* workspace, void* stream);
 
 /* wcn_kmap_search followed by wcn_kmap_scan, for callers that must not allocate device
  * memory.  Some hosts of this library cannot call cudaMalloc around it: plugins that are
@@ -154,8 +161,12 @@ int wcn_kmap_search_dilated(const void* table, int64_t capacity, int hash_method
  * Limit: num_offsets * ceil(num_queries / 256) + num_offsets + 16 <= 1048576 (about 9.9 M
  * queries for a 3x3x3 window); larger problems return WCN_ERR_SCRATCH_TOO_SMALL and launch
  * nothing.  The entry point calls no allocator of any kind.  The first call on a device
- * looks up the array's device address (cudaGetSymbolAddress); make that call before any
- * stream capture begins.  All calls on a device share the one array and it keeps the last
+ * looks up the array's device address (cudaGetSymbolAddress) for the CURRENT device, so the
+ * device that owns `stream` must be current in the calling thread; make that first call before
+ * any stream capture begins (concurrent first calls from several host threads are safe).  The
+ * scanned hit counts stay inside the library, so this call yields the dense table and the
+ * per-offset totals only: a caller that also wants the compact (in, out) lists runs
+ * wcn_kmap_count + wcn_kmap_scan + wcn_kmap_compact with a workspace of its own.  All calls on a device share the one array and it keeps the last
  * call's contents (nothing in it needs clearing between calls), so two calls whose kernels
  * overlap on the GPU — different streams, no ordering between them — race; serialise them.
  * Every GPU that loads the library holds the array until the process exits.
@@ -245,16 +256,18 @@ int wcn_morton20(const int32_t* coords, int64_t n, int32_t row_ints, int32_t col
 
 /* ------------------------------------------------------------------ convolution */
 
-/* dst[r, :] = src[idx[r], :]  (rows of `channels` elements).
+/* dst[r, :] = src[idx[r], :]  (rows of `channels` elements; src has num_src rows).  An idx
+ * outside [0, num_src) yields a zero row and WCN_ERR_BOUNDS in dev_status (NULL: not reported).
  * Replaces the `comp_in_feats[in_map]` gather of _explicit_gemm_forward_logic
  * (warpconvnet/nn/functional/sparse_conv.py:309). */
-int wcn_gather_rows(const void* src, const int32_t* idx, void* dst, int64_t num_rows,
-                    int32_t channels, int dtype, void* stream);
+int wcn_gather_rows(const void* src, int64_t num_src, const int32_t* idx, void* dst, int64_t num_rows,
+                    int32_t channels, int dtype, int32_t* dev_status, void* stream);
 
-/* dst[idx[r], :] += src[r, :]; idx must hold distinct rows (one kernel offset).
+/* dst[idx[r], :] += src[r, :]; idx must hold distinct rows (one kernel offset; dst has num_dst
+ * rows).  An idx outside [0, num_dst) is skipped and reported like above.
  * Replaces `output_feature_tensor[out_map] += ...` (sparse_conv.py:310). */
-int wcn_scatter_add_rows(const void* src, const int32_t* idx, void* dst, int64_t num_rows,
-                         int32_t channels, int dtype, void* stream);
+int wcn_scatter_add_rows(const void* src, const int32_t* idx, void* dst, int64_t num_dst, int64_t num_rows,
+                         int32_t channels, int dtype, int32_t* dev_status, void* stream);
 
 /* Bytes of the packed-weight buffer wcn_conv_fwd needs for (algo, shape, dtype); 0 when
  * the chosen kernel reads the weights as given. */
@@ -266,6 +279,14 @@ int wcn_conv_packed_weight_bytes(int algo, int32_t num_offsets, int32_t c_in, in
 int wcn_conv_pack_weight(int algo, const void* weight, int32_t num_offsets, int32_t c_in,
                          int32_t c_out, int dtype, void* packed, void* stream);
 
+/* Bytes of `workspace` wcn_conv_fwd needs for this problem on the current device (0: none).  Only
+ * the tensor-core kernel uses one, when it divides the kernel offsets of a row block among several
+ * CTAs (see split_k below): S * num_out * c_out fp32 partial sums.
+ * Replaces the cudaMalloc inside the reference's split-K launcher
+ * (warpconvnet/csrc/implicit_gemm_split_k.cu:254-258). */
+int wcn_conv_workspace_bytes(int algo, int64_t num_out, int32_t num_offsets, int32_t c_in, int32_t c_out,
+                             int dtype, int out_dtype, int32_t split_k, int64_t* bytes);
+
 /* Output-stationary sparse convolution with a fused epilogue:
  *   acc[s, :] = sum_k feats[nbr[k*M + s], :] @ weight[k]      (rows with nbr < 0 skipped, fp32 accumulation)
  *   m = out_rows[s]           (out_rows NULL: m = s; else a permutation of 0..M-1, see
@@ -276,30 +297,45 @@ int wcn_conv_pack_weight(int algo, const void* weight, int32_t num_offsets, int3
  *   out[m, :] = (out dtype) y
  * feats / weight share `dtype`; scale / shift are fp32 [c_out].  Each output row is written
  * once by the block that owns it: no atomics, bit-reproducible.
+ * feats_ld / residual_ld / out_ld are the distances between consecutive rows of the three
+ * matrices in elements (0 = dense: c_in / c_out), so a matrix may be a column block of a wider
+ * one (a skip connection's half of a concatenated buffer); rows must start on 16-byte boundaries
+ * for the tensor-core kernel.  nbr entries >= num_in count as absent and raise WCN_ERR_BOUNDS.
  * algo WCN_CONV_TCGEN05 needs dtype f16/bf16, c_in % 32 == 0, c_out % 16 == 0, 16 <= c_out <= 256
  * and `packed_weight` from wcn_conv_pack_weight; WCN_CONV_AUTO picks it when those hold and
  * packed_weight is not NULL, else the SIMT kernel.
+ * split_k: the tensor-core kernel may divide the kernel offsets of a 128-row block among S CTAs
+ * (slice s owns offsets [s*K/S, (s+1)*K/S)), each leaving fp32 partial sums in `workspace`, which
+ * a second kernel adds in slice order before the epilogue: for problems with fewer row blocks
+ * than multiprocessors.  0 = the library decides, 1 = never, 2..16 = that many slices; a negative
+ * value divides the OUTPUT COLUMNS into -split_k blocks instead (a tuning aid).  `workspace` must
+ * hold wcn_conv_workspace_bytes(...) for the same arguments (NULL / 0 when that is 0).  Results
+ * are the same bits on every run for a given S; different S round differently (fp32 sums are
+ * grouped by slice).
  * Replaces implicit_gemm (warpconvnet/csrc/warpconvnet_pybind.cpp:732-837,
- * warpconvnet/csrc/implicit_gemm.cu:44-267) and cutlass_gemm_AD_gather_scatter
- * (warpconvnet_pybind.cpp:396-509, warpconvnet/csrc/cutlass_gemm_gather_scatter.cu:207-464),
- * the per-offset loop around them (warpconvnet/nn/functional/sparse_conv.py:396-413, 516-544),
- * the bias add (sparse_conv.py:1794-1795) and the BatchNorm1d / ReLU / residual-add chain of
- * the model blocks (examples/mink_unet.py:36-47, 129-141). */
-int wcn_conv_fwd(int algo, const void* feats, int64_t num_in, const void* weight,
-                 const void* packed_weight, const int32_t* nbr, const int32_t* out_rows,
-                 int64_t num_out, int32_t num_offsets, int32_t c_in, int32_t c_out, int dtype, const float* scale,
-                 const float* shift, const void* residual, int relu, void* out, int out_dtype,
+ * warpconvnet/csrc/implicit_gemm.cu:44-267) and cutlass_gemm_AD_gather_scatter with its
+ * split_k_slices argument (warpconvnet_pybind.cpp:396-509,
+ * warpconvnet/csrc/cutlass_gemm_gather_scatter.cu:176-464), the per-offset loop around them
+ * (warpconvnet/nn/functional/sparse_conv.py:396-413, 516-544), the bias add
+ * (sparse_conv.py:1794-1795) and the BatchNorm1d / ReLU / residual-add / concatenation chain of
+ * the model blocks (examples/mink_unet.py:36-47, 129-141, 340-358). */
+int wcn_conv_fwd(int algo, const void* feats, int64_t num_in, int64_t feats_ld, const void* weight,
+                 const void* packed_weight, const int32_t* nbr, const int32_t* out_rows, int64_t num_out,
+                 int32_t num_offsets, int32_t c_in, int32_t c_out, int dtype, const float* scale,
+                 const float* shift, const void* residual, int64_t residual_ld, int relu, void* out,
+                 int64_t out_ld, int out_dtype, int32_t split_k, void* workspace, int64_t workspace_bytes,
                  int32_t* dev_status, void* stream);
 
 /* Pooling over a kernel map: out[m, :] = op over the offsets k with nbr[k*M + m] >= 0 of
  * feats[nbr[k*M + m], :] (fp32 accumulation, offsets in ascending order; rows without a neighbour
  * become 0; mean divides by the number of neighbours).  With the transposed table of a
- * non-overlapping pooling it is the un-pooling gather.
+ * non-overlapping pooling it is the un-pooling gather.  nbr entries >= num_in count as absent
+ * and raise WCN_ERR_BOUNDS in dev_status (NULL: not reported).
  * Replaces kernel_map.to_csr() + row_reduction / torch_scatter.segment_csr of sparse_reduce
  * (warpconvnet/nn/functional/sparse_pool.py:87-92, warpconvnet/ops/reductions.py:36-70) and the
  * argsort + gather of sparse_unpool (sparse_pool.py:168-172). */
-int wcn_row_reduce(const void* feats, const int32_t* nbr, int64_t num_out, int32_t num_offsets,
-                   int32_t channels, int dtype, int op, void* out, void* stream);
+int wcn_row_reduce(const void* feats, int64_t num_in, const int32_t* nbr, int64_t num_out, int32_t num_offsets,
+                   int32_t channels, int dtype, int op, void* out, int32_t* dev_status, void* stream);
 
 /* Weight gradient of the convolution above, accumulated into grad_weight[K, c_in, c_out] (fp32; the
  * caller zeroes it):
@@ -317,6 +353,15 @@ int wcn_row_reduce(const void* feats, const int32_t* nbr, int64_t num_out, int32
 int wcn_conv_wgrad(const void* feats, int64_t num_in, const void* grad_out, const int32_t* nbr,
                    const int32_t* out_rows, const uint32_t* tile_masks, int64_t num_out, int32_t num_offsets, int32_t c_in, int32_t c_out, int dtype,
                    float* grad_weight, int32_t* dev_status, void* stream);
+
+/* ------------------------------------------------------------------ self test */
+
+/* Checks the library's bounded device-side waits: launches one small kernel that waits, with a
+ * limit of `limit_cycles` SM clock cycles (1e3 .. 2e9), for a barrier phase that nothing can
+ * complete.  The wait must give up, store WCN_ERR_WAIT_EXPIRED in dev_status and let the kernel
+ * end normally; gave_up (device int32, may be NULL) receives 1 when it did.  The context stays
+ * usable.  No counterpart in the reference (its kernels have no device-side waits). */
+int wcn_selftest_bounded_wait(int64_t limit_cycles, int32_t* dev_status, int32_t* gave_up, void* stream);
 
 #ifdef __cplusplus
 }

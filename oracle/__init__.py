@@ -29,6 +29,15 @@ Parity status
 * Explicit-GEMM convolution: PINNED — ``sparse_conv.py`` is checked against the
   reference's ``_explicit_gemm_forward_logic`` run on CPU tensors and against
   golden vectors generated from it.
+* Dilated windows and custom window centres: PINNED — ``kernel_map_found`` with a
+  dilation / centre equals the reference's offset-list kernel
+  (``kernel_map_offset_*``) run on its own ``kernel_offsets_from_size`` lists
+  (``tests/golden/kmap_extra.npz``).
+* Output support of a generative convolution (``expand_coords``): pinned as a SET
+  against the reference's expansion loop run with its own hash-search kernel.
+* Window reductions (``sparse_conv.window_reduce``): pinned to the reference's
+  ``IntSearchResult.to_csr`` + ``row_reduction`` with ``torch.segment_reduce``
+  standing in for ``torch_scatter.segment_csr`` (third-party, not installed here).
 * Stride-2 output coordinates: pinned as a SET (the reference's row order is
   run-to-run nondeterministic); compared after lexicographic sorting.
 * CUTLASS implicit GEMM: third-party arithmetic absent from the reference tree

@@ -123,18 +123,19 @@ def identity_map_index(kernel_size: Sequence[int], n_in: int, n_out: int) -> Opt
 
 def kernel_map_found(
     in_coords: np.ndarray, out_coords: np.ndarray, stride: Sequence[int], kernel_size: Sequence[int],
-    kernel_dilation: Optional[Sequence[int]] = None
+    kernel_dilation: Optional[Sequence[int]] = None, center_offset: Optional[Sequence[int]] = None
 ) -> np.ndarray:
     """found[K, M]: input row matching ``out*stride + offset[k]`` or -1 (offsets scaled by the
-    dilation, torch_discrete.py:60-77).
+    dilation and shifted by a custom window centre, torch_discrete.py:60-77).
 
     Restates ``kernel_map_size_4d_templated``
-    (warpconvnet/csrc/discrete_kernels.cu:264-334) with the stride product of
+    (warpconvnet/csrc/discrete_kernels.cu:264-334) and, for dilated or re-centred windows,
+    ``kernel_map_offset_templated`` (discrete_kernels.cu:129-180) with the stride product of
     ``generate_kernel_map`` (torch_discrete.py:406-416).
     """
     in_coords = np.ascontiguousarray(in_coords, dtype=np.int32)
     out_coords = np.ascontiguousarray(out_coords, dtype=np.int32)
-    offs = kernel_offsets_from_size(kernel_size, kernel_dilation)
+    offs = kernel_offsets_from_size(kernel_size, kernel_dilation, center_offset)
     K, M = len(offs), len(out_coords)
     svec = np.array([1, *stride], dtype=np.int32)
     q0 = out_coords * svec

@@ -23,14 +23,22 @@ TARGETS = {
 
 
 def default_reference_root():
-    return os.environ.get("WCN_REFERENCE_ROOT", "/root/reference")
+    """Where the reference project is checked out: the WCN_REFERENCE_ROOT environment variable,
+    else a directory named ``reference`` beside this repository if it holds the package.
+    Neither means "not on this machine": nothing is built and the tests that need the compiled
+    reference skip."""
+    root = os.environ.get("WCN_REFERENCE_ROOT", "")
+    if root:
+        return root
+    sibling = os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
+    return sibling if os.path.isdir(os.path.join(sibling, "warpconvnet")) else ""
 
 
 def build(reference_root=None, force=False, verbose=False):
     """Compile every target whose reference source exists. Returns the list built."""
     reference_root = reference_root or default_reference_root()
     built = []
-    if not os.path.isdir(reference_root):
+    if not reference_root or not os.path.isdir(reference_root):
         return built
     os.makedirs(OUT, exist_ok=True)
     for lib, (driver, rel_src) in TARGETS.items():

@@ -83,6 +83,20 @@ def ref_kernel_map_found(in_coords, out_coords, stride, kernel_size, method="cit
     return found
 
 
+def ref_kernel_map_found_offsets(in_coords, out_coords, stride, kernel_offsets, method="city"):
+    """found[K, M] from the reference's ``kernel_map_offset_*`` kernel for an explicit offset list
+    ``[K, 4]`` (what ``kernel_offsets_from_size`` returns for a dilation / custom centre)."""
+    table = RefHashTable(in_coords, method)
+    q = np.ascontiguousarray(np.asarray(out_coords, dtype=np.int32) * np.array([1, *stride], dtype=np.int32))
+    offs = np.ascontiguousarray(kernel_offsets, dtype=np.int32)
+    found = np.empty((len(offs), len(q)), dtype=np.int32)
+    rc = _lib("libref_discrete.so").ref_kernel_map_offset(
+        _iptr(table.table), _iptr(table.keys), _iptr(q), _iptr(offs), _iptr(found), len(q), 4, len(offs),
+        table.capacity, table.method)
+    assert rc == 0
+    return found
+
+
 def ref_compact_found(found: np.ndarray):
     """The reference's compaction: torch-side cumsum restated with NumPy
     (torch_discrete.py:103-119) + its own scatter kernel."""
@@ -122,28 +136,65 @@ def ref_morton20(coords_xyz: np.ndarray) -> np.ndarray:
 
 
 def reference_tree_present(root: str | None = None) -> bool:
-    root = root or os.environ.get("WCN_REFERENCE_ROOT", "/root/reference")
-    return os.path.isdir(os.path.join(root, "warpconvnet"))
+    from .ref_build import default_reference_root
+    root = root or default_reference_root()
+    return bool(root) and os.path.isdir(os.path.join(root, "warpconvnet"))
 
 
 def import_reference_python(root: str | None = None):
     """Import the reference package with cupy / warp / torch_scatter / the
     compiled ``_C`` module replaced by mocks; returns a namespace with the few
     pure-torch entry points that run on CPU tensors."""
-    root = root or os.environ.get("WCN_REFERENCE_ROOT", "/root/reference")
-    for name in ("cupy", "cupy.cuda", "warp", "warp.utils", "torch_scatter", "warpconvnet._C"):
+    from .ref_build import default_reference_root
+    root = root or default_reference_root()
+    if not reference_tree_present(root):
+        raise RuntimeError("set WCN_REFERENCE_ROOT to the reference project's checkout")
+    for name in ("cupy", "cupy.cuda", "warp", "warp.utils", "warpconvnet._C"):
         if name not in sys.modules:
             sys.modules[name] = mock.MagicMock(name=name)
+    if "torch_scatter" not in sys.modules:
+        # torch_scatter is not installed here.  Its ``segment_csr(src, indptr, reduce)`` reduces the
+        # rows src[indptr[i]:indptr[i+1]]; PyTorch's own ``torch.segment_reduce`` does the same, so
+        # the reference's ``row_reduction`` runs on top of it.
+        import torch
+        stand_in = types.ModuleType("torch_scatter")
+
+        def segment_csr(src, indptr, out=None, reduce="sum"):
+            return torch.segment_reduce(src, {"mul": "prod"}.get(reduce, reduce), offsets=indptr.long(), axis=0)
+
+        stand_in.segment_csr = segment_csr
+        sys.modules["torch_scatter"] = stand_in
     if root not in sys.path:
         sys.path.insert(0, root)
     from warpconvnet.geometry.coords.search.search_results import IntSearchResult
     from warpconvnet.geometry.coords.search.torch_discrete import kernel_offsets_from_size
     from warpconvnet.nn.functional.sparse_conv import _explicit_gemm_forward_logic
     from warpconvnet.nn.modules.sparse_conv import SpatiallySparseConv
+    from warpconvnet.ops.reductions import row_reduction
 
     return types.SimpleNamespace(
         IntSearchResult=IntSearchResult,
         kernel_offsets_from_size=kernel_offsets_from_size,
         explicit_gemm_forward=_explicit_gemm_forward_logic,
         SpatiallySparseConv=SpatiallySparseConv,
+        row_reduction=row_reduction,
     )
+
+
+def ref_expand_coords(coords: np.ndarray, kernel_offsets: np.ndarray, kernel_batch: int, method: str = "city"):
+    """The coordinate set the reference's ``expand_coords`` produces
+    (warpconvnet/geometry/coords/ops/expand.py:17-64), with every hash-table search done by the
+    reference's own search kernel: offsets are applied in batches of ``kernel_batch``, the
+    candidates that the current table does not hold are appended, and the table is rebuilt over
+    the distinct rows.  Returned in lexicographic order (the reference's row order depends on
+    hash slots)."""
+    base = np.ascontiguousarray(coords, dtype=np.int32)
+    unique = base
+    table = RefHashTable(unique, method)
+    offs = np.asarray(kernel_offsets, dtype=np.int32)
+    for s in range(0, len(offs), kernel_batch):
+        cand = (base[None, :, :] + offs[s:s + kernel_batch, None, :]).reshape(-1, base.shape[1])
+        missing = table.search(cand) < 0
+        unique = np.unique(np.concatenate([unique, cand[missing]], 0), axis=0)
+        table = RefHashTable(unique, method)
+    return unique[np.lexsort(tuple(unique[:, d] for d in reversed(range(unique.shape[1]))))]

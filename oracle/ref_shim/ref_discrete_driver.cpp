@@ -50,3 +50,31 @@ extern "C" int ref_map_found_indices_to_maps(const int* found, const int* mapped
   }
   return 0;
 }
+
+// found[k * M + m] for an explicit list of kernel offsets [K, key_dim] (batch column first),
+// exactly as launched by _kernel_map_from_offsets (torch_discrete.py:160-241): 2-D grid of
+// (ceil(M/128), ceil(K/8)) blocks of (128, 8) threads.  This is the reference's path for
+// dilated windows and custom window centres.
+extern "C" int ref_kernel_map_offset(const int* table_kvs, const int* keys, const int* queries,
+                                     const int* kernel_offsets, int* found, int num_queries, int key_dim,
+                                     int num_offsets, int capacity, int hash_method) {
+  const int tx = 128, ty = 8;
+  blockDim = {(unsigned)tx, (unsigned)ty, 1};
+  unsigned gx = (num_queries + tx - 1) / tx, gy = (num_offsets + ty - 1) / ty;
+  gridDim = {gx, gy, 1};
+  for (unsigned by = 0; by < gy; ++by)
+    for (unsigned bx = 0; bx < gx; ++bx) {
+      blockIdx = {bx, by, 0};
+      for (unsigned y = 0; y < (unsigned)ty; ++y)
+        for (unsigned x = 0; x < (unsigned)tx; ++x) {
+          threadIdx = {x, y, 0};
+          switch (hash_method) {
+            case 0: kernel_map_offset_fnv1a(table_kvs, keys, queries, kernel_offsets, found, num_queries, key_dim, num_offsets, capacity); break;
+            case 1: kernel_map_offset_city(table_kvs, keys, queries, kernel_offsets, found, num_queries, key_dim, num_offsets, capacity); break;
+            case 2: kernel_map_offset_murmur(table_kvs, keys, queries, kernel_offsets, found, num_queries, key_dim, num_offsets, capacity); break;
+            default: return -1;
+          }
+        }
+    }
+  return 0;
+}

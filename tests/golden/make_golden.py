@@ -42,6 +42,9 @@ def batched_cloud(rng, n_per_batch, lo, hi):
 def main():
     ref_build.build(force=True)
     ref = ref_loader.import_reference_python()
+    if sys.argv[1:] == ["extra"]:  # only the newer fixture; the others stay byte-identical
+        extra(ref)
+        return
     rng = np.random.default_rng(1234)
 
     # 1. kernel offsets
@@ -108,9 +111,41 @@ def main():
         offsets=f1, in_maps_sum=np.array(i1.astype(np.int64).sum()), out_maps_sum=np.array(o1.astype(np.int64).sum()),
         weight_bound=np.array(float(w1.abs().max())),
     )
+    extra(ref)
     for f in sorted(os.listdir(OUT)):
         if f.endswith(".npz"):
             print(f, os.path.getsize(os.path.join(OUT, f)))
+
+
+def extra(ref):
+    """kmap_extra.npz: dilated and re-centred kernel maps (the reference's offset-list kernel),
+    the output support of a generative convolution (its expand_coords with its own search kernel)
+    and window reductions (its to_csr + row_reduction)."""
+    rng = np.random.default_rng(4321)
+    coords = batched_cloud(rng, [700, 25, 500], -7, 7)
+    dil, ctr = (2, 1, 3), (0, 1, 2)
+    offs_d = ref.kernel_offsets_from_size((3, 3, 3), dil).numpy()
+    offs_c = ref.kernel_offsets_from_size((3, 2, 3), (1, 1, 1), center_offset=ctr).numpy()
+    found_d = ref_loader.ref_kernel_map_found_offsets(coords, coords, (1, 1, 1), offs_d)
+    found_c = ref_loader.ref_kernel_map_found_offsets(coords, coords, (1, 1, 1), offs_c)
+    coarse, _ = km.stride_coords(coords, (2, 2, 2))
+    found_ds = ref_loader.ref_kernel_map_found_offsets(coords, coarse, (2, 2, 2), offs_d)
+    offs_e = ref.kernel_offsets_from_size((3, 3, 3), (1, 2, 1)).numpy()
+    grown = ref_loader.ref_expand_coords(coords, offs_e, kernel_batch=9)  # 27 // kernel_size[0], expand.py:28-29
+    # pooling over the 2x2x2 stride-2 map: the reference's CSR form and row_reduction
+    i222, o222, f222 = ref_loader.ref_generate_kernel_map(coords, coarse, (2, 2, 2), (2, 2, 2))
+    kmap = ref.IntSearchResult(torch.from_numpy(i222), torch.from_numpy(o222), torch.from_numpy(f222), None)
+    in_csr, uniq_out, splits = kmap.to_csr()
+    feats = torch.from_numpy(rng.standard_normal((len(coords), 6)).astype(np.float32))
+    pooled = {}
+    for red in ("max", "min", "mean", "sum", "mul", "var", "std"):
+        out = torch.zeros(len(coarse), 6)
+        out[uniq_out.long()] = ref.row_reduction(feats[in_csr.long()], splits, red)  # sparse_pool.py:87-104
+        pooled["pool_" + red] = out.numpy()
+    np.savez_compressed(
+        os.path.join(OUT, "kmap_extra.npz"), coords=coords, coarse=coarse, dilation=np.array(dil), center=np.array(ctr),
+        offs_d=offs_d, offs_c=offs_c, found_d=found_d, found_c=found_c, found_ds=found_ds, grown=grown,
+        in222=i222, out222=o222, off222=f222, feats=feats.numpy(), **pooled)
 
 
 if __name__ == "__main__":

@@ -104,6 +104,38 @@ def test_probe_sequence_restatement_tiny():
         assert np.array_equal(t.search(q), km.hash_search(keys, q))
 
 
+def test_dilated_and_recentred_maps_match_reference(golden):
+    """Dilated windows and a custom window centre: the oracle's found[K, M] against the reference's
+    offset-list kernel (discrete_kernels.cu:129-180) run on its own offset lists."""
+    g = golden("kmap_extra.npz")
+    dil, ctr = tuple(g["dilation"]), tuple(g["center"])
+    assert np.array_equal(km.kernel_offsets_from_size((3, 3, 3), dil), g["offs_d"])
+    assert np.array_equal(km.kernel_offsets_from_size((3, 2, 3), None, ctr), g["offs_c"])
+    assert np.array_equal(km.kernel_map_found(g["coords"], g["coords"], (1, 1, 1), (3, 3, 3), dil), g["found_d"])
+    assert np.array_equal(km.kernel_map_found(g["coords"], g["coords"], (1, 1, 1), (3, 2, 3), None, ctr), g["found_c"])
+    assert np.array_equal(km.kernel_map_found(g["coords"], g["coarse"], (2, 2, 2), (3, 3, 3), dil), g["found_ds"])
+    assert (g["found_d"] >= 0).sum() > len(g["coords"])  # the fixture is not trivially empty
+
+
+def test_expand_coords_matches_reference(golden):
+    """Output support of a generative convolution: the oracle's set against the reference's
+    expand_coords loop run with its own hash-search kernel."""
+    g = golden("kmap_extra.npz")
+    out, offsets = km.expand_coords(g["coords"], (3, 3, 3), (1, 2, 1))
+    assert np.array_equal(out, g["grown"])
+    assert offsets[-1] == len(out) and len(out) > len(g["coords"])
+
+
+@pytest.mark.parametrize("red", ["max", "min", "mean", "sum", "mul", "var", "std"])
+def test_window_reduce_matches_reference(golden, red):
+    """Pooling: the oracle's window_reduce against the reference's to_csr + row_reduction
+    (ops/reductions.py:36-70) with torch.segment_reduce standing in for torch_scatter.segment_csr."""
+    g = golden("kmap_extra.npz")
+    got = osc.window_reduce(g["feats"], g["in222"], g["out222"], len(g["coarse"]), red)
+    # the reference evaluates mean(x^2) - mean(x)^2 in fp32 (cancellation); the root magnifies that
+    assert np.allclose(got, g["pool_" + red], rtol=1e-5, atol=2e-4 if red == "std" else 1e-5)
+
+
 # -- against the reference's kernels compiled for the host (built where the reference tree is present)
 
 needs_ref = pytest.mark.skipif(not ref_loader.have_compiled_reference(), reason="oracle/_ref not built")

@@ -36,23 +36,25 @@ SIGNATURES = {
     "wcn_kmap_search": [_c_vp, _c_i64, _c_i32, _c_vp, _c_i64, _c_vp, _c_vp, _c_i32, _c_vp, _c_vp, _c_vp],
     "wcn_kmap_search_static": [_c_vp, _c_i64, _c_i32, _c_vp, _c_i64, _c_vp, _c_vp, _c_i32, _c_vp, _c_vp, _c_vp],
     "wcn_kmap_search_self": [_c_vp, _c_i64, _c_i32, _c_vp, _c_i64, _c_vp, _c_vp, _c_vp, _c_vp],
-    "wcn_kmap_search_dilated": [_c_vp, _c_i64, _c_i32, _c_vp, _c_i64, _c_vp, _c_vp, _c_vp, _c_i32, _c_vp, _c_vp, _c_vp],
+    "wcn_kmap_search_dilated": [_c_vp, _c_i64, _c_i32, _c_vp, _c_i64, _c_vp, _c_vp, _c_vp, _c_vp, _c_i32, _c_vp, _c_vp, _c_vp],
     "wcn_kmap_count": [_c_vp, _c_i64, _c_i32, _c_vp, _c_vp],
     "wcn_kmap_scan": [_c_vp, _c_i64, _c_i32, _c_vp, _c_vp],
     "wcn_kmap_compact": [_c_vp, _c_i64, _c_i32, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp],
     "wcn_nbr_from_maps": [_c_vp, _c_vp, _c_vp, _c_i32, _c_i64, _c_i64, _c_vp, _c_vp],
     "wcn_nbr_transpose": [_c_vp, _c_i32, _c_i64, _c_i64, _c_vp, _c_vp],
     "wcn_morton20": [_c_vp, _c_i64, _c_i32, _c_i32, _c_vp, _c_vp, _c_vp],
-    "wcn_gather_rows": [_c_vp, _c_vp, _c_vp, _c_i64, _c_i32, _c_i32, _c_vp],
-    "wcn_scatter_add_rows": [_c_vp, _c_vp, _c_vp, _c_i64, _c_i32, _c_i32, _c_vp],
+    "wcn_gather_rows": [_c_vp, _c_i64, _c_vp, _c_vp, _c_i64, _c_i32, _c_i32, _c_vp, _c_vp],
+    "wcn_scatter_add_rows": [_c_vp, _c_vp, _c_vp, _c_i64, _c_i64, _c_i32, _c_i32, _c_vp, _c_vp],
     "wcn_conv_packed_weight_bytes": [_c_i32, _c_i32, _c_i32, _c_i32, _c_i32, _p_i64],
     "wcn_conv_pack_weight": [_c_i32, _c_vp, _c_i32, _c_i32, _c_i32, _c_i32, _c_vp, _c_vp],
     "wcn_kmap_tile_order": [_c_vp, _c_i64, _c_i32, _c_vp, _c_vp, _c_vp],
-    "wcn_row_reduce": [_c_vp, _c_vp, _c_i64, _c_i32, _c_i32, _c_i32, _c_i32, _c_vp, _c_vp],
+    "wcn_row_reduce": [_c_vp, _c_i64, _c_vp, _c_i64, _c_i32, _c_i32, _c_i32, _c_i32, _c_vp, _c_vp, _c_vp],
     "wcn_kmap_tile_masks": [_c_vp, _c_i64, _c_i32, _c_vp, _c_vp],
     "wcn_conv_wgrad": [_c_vp, _c_i64, _c_vp, _c_vp, _c_vp, _c_vp, _c_i64, _c_i32, _c_i32, _c_i32, _c_i32, _c_vp, _c_vp, _c_vp],
-    "wcn_conv_fwd": [_c_i32, _c_vp, _c_i64, _c_vp, _c_vp, _c_vp, _c_vp, _c_i64, _c_i32, _c_i32, _c_i32, _c_i32,
-                     _c_vp, _c_vp, _c_vp, _c_i32, _c_vp, _c_i32, _c_vp, _c_vp],
+    "wcn_conv_workspace_bytes": [_c_i32, _c_i64, _c_i32, _c_i32, _c_i32, _c_i32, _c_i32, _c_i32, _p_i64],
+    "wcn_conv_fwd": [_c_i32, _c_vp, _c_i64, _c_i64, _c_vp, _c_vp, _c_vp, _c_vp, _c_i64, _c_i32, _c_i32, _c_i32, _c_i32,
+                     _c_vp, _c_vp, _c_vp, _c_i64, _c_i32, _c_vp, _c_i64, _c_i32, _c_i32, _c_vp, _c_i64, _c_vp, _c_vp],
+    "wcn_selftest_bounded_wait": [_c_i64, _c_vp, _c_vp, _c_vp],
 }
 
 _lib = None
@@ -64,6 +66,7 @@ KERNELS_PER_CALL = {
     "wcn_kmap_scan": 2, "wcn_kmap_compact": 1, "wcn_nbr_from_maps": 1, "wcn_nbr_transpose": 1, "wcn_morton20": 1,
     "wcn_kmap_tile_order": 3, "wcn_conv_wgrad": 1, "wcn_kmap_tile_masks": 1, "wcn_row_reduce": 1, "wcn_kmap_search_self": 1, "wcn_kmap_search_dilated": 1, "wcn_kmap_count": 1,
     "wcn_gather_rows": 1, "wcn_scatter_add_rows": 1, "wcn_conv_pack_weight": 1, "wcn_conv_fwd": 1,
+    "wcn_selftest_bounded_wait": 1,
 }
 LAUNCH_COUNTS: Counter = Counter()
 
@@ -165,13 +168,23 @@ def device_status(device: torch.device) -> torch.Tensor:
     return _status_words[key]
 
 
-def check_device_status(device: torch.device) -> None:
-    """Read the status word (synchronises) and raise if a kernel recorded a failure."""
-    word = device_status(device)
-    code = int(word.item())
+def raise_for_status(code: int, device: torch.device) -> None:
+    """Raise for a status-word value the caller has already brought to the host; the word is
+    zeroed so that the next launches run again."""
     if code != 0:
-        word.zero_()
-        raise RuntimeError(f"libwcn_b200 kernel reported: {status_string(code)} ({code})")
+        device_status(device).zero_()
+        raise RuntimeError(f"libwcn_b200 kernel reported: {status_string(int(code))} ({int(code)})")
+
+
+def check_device_status(device: torch.device) -> None:
+    """Read the status word (synchronises) and raise if a kernel recorded a failure.
+
+    Kernels report hash-table overflow, an expired bounded wait and out-of-range indices only
+    through this word, and the tensor-core kernels do no work while it is set (convolution
+    outputs are then filled with NaN).  The package reads it wherever it synchronises with the
+    host anyway (sizing strided coordinates, compacting a kernel map); a caller that never reaches
+    such a point should call this after the work it wants checked."""
+    raise_for_status(int(device_status(device).item()), device)
 
 
 def query_bytes(fn_name: str, *args) -> int:

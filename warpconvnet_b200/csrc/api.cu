@@ -3,31 +3,37 @@
 #include "wcn_common.cuh"
 
 // conv_simt.cu
-int wcn_conv_simt_fwd(const void* feats, const void* weight, const int32_t* nbr, const int32_t* out_rows,
-                      int64_t M, int K, int c_in,
-                      int c_out, int dtype, const float* scale, const float* shift, const void* residual,
-                      int relu, void* out, int out_dtype, cudaStream_t st);
+int wcn_conv_simt_fwd(const void* feats, int64_t num_in, int64_t feats_ld, const void* weight, const int32_t* nbr,
+                      const int32_t* out_rows, int64_t M, int K, int c_in, int c_out, int dtype, const float* scale,
+                      const float* shift, const void* residual, int64_t residual_ld, int relu, void* out,
+                      int64_t out_ld, int out_dtype, int32_t* dev_status, cudaStream_t st);
+bool wcn_conv_narrow_supported(int K, int c_in, int c_out, const void* out, int64_t out_ld, const void* residual,
+                               int64_t residual_ld, int out_dtype);
+int wcn_conv_narrow_fwd(const void* feats, int64_t num_in, int64_t feats_ld, const void* weight, const int32_t* nbr,
+                        const int32_t* out_rows, int64_t M, int K, int c_in, int c_out, int dtype,
+                        const float* scale, const float* shift, const void* residual, int64_t residual_ld, int relu,
+                        void* out, int64_t out_ld, int out_dtype, int32_t* dev_status, cudaStream_t st);
+bool wcn_conv_narrow_out_supported(int K, int c_in, int c_out, int dtype, const void* feats, int64_t feats_ld);
+int wcn_conv_narrow_out_fwd(const void* feats, int64_t num_in, int64_t feats_ld, const void* weight,
+                            const int32_t* nbr, const int32_t* out_rows, int64_t M, int K, int c_in, int c_out,
+                            int dtype, const float* scale, const float* shift, const void* residual,
+                            int64_t residual_ld, int relu, void* out, int64_t out_ld, int out_dtype,
+                            int32_t* dev_status, cudaStream_t st);
 // conv_tcgen05.cu
 bool wcn_conv_tcgen05_supported(int K, int c_in, int c_out, int dtype, int out_dtype);
 int64_t wcn_conv_tcgen05_packed_bytes(int K, int c_in, int c_out);
+int64_t wcn_conv_tcgen05_workspace_bytes(int64_t M, int K, int c_in, int c_out, int split_k);
 int wcn_conv_tcgen05_pack(const void* weight, int K, int c_in, int c_out, void* packed, cudaStream_t st);
-bool wcn_conv_narrow_supported(int K, int c_in, int c_out, const void* out, const void* residual);
-int wcn_conv_narrow_fwd(const void* feats, const void* weight, const int32_t* nbr, const int32_t* out_rows,
-                        int64_t M, int K, int c_in, int c_out, int dtype, const float* scale, const float* shift,
-                        const void* residual, int relu, void* out, int out_dtype, cudaStream_t st);
-bool wcn_conv_narrow_out_supported(int K, int c_in, int c_out, int dtype, const void* feats);
-int wcn_conv_narrow_out_fwd(const void* feats, const void* weight, const int32_t* nbr, const int32_t* out_rows,
-                            int64_t M, int K, int c_in, int c_out, int dtype, const float* scale,
-                            const float* shift, const void* residual, int relu, void* out, int out_dtype,
-                            cudaStream_t st);
+int wcn_conv_tcgen05_fwd(const void* feats, int64_t num_in, int64_t feats_ld, const void* packed, const int32_t* nbr,
+                         const int32_t* out_rows, int64_t M, int K, int c_in, int c_out, int dtype,
+                         const float* scale, const float* shift, const void* residual, int64_t residual_ld, int relu,
+                         void* out, int64_t out_ld, int out_dtype, int split_k, void* workspace,
+                         int64_t workspace_bytes, int32_t* dev_status, cudaStream_t st);
+// conv_wgrad_tcgen05.cu
 bool wcn_conv_wgrad_tcgen05_supported(int K, int c_in, int c_out, int dtype);
 int wcn_conv_wgrad_tcgen05(const void* feats, int64_t num_in, const void* grad_out, const int32_t* nbr,
                            const int32_t* out_rows, const uint32_t* tile_masks, int64_t M, int K, int c_in, int c_out, int dtype,
                            float* grad_weight, int32_t* dev_status, cudaStream_t st);
-int wcn_conv_tcgen05_fwd(const void* feats, int64_t num_in, const void* packed, const int32_t* nbr,
-                         const int32_t* out_rows, int64_t M, int K, int c_in,
-                         int c_out, int dtype, const float* scale, const float* shift, const void* residual,
-                         int relu, void* out, int out_dtype, int32_t* dev_status, cudaStream_t st);
 
 extern "C" int wcn_version(void) { return 100; }
 
@@ -66,40 +72,61 @@ extern "C" int wcn_conv_pack_weight(int algo, const void* weight, int32_t num_of
   return wcn_conv_tcgen05_pack(weight, num_offsets, c_in, c_out, packed, wcn_stream(stream));
 }
 
-extern "C" int wcn_conv_fwd(int algo, const void* feats, int64_t num_in, const void* weight,
+static bool conv_takes_tcgen05(int algo, bool tc_ok, const void* packed_weight, const int32_t* dev_status,
+                               int64_t num_in) {
+  return algo == WCN_CONV_TCGEN05 || (algo == WCN_CONV_AUTO && tc_ok && packed_weight && dev_status && num_in > 0);
+}
+
+extern "C" int wcn_conv_workspace_bytes(int algo, int64_t num_out, int32_t num_offsets, int32_t c_in, int32_t c_out,
+                                        int dtype, int out_dtype, int32_t split_k, int64_t* bytes) {
+  if (!bytes || num_out < 0 || num_offsets <= 0 || c_in <= 0 || c_out <= 0) return WCN_ERR_INVALID_PARAMETERS;
+  *bytes = 0;
+  if (algo == WCN_CONV_SIMT || !wcn_conv_tcgen05_supported(num_offsets, c_in, c_out, dtype, out_dtype)) return WCN_OK;
+  *bytes = wcn_conv_tcgen05_workspace_bytes(num_out, num_offsets, c_in, c_out, split_k);
+  return WCN_OK;
+}
+
+extern "C" int wcn_conv_fwd(int algo, const void* feats, int64_t num_in, int64_t feats_ld, const void* weight,
                             const void* packed_weight, const int32_t* nbr, const int32_t* out_rows,
-                            int64_t num_out,
-                            int32_t num_offsets, int32_t c_in, int32_t c_out, int dtype, const float* scale,
-                            const float* shift, const void* residual, int relu, void* out, int out_dtype,
-                            int32_t* dev_status, void* stream) {
+                            int64_t num_out, int32_t num_offsets, int32_t c_in, int32_t c_out, int dtype,
+                            const float* scale, const float* shift, const void* residual, int64_t residual_ld,
+                            int relu, void* out, int64_t out_ld, int out_dtype, int32_t split_k, void* workspace,
+                            int64_t workspace_bytes, int32_t* dev_status, void* stream) {
   if (num_in < 0 || num_out < 0 || num_offsets <= 0 || c_in <= 0 || c_out <= 0) return WCN_ERR_INVALID_PARAMETERS;
   if (dtype < WCN_F32 || dtype > WCN_BF16 || out_dtype < WCN_F32 || out_dtype > WCN_BF16)
     return WCN_ERR_INVALID_PARAMETERS;
+  if (feats_ld == 0) feats_ld = c_in;  // 0: rows are dense
+  if (out_ld == 0) out_ld = c_out;
+  if (residual_ld == 0) residual_ld = c_out;
+  if (feats_ld < c_in || out_ld < c_out || residual_ld < c_out) return WCN_ERR_INVALID_PARAMETERS;
   if (num_out == 0) return WCN_OK;
   if (!nbr || !out || (num_in > 0 && !feats)) return WCN_ERR_INVALID_PARAMETERS;
   cudaStream_t st = wcn_stream(stream);
   const bool tc_ok = wcn_conv_tcgen05_supported(num_offsets, c_in, c_out, dtype, out_dtype);
-  if (algo == WCN_CONV_TCGEN05 || (algo == WCN_CONV_AUTO && tc_ok && packed_weight && dev_status && num_in > 0)) {
+  if (conv_takes_tcgen05(algo, tc_ok, packed_weight, dev_status, num_in)) {
     if (!tc_ok) return WCN_ERR_UNSUPPORTED_CONFIG;
-    return wcn_conv_tcgen05_fwd(feats, num_in, packed_weight, nbr, out_rows, num_out, num_offsets, c_in, c_out, dtype, scale, shift,
-                                residual, relu, out, out_dtype, dev_status, st);
+    return wcn_conv_tcgen05_fwd(feats, num_in, feats_ld, packed_weight, nbr, out_rows, num_out, num_offsets, c_in,
+                                c_out, dtype, scale, shift, residual, residual_ld, relu, out, out_ld, out_dtype,
+                                split_k, workspace, workspace_bytes, dev_status, st);
   }
   if (algo != WCN_CONV_SIMT && algo != WCN_CONV_AUTO) return WCN_ERR_INVALID_PARAMETERS;
   if (!weight) return WCN_ERR_INVALID_PARAMETERS;
-  if (algo == WCN_CONV_AUTO && wcn_conv_narrow_supported(num_offsets, c_in, c_out, out, residual)) {
+  if (algo == WCN_CONV_AUTO && wcn_conv_narrow_supported(num_offsets, c_in, c_out, out, out_ld, residual, residual_ld, out_dtype)) {
     // a few input channels: the streaming kernel (same numbers as the FP32-pipe kernel)
-    const int rc = wcn_conv_narrow_fwd(feats, weight, nbr, out_rows, num_out, num_offsets, c_in, c_out, dtype, scale,
-                                       shift, residual, relu, out, out_dtype, st);
+    const int rc = wcn_conv_narrow_fwd(feats, num_in, feats_ld, weight, nbr, out_rows, num_out, num_offsets, c_in,
+                                       c_out, dtype, scale, shift, residual, residual_ld, relu, out, out_ld,
+                                       out_dtype, dev_status, st);
     if (rc != WCN_ERR_UNSUPPORTED_CONFIG) return rc;
   }
-  if (algo == WCN_CONV_AUTO && num_in > 0 && wcn_conv_narrow_out_supported(num_offsets, c_in, c_out, dtype, feats)) {
+  if (algo == WCN_CONV_AUTO && num_in > 0 && wcn_conv_narrow_out_supported(num_offsets, c_in, c_out, dtype, feats, feats_ld)) {
     // a few output channels (a classification head): one thread per output row
-    const int rc = wcn_conv_narrow_out_fwd(feats, weight, nbr, out_rows, num_out, num_offsets, c_in, c_out, dtype,
-                                           scale, shift, residual, relu, out, out_dtype, st);
+    const int rc = wcn_conv_narrow_out_fwd(feats, num_in, feats_ld, weight, nbr, out_rows, num_out, num_offsets, c_in,
+                                           c_out, dtype, scale, shift, residual, residual_ld, relu, out, out_ld,
+                                           out_dtype, dev_status, st);
     if (rc != WCN_ERR_UNSUPPORTED_CONFIG) return rc;
   }
-  return wcn_conv_simt_fwd(feats, weight, nbr, out_rows, num_out, num_offsets, c_in, c_out, dtype, scale, shift, residual,
-                           relu, out, out_dtype, st);
+  return wcn_conv_simt_fwd(feats, num_in, feats_ld, weight, nbr, out_rows, num_out, num_offsets, c_in, c_out, dtype,
+                           scale, shift, residual, residual_ld, relu, out, out_ld, out_dtype, dev_status, st);
 }
 
 extern "C" int wcn_conv_wgrad(const void* feats, int64_t num_in, const void* grad_out, const int32_t* nbr,

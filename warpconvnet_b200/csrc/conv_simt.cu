@@ -13,12 +13,20 @@ constexpr int TN = 64;   // output columns per block
 constexpr int TK = 16;   // input channels per step
 constexpr int NT = 256;  // threads: 16 x 16, each a 4 x 4 micro-tile
 
+// Row strides (elements) of the three matrices, the number of feature rows an index may name
+// and where to report one that does not (null: such an index is skipped silently).
+struct RowLayout {
+  int64_t in_ld, out_ld, res_ld;
+  int num_in;
+  int32_t* dev_status;
+};
+
 template <typename T, typename TO>
 __global__ void __launch_bounds__(NT)
 conv_simt_kernel(const T* __restrict__ feats, const T* __restrict__ weight, const int32_t* __restrict__ nbr,
                  const int32_t* __restrict__ out_rows, int64_t M, int K, int c_in, int c_out, const float* __restrict__ scale,
                  const float* __restrict__ shift, const TO* __restrict__ residual, int relu,
-                 TO* __restrict__ out) {
+                 TO* __restrict__ out, const RowLayout lay) {
   __shared__ float As[TK][TM + 4];
   __shared__ float Ws[TK][TN + 4];
   __shared__ int rows[TM];
@@ -34,6 +42,10 @@ conv_simt_kernel(const T* __restrict__ feats, const T* __restrict__ weight, cons
     if (threadIdx.x < TM) {
       const int64_t m = m0 + threadIdx.x;
       r = m < M ? __ldg(&nbr[(int64_t)k * M + m]) : -1;
+      if (r >= lay.num_in) {  // not a feature row: treated as absent and reported
+        r = -1;
+        if (lay.dev_status) atomicMin(lay.dev_status, (int)WCN_ERR_BOUNDS);
+      }
       rows[threadIdx.x] = r;
     }
     if (!__syncthreads_or(r >= 0)) continue;  // no neighbour at this offset in the tile
@@ -45,7 +57,7 @@ conv_simt_kernel(const T* __restrict__ feats, const T* __restrict__ weight, cons
         const int rr = e / TK, cc = e % TK;
         const int src = rows[rr];
         float v = 0.f;
-        if (src >= 0 && c0 + cc < c_in) v = wcn_to_float<T>(feats[(int64_t)src * c_in + c0 + cc]);
+        if (src >= 0 && c0 + cc < c_in) v = wcn_to_float<T>(feats[(int64_t)src * lay.in_ld + c0 + cc]);
         As[cc][rr] = v;
       }
       // W: TK x TN slice of weight[k]
@@ -84,9 +96,9 @@ conv_simt_kernel(const T* __restrict__ feats, const T* __restrict__ weight, cons
       if (n >= c_out) continue;
       float y = acc[i][j];
       y = wcn_affine(y, scale, shift, n);
-      if (residual) y = __fadd_rn(y, wcn_to_float<TO>(residual[m * c_out + n]));
+      if (residual) y = __fadd_rn(y, wcn_to_float<TO>(residual[m * lay.res_ld + n]));
       if (relu) y = fmaxf(y, 0.f);
-      out[m * c_out + n] = wcn_from_float<TO>(y);
+      out[m * lay.out_ld + n] = wcn_from_float<TO>(y);
     }
   }
 }
@@ -94,10 +106,10 @@ conv_simt_kernel(const T* __restrict__ feats, const T* __restrict__ weight, cons
 template <typename T, typename TO>
 int launch_simt(const void* feats, const void* weight, const int32_t* nbr, const int32_t* out_rows, int64_t M, int K, int c_in,
                 int c_out, const float* scale, const float* shift, const void* residual, int relu, void* out,
-                cudaStream_t st) {
+                const RowLayout& lay, cudaStream_t st) {
   dim3 grid((unsigned)((M + TM - 1) / TM), (unsigned)((c_out + TN - 1) / TN));
   conv_simt_kernel<T, TO><<<grid, NT, 0, st>>>((const T*)feats, (const T*)weight, nbr, out_rows, M, K, c_in, c_out, scale,
-                                              shift, (const TO*)residual, relu, (TO*)out);
+                                              shift, (const TO*)residual, relu, (TO*)out, lay);
   return cudaGetLastError() == cudaSuccess ? WCN_OK : WCN_ERR_EXECUTION;
 }
 
@@ -118,7 +130,7 @@ __global__ void __launch_bounds__(NT)
 conv_narrow_kernel(const T* __restrict__ feats, const T* __restrict__ weight, const int32_t* __restrict__ nbr,
                    const int32_t* __restrict__ out_rows, int64_t M, int K, int c_in, int c_out,
                    const float* __restrict__ scale, const float* __restrict__ shift,
-                   const TO* __restrict__ residual, int relu, TO* __restrict__ out) {
+                   const TO* __restrict__ residual, int relu, TO* __restrict__ out, const RowLayout lay) {
   __shared__ __align__(16) float w_s[NARROW_MAX_WEIGHTS];
   for (int i = threadIdx.x; i < K * c_in * c_out; i += NT) w_s[i] = wcn_to_float<T>(weight[i]);
   __syncthreads();
@@ -131,7 +143,11 @@ conv_narrow_kernel(const T* __restrict__ feats, const T* __restrict__ weight, co
   for (int k = 0; k < K; ++k) {
     const int src = __ldg(&nbr[(int64_t)k * M + slot]);
     if (src < 0) continue;
-    const T* x = feats + (int64_t)src * c_in;
+    if (src >= lay.num_in) {
+      if (lay.dev_status) atomicMin(lay.dev_status, (int)WCN_ERR_BOUNDS);
+      continue;
+    }
+    const T* x = feats + (int64_t)src * lay.in_ld;
     for (int c = 0; c < c_in; ++c) {
       const float xv = wcn_to_float<T>(x[c]);
       const float4 w0 = *reinterpret_cast<const float4*>(&w_s[(k * c_in + c) * c_out + n0]);
@@ -148,7 +164,7 @@ conv_narrow_kernel(const T* __restrict__ feats, const T* __restrict__ weight, co
   if (residual) {
 #pragma unroll
     for (int v = 0; v < VEC; ++v)
-      reinterpret_cast<uint4*>(tmp)[v] = __ldg(reinterpret_cast<const uint4*>(residual + m * c_out + n0) + v);
+      reinterpret_cast<uint4*>(tmp)[v] = __ldg(reinterpret_cast<const uint4*>(residual + m * lay.res_ld + n0) + v);
   }
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
@@ -159,17 +175,17 @@ conv_narrow_kernel(const T* __restrict__ feats, const T* __restrict__ weight, co
     tmp[j] = wcn_from_float<TO>(y);
   }
 #pragma unroll
-  for (int v = 0; v < VEC; ++v) reinterpret_cast<uint4*>(out + m * c_out + n0)[v] = reinterpret_cast<uint4*>(tmp)[v];
+  for (int v = 0; v < VEC; ++v) reinterpret_cast<uint4*>(out + m * lay.out_ld + n0)[v] = reinterpret_cast<uint4*>(tmp)[v];
 }
 
 template <typename T, typename TO>
 int launch_narrow(const void* feats, const void* weight, const int32_t* nbr, const int32_t* out_rows, int64_t M,
                   int K, int c_in, int c_out, const float* scale, const float* shift, const void* residual,
-                  int relu, void* out, cudaStream_t st) {
+                  int relu, void* out, const RowLayout& lay, cudaStream_t st) {
   const int64_t threads = M * (c_out >> 3);
   conv_narrow_kernel<T, TO><<<(unsigned)((threads + NT - 1) / NT), NT, 0, st>>>(
       (const T*)feats, (const T*)weight, nbr, out_rows, M, K, c_in, c_out, scale, shift, (const TO*)residual, relu,
-      (TO*)out);
+      (TO*)out, lay);
   return cudaGetLastError() == cudaSuccess ? WCN_OK : WCN_ERR_EXECUTION;
 }
 
@@ -185,7 +201,7 @@ __global__ void __launch_bounds__(NT)
 conv_narrow_out_kernel(const T* __restrict__ feats, const T* __restrict__ weight, const int32_t* __restrict__ nbr,
                        const int32_t* __restrict__ out_rows, int64_t M, int K, int c_in, int c_out,
                        const float* __restrict__ scale, const float* __restrict__ shift,
-                       const TO* __restrict__ residual, int relu, TO* __restrict__ out) {
+                       const TO* __restrict__ residual, int relu, TO* __restrict__ out, const RowLayout lay) {
   __shared__ __align__(16) float w_s[NARROW_MAX_WEIGHTS];  // [K][c_in][NP]
   for (int i = threadIdx.x; i < K * c_in * NP; i += NT) {
     const int n = i % NP, kc = i / NP;
@@ -201,7 +217,11 @@ conv_narrow_out_kernel(const T* __restrict__ feats, const T* __restrict__ weight
   for (int k = 0; k < K; ++k) {
     const int src = __ldg(&nbr[(int64_t)k * M + slot]);
     if (src < 0) continue;
-    const uint4* x = reinterpret_cast<const uint4*>(feats + (int64_t)src * c_in);
+    if (src >= lay.num_in) {
+      if (lay.dev_status) atomicMin(lay.dev_status, (int)WCN_ERR_BOUNDS);
+      continue;
+    }
+    const uint4* x = reinterpret_cast<const uint4*>(feats + (int64_t)src * lay.in_ld);
     const float* wk = w_s + (int64_t)k * c_in * NP;
     for (int c0 = 0; c0 < c_in; c0 += EPV) {
       const uint4 raw = __ldg(x + c0 / EPV);
@@ -222,10 +242,11 @@ conv_narrow_out_kernel(const T* __restrict__ feats, const T* __restrict__ weight
     }
   }
   const int64_t m = out_rows ? (int64_t)__ldg(&out_rows[slot]) : slot;
-  TO* orow = out + m * c_out;
-  const TO* rrow = residual ? residual + m * c_out : nullptr;
+  TO* orow = out + m * lay.out_ld;
+  const TO* rrow = residual ? residual + m * lay.res_ld : nullptr;
   constexpr int PER8 = (int)(8 / sizeof(TO));  // outputs per 8-byte store
-  const bool wide = (c_out % PER8) == 0 && (reinterpret_cast<uintptr_t>(out) & 7) == 0;  // rows start 8-byte aligned
+  const bool wide = (c_out % PER8) == 0 && (lay.out_ld % PER8) == 0 &&
+                    (reinterpret_cast<uintptr_t>(out) & 7) == 0;  // rows start 8-byte aligned
 #pragma unroll
   for (int j0 = 0; j0 < NP; j0 += PER8) {
     __align__(8) TO o[PER8];
@@ -253,11 +274,11 @@ conv_narrow_out_kernel(const T* __restrict__ feats, const T* __restrict__ weight
 template <typename T, typename TO>
 int launch_narrow_out(const void* feats, const void* weight, const int32_t* nbr, const int32_t* out_rows, int64_t M,
                       int K, int c_in, int c_out, const float* scale, const float* shift, const void* residual,
-                      int relu, void* out, cudaStream_t st) {
+                      int relu, void* out, const RowLayout& lay, cudaStream_t st) {
   const unsigned blocks = (unsigned)((M + NT - 1) / NT);
 #define WCN_NOUT(NPV) \
   conv_narrow_out_kernel<T, TO, NPV><<<blocks, NT, 0, st>>>((const T*)feats, (const T*)weight, nbr, out_rows, M, K, c_in, \
-                                                            c_out, scale, shift, (const TO*)residual, relu, (TO*)out)
+                                                            c_out, scale, shift, (const TO*)residual, relu, (TO*)out, lay)
   if (c_out <= 8) WCN_NOUT(8);
   else if (c_out <= 16) WCN_NOUT(16);
   else if (c_out <= 24) WCN_NOUT(24);
@@ -268,13 +289,22 @@ int launch_narrow_out(const void* feats, const void* weight, const int32_t* nbr,
 
 }  // namespace
 
-int wcn_conv_simt_fwd(const void* feats, const void* weight, const int32_t* nbr, const int32_t* out_rows,
-                      int64_t M, int K, int c_in,
-                      int c_out, int dtype, const float* scale, const float* shift, const void* residual,
-                      int relu, void* out, int out_dtype, cudaStream_t st) {
+static RowLayout make_layout(int64_t num_in, int64_t feats_ld, int64_t out_ld, int64_t residual_ld, int32_t* dev_status) {
+  RowLayout lay;
+  lay.in_ld = feats_ld; lay.out_ld = out_ld; lay.res_ld = residual_ld;
+  lay.num_in = (int)(num_in < 0x7FFFFFFFll ? num_in : 0x7FFFFFFFll);
+  lay.dev_status = dev_status;
+  return lay;
+}
+
+int wcn_conv_simt_fwd(const void* feats, int64_t num_in, int64_t feats_ld, const void* weight, const int32_t* nbr,
+                      const int32_t* out_rows, int64_t M, int K, int c_in, int c_out, int dtype, const float* scale,
+                      const float* shift, const void* residual, int64_t residual_ld, int relu, void* out,
+                      int64_t out_ld, int out_dtype, int32_t* dev_status, cudaStream_t st) {
+  const RowLayout lay = make_layout(num_in, feats_ld, out_ld, residual_ld, dev_status);
 #define WCN_SIMT_CASE(DT, T, ODT, TO) \
   if (dtype == DT && out_dtype == ODT) \
-    return launch_simt<T, TO>(feats, weight, nbr, out_rows, M, K, c_in, c_out, scale, shift, residual, relu, out, st);
+    return launch_simt<T, TO>(feats, weight, nbr, out_rows, M, K, c_in, c_out, scale, shift, residual, relu, out, lay, st);
   WCN_SIMT_CASE(WCN_F32, float, WCN_F32, float)
   WCN_SIMT_CASE(WCN_F16, __half, WCN_F16, __half)
   WCN_SIMT_CASE(WCN_BF16, __nv_bfloat16, WCN_BF16, __nv_bfloat16)
@@ -286,17 +316,23 @@ int wcn_conv_simt_fwd(const void* feats, const void* weight, const int32_t* nbr,
   return WCN_ERR_UNSUPPORTED_CONFIG;
 }
 
-bool wcn_conv_narrow_supported(int K, int c_in, int c_out, const void* out, const void* residual) {
+// Rows of `out` and `residual` must start on 16-byte boundaries for the vector stores.
+bool wcn_conv_narrow_supported(int K, int c_in, int c_out, const void* out, int64_t out_ld, const void* residual,
+                               int64_t residual_ld, int out_dtype) {
+  const int64_t osz = out_dtype == WCN_F32 ? 4 : 2;
   return c_in <= NARROW_MAX_CIN && c_out % 8 == 0 && (int64_t)K * c_in * c_out <= NARROW_MAX_WEIGHTS &&
-         (reinterpret_cast<uintptr_t>(out) & 15) == 0 && (reinterpret_cast<uintptr_t>(residual) & 15) == 0;
+         (reinterpret_cast<uintptr_t>(out) & 15) == 0 && (reinterpret_cast<uintptr_t>(residual) & 15) == 0 &&
+         (out_ld * osz) % 16 == 0 && (!residual || (residual_ld * osz) % 16 == 0);
 }
 
-int wcn_conv_narrow_fwd(const void* feats, const void* weight, const int32_t* nbr, const int32_t* out_rows,
-                        int64_t M, int K, int c_in, int c_out, int dtype, const float* scale, const float* shift,
-                        const void* residual, int relu, void* out, int out_dtype, cudaStream_t st) {
+int wcn_conv_narrow_fwd(const void* feats, int64_t num_in, int64_t feats_ld, const void* weight, const int32_t* nbr,
+                        const int32_t* out_rows, int64_t M, int K, int c_in, int c_out, int dtype,
+                        const float* scale, const float* shift, const void* residual, int64_t residual_ld, int relu,
+                        void* out, int64_t out_ld, int out_dtype, int32_t* dev_status, cudaStream_t st) {
+  const RowLayout lay = make_layout(num_in, feats_ld, out_ld, residual_ld, dev_status);
 #define WCN_NARROW_CASE(DT, T, ODT, TO) \
   if (dtype == DT && out_dtype == ODT) \
-    return launch_narrow<T, TO>(feats, weight, nbr, out_rows, M, K, c_in, c_out, scale, shift, residual, relu, out, st);
+    return launch_narrow<T, TO>(feats, weight, nbr, out_rows, M, K, c_in, c_out, scale, shift, residual, relu, out, lay, st);
   WCN_NARROW_CASE(WCN_F32, float, WCN_F32, float)
   WCN_NARROW_CASE(WCN_F16, __half, WCN_F16, __half)
   WCN_NARROW_CASE(WCN_BF16, __nv_bfloat16, WCN_BF16, __nv_bfloat16)
@@ -306,19 +342,22 @@ int wcn_conv_narrow_fwd(const void* feats, const void* weight, const int32_t* nb
   return WCN_ERR_UNSUPPORTED_CONFIG;
 }
 
-bool wcn_conv_narrow_out_supported(int K, int c_in, int c_out, int dtype, const void* feats) {
+// Feature rows must start on 16-byte boundaries for the vector loads.
+bool wcn_conv_narrow_out_supported(int K, int c_in, int c_out, int dtype, const void* feats, int64_t feats_ld) {
   const int np = (c_out + 7) / 8 * 8;
   return c_out <= 32 && (int64_t)K * c_in * np <= NARROW_MAX_WEIGHTS && (c_in * wcn_dtype_size(dtype)) % 16 == 0 &&
-         (reinterpret_cast<uintptr_t>(feats) & 15) == 0;
+         (feats_ld * wcn_dtype_size(dtype)) % 16 == 0 && (reinterpret_cast<uintptr_t>(feats) & 15) == 0;
 }
 
-int wcn_conv_narrow_out_fwd(const void* feats, const void* weight, const int32_t* nbr, const int32_t* out_rows,
-                            int64_t M, int K, int c_in, int c_out, int dtype, const float* scale,
-                            const float* shift, const void* residual, int relu, void* out, int out_dtype,
-                            cudaStream_t st) {
+int wcn_conv_narrow_out_fwd(const void* feats, int64_t num_in, int64_t feats_ld, const void* weight,
+                            const int32_t* nbr, const int32_t* out_rows, int64_t M, int K, int c_in, int c_out,
+                            int dtype, const float* scale, const float* shift, const void* residual,
+                            int64_t residual_ld, int relu, void* out, int64_t out_ld, int out_dtype,
+                            int32_t* dev_status, cudaStream_t st) {
+  const RowLayout lay = make_layout(num_in, feats_ld, out_ld, residual_ld, dev_status);
 #define WCN_NOUT_CASE(DT, T, ODT, TO) \
   if (dtype == DT && out_dtype == ODT) \
-    return launch_narrow_out<T, TO>(feats, weight, nbr, out_rows, M, K, c_in, c_out, scale, shift, residual, relu, out, st);
+    return launch_narrow_out<T, TO>(feats, weight, nbr, out_rows, M, K, c_in, c_out, scale, shift, residual, relu, out, lay, st);
   WCN_NOUT_CASE(WCN_F32, float, WCN_F32, float)
   WCN_NOUT_CASE(WCN_F16, __half, WCN_F16, __half)
   WCN_NOUT_CASE(WCN_BF16, __nv_bfloat16, WCN_BF16, __nv_bfloat16)

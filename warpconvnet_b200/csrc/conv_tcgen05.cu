@@ -19,7 +19,13 @@
 //    releases ring slots with tcgen05.commit;
 //  * epilogue warps read the accumulators with tcgen05.ld, apply scale/shift
 //    (folded BatchNorm or bias), residual add and ReLU, convert and store every
-//    output row exactly once.  No atomics, no split-K workspace, bit-reproducible.
+//    output row exactly once.  No atomics, bit-reproducible.
+//
+// Problems with fewer 128-row tiles than multiprocessors divide the kernel offsets of a tile
+// among S CTAs ("split-K over kernel offsets": slice s owns the offsets [s*K/S, (s+1)*K/S)).
+// Each CTA then leaves its fp32 accumulators in a caller-supplied workspace [S][M][C_out] and a
+// second kernel adds the S slices in slice order and runs the epilogue; still no atomics and the
+// same bits on every run.
 //
 // Every wait is bounded: a wait that runs out stores WCN_ERR_WAIT_EXPIRED in the
 // device status word, the other waits notice it and the CTA leaves through the
@@ -41,16 +47,6 @@ constexpr int MMA_WARP = 16;          // warps 16, 17: MMA issuers (even / odd s
 constexpr int MMA_ISSUERS = 2;
 constexpr int WEIGHT_WARP = 18;       // weight bulk copies
 constexpr int THREADS = 608;
-#ifdef WCN_WAIT_STATS
-// Development aid (never compiled into the shipped library): cycles each role spends
-// waiting, summed over CTAs into a global array.
-__device__ long long g_wait_stats[16];
-#define WCN_T0(var) const long long var = clock64()
-#define WCN_ACC(slot, var, cond) do { if (cond) atomicAdd((unsigned long long*)&g_wait_stats[slot], (unsigned long long)(clock64() - var)); } while (0)
-#else
-#define WCN_T0(var)
-#define WCN_ACC(slot, var, cond)
-#endif
 
 struct ConvTcParams {
   const char* feats;
@@ -58,6 +54,8 @@ struct ConvTcParams {
   const int32_t* nbr;
   const int32_t* out_rows;  // slot -> output row, or null for the identity
   int64_t M, num_in;
+  int64_t in_ld_bytes;      // distance between consecutive feature rows, bytes
+  int64_t out_ld, res_ld;   // distance between consecutive output / residual rows, elements
   int K, c_in, c_out;
   const float* scale;
   const float* shift;
@@ -72,7 +70,18 @@ struct ConvTcParams {
   int sa, sb;       // ring depths
   int kbc;          // channel slices per ring slot (a slot holds kbc K-major tiles side by side)
   int64_t supertiles;
+  int S;            // offset slices per supertile (split-K over kernel offsets); 1 = none
+  int64_t units;    // supertiles * S work units, walked by the persistent CTAs
+  float* partial;   // [S][M][c_out] fp32 accumulators of the slices (S > 1)
 };
+
+// Offsets of slice s of S: bits [s*K/S, (s+1)*K/S).
+__device__ __forceinline__ uint32_t slice_mask(int s, int S, int K) {
+  if (S <= 1) return 0xFFFFFFFFu;
+  const int lo = (s * K) / S, hi = ((s + 1) * K) / S;
+  const uint32_t upto_hi = hi >= 32 ? 0xFFFFFFFFu : ((1u << hi) - 1u);
+  return upto_hi & ~((1u << lo) - 1u);
+}
 
 template <typename TO> struct OutVec;
 template <> struct OutVec<float> {
@@ -182,7 +191,24 @@ conv_tcgen05_kernel(const ConvTcParams p) {
 
   if (tid == 0) ctl->skip = *(volatile int32_t*)p.dev_status;  // an earlier launch on this status word failed
   __syncthreads();
-  if (ctl->skip != 0) return;
+  if (ctl->skip != 0) {
+    // Nothing is computed while the status word holds an error.  The rows this CTA would have
+    // produced are filled with NaN so that the failure cannot pass for data (with offset slices
+    // the second kernel does the same).
+    if (p.S == 1) {
+      const TO nan = wcn_from_float<TO>(__int_as_float(0x7FC00000));
+      for (int64_t st = blockIdx.x; st < p.supertiles; st += gridDim.x) {
+        const int64_t m0 = st * G * BLOCK_M;
+        const int64_t rows = min((int64_t)G * BLOCK_M, p.M - m0);
+        for (int64_t i = tid; i < rows * BN; i += THREADS) {
+          const int64_t slot = m0 + i / BN;
+          const int64_t m = p.out_rows ? (int64_t)__ldg(&p.out_rows[slot]) : slot;
+          reinterpret_cast<TO*>(p.out)[m * p.out_ld + n0 + (int)(i % BN)] = nan;
+        }
+      }
+    }
+    return;
+  }
 
   if (tid == 0) {
     for (int s = 0; s < p.sa; ++s) { mbar_init(bar(&ctl->a_full[s]), GATHER_THREADS); mbar_init(bar(&ctl->a_empty[s]), MMA_ISSUERS); }
@@ -213,11 +239,18 @@ conv_tcgen05_kernel(const ConvTcParams p) {
     // ================================================================ index warps
     // Stage the neighbour table of a supertile (one supertile ahead of the copies):
     // rows_idx[ib][g][k][row] = input row, or -1 where there is no neighbour.
+    // Only the offsets of the unit's slice are read; the others are staged as "no neighbour",
+    // so every role downstream sees a supertile that simply has fewer offsets.  An index that
+    // does not name a feature row is treated as absent and reported (WCN_ERR_BOUNDS).
     const int itid = tid - EPI_THREADS;
+    const int num_in = (int)p.num_in;
     int ib = 0, iphase = 0, sphase = 0;
-    for (int64_t st = blockIdx.x; st < p.supertiles && ok; st += gridDim.x) {
+    bool bad = false;
+    for (int64_t wu = blockIdx.x; wu < p.units && ok; wu += gridDim.x) {
+      const int64_t st = p.S > 1 ? wu / p.S : wu;
+      const uint32_t kmask = slice_mask((int)(wu - st * p.S), p.S, K);
       const int64_t m0 = st * G * BLOCK_M;
-      if (!mbar_wait(bar(&ctl->info_empty[ib]), iphase ^ 1, p.dev_status, 64)) { ok = false; break; }
+      if (!mbar_wait(bar(&ctl->info_empty[ib]), iphase ^ 1, p.dev_status)) { ok = false; break; }
       int32_t* dst = rows_idx + ib * IDX_INTS;
       for (int g = 0; g < G; ++g) {
         const int64_t m = m0 + (int64_t)g * BLOCK_M + itid;
@@ -225,10 +258,11 @@ conv_tcgen05_kernel(const ConvTcParams p) {
         int r[MAX_OFFSETS];  // all loads are issued before the first one is consumed
 #pragma unroll
         for (int k = 0; k < MAX_OFFSETS; ++k)
-          r[k] = (k < K && m < p.M) ? __ldg(&p.nbr[(int64_t)k * p.M + m]) : -1;
+          r[k] = (k < K && ((kmask >> k) & 1u) && m < p.M) ? __ldg(&p.nbr[(int64_t)k * p.M + m]) : -1;
 #pragma unroll
         for (int k = 0; k < MAX_OFFSETS; ++k) {
           if (k < K) {
+            if (r[k] >= num_in) { r[k] = -1; bad = true; }
             dst[(g * K + k) * BLOCK_M + itid] = r[k];
             if (__any_sync(0xFFFFFFFFu, r[k] >= 0)) mine |= 1u << k;
           }
@@ -248,12 +282,13 @@ conv_tcgen05_kernel(const ConvTcParams p) {
       }
       if (++ib == 2) { ib = 0; iphase ^= 1; }
     }
+    if (bad) atomicMin(p.dev_status, (int)WCN_ERR_BOUNDS);
   } else if (warp == WEIGHT_WARP) {
     // ================================================================ weight loader
     if (lane == 0) {
       Ring rb{0, 0, p.sb};
       int ib = 0, iphase = 0;
-      for (int64_t st = blockIdx.x; st < p.supertiles && ok; st += gridDim.x) {
+      for (int64_t wu = blockIdx.x; wu < p.units && ok; wu += gridDim.x) {
         if (!mbar_wait(bar(&ctl->info_full[ib]), iphase, p.dev_status)) { ok = false; break; }
         uint32_t rest = ctl->info_mask[ib][0] | ctl->info_mask[ib][1] | ctl->info_mask[ib][2] | ctl->info_mask[ib][3];
         mbar_arrive(bar(&ctl->info_empty[ib]));  // only the masks were needed
@@ -280,9 +315,7 @@ conv_tcgen05_kernel(const ConvTcParams p) {
           const char* bsrc_k = p.wpacked + ((int64_t)k * KB * p.c_out + n0) * RB;
           for (int kb0 = 0; kb0 < KB; kb0 += KBC) {
             // weight tiles (offset k, channel slices kb0..): bulk copies onto one barrier, shared by all sub-tiles
-            WCN_T0(t_be);
             if (!mbar_wait(bar(&ctl->b_empty[rb.slot]), rb.phase ^ 1, p.dev_status)) { ok = false; break; }
-            WCN_ACC(1, t_be, true);
             const uint32_t fullb = bar(&ctl->b_full[rb.slot]);
             mbar_expect_tx(fullb, (uint32_t)(KBC * B_BYTES));
 #pragma unroll
@@ -306,11 +339,8 @@ conv_tcgen05_kernel(const ConvTcParams p) {
     for (int j = 0; j < NJ; ++j) aoff[j] = tile_offset<RB>(gwarp * ROWS_PER_WARP + j * RPI + sub_row, chunk);
     Ring ra{0, 0, p.sa};
     int ib = 0, iphase = 0;
-    WCN_T0(t_prod);
-    for (int64_t st = blockIdx.x; st < p.supertiles && ok; st += gridDim.x) {
-      WCN_T0(t_idx);
+    for (int64_t wu = blockIdx.x; wu < p.units && ok; wu += gridDim.x) {
       if (!mbar_wait(bar(&ctl->info_full[ib]), iphase, p.dev_status)) { ok = false; break; }
-      WCN_ACC(2, t_idx, tid == GATHER_WARP0 * 32);
       const uint32_t mk0 = ctl->info_mask[ib][0], mk1 = ctl->info_mask[ib][1];
       const uint32_t mk2 = ctl->info_mask[ib][2], mk3 = ctl->info_mask[ib][3];
       const int32_t* tab = rows_idx + ib * IDX_INTS + gwarp * ROWS_PER_WARP + sub_row;
@@ -339,7 +369,7 @@ conv_tcgen05_kernel(const ConvTcParams p) {
 #pragma unroll
               for (int j = 0; j < NJ; ++j) {
                 const bool have = src[j] >= 0;
-                cp_async16(a_dst + u * A_BYTES + aoff[j], have ? fbase + (int64_t)src[j] * p.c_in * 2 : p.feats,
+                cp_async16(a_dst + u * A_BYTES + aoff[j], have ? fbase + (int64_t)src[j] * p.in_ld_bytes : p.feats,
                            have ? 16u : 0u);
               }
             }
@@ -355,9 +385,7 @@ conv_tcgen05_kernel(const ConvTcParams p) {
         for (int kb0 = 0; kb0 < KB && ok; kb0 += KBC) {
           for (uint32_t gb = gbits; gb; gb &= gb - 1) {
             const int g = __ffs(gb) - 1;
-            WCN_T0(t_ae);
             if (!mbar_wait(bar(&ctl->a_empty[ra.slot]), ra.phase ^ 1, p.dev_status)) { ok = false; break; }
-            WCN_ACC(0, t_ae, tid == GATHER_WARP0 * 32);
             const uint32_t a_dst = a_base + ra.slot * A_SLOT;
             const int32_t* rk = tab + (g * K + k) * BLOCK_M;
             int src[NJ];  // all index reads first, so the copies below issue back to back
@@ -367,7 +395,7 @@ conv_tcgen05_kernel(const ConvTcParams p) {
 #pragma unroll
             for (int j = 0; j < NJ; ++j) {
               const bool have = src[j] >= 0;
-              const char* sp = have ? fbase + (int64_t)src[j] * p.c_in * 2 : p.feats;
+              const char* sp = have ? fbase + (int64_t)src[j] * p.in_ld_bytes : p.feats;
 #pragma unroll
               for (int u = 0; u < KBC; ++u)  // the row's next channel slices are contiguous in memory
                 cp_async16(a_dst + u * A_BYTES + aoff[j], have ? sp + u * RB : sp, have ? 16u : 0u);
@@ -381,7 +409,6 @@ conv_tcgen05_kernel(const ConvTcParams p) {
       if (lane == 0) mbar_arrive(bar(&ctl->info_empty[ib]));  // this warp is done with the staged table
       if (++ib == 2) { ib = 0; iphase ^= 1; }
     }
-    WCN_ACC(3, t_prod, tid == GATHER_WARP0 * 32);
     cp_async_drain();
   } else if (warp >= MMA_WARP && warp < MMA_WARP + MMA_ISSUERS) {
     // ================================================================ MMA issuers
@@ -394,20 +421,15 @@ conv_tcgen05_kernel(const ConvTcParams p) {
                              ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BLOCK_M >> 4) << 24);
       Ring ra{0, 0, p.sa}, rb{0, 0, p.sb};
       int ib = 0, iphase = 0, ab = 0, aphase = 0;
-      WCN_T0(t_mma);
-      for (int64_t st = blockIdx.x; st < p.supertiles && ok; st += gridDim.x) {
-        WCN_T0(t_info);
+      for (int64_t wu = blockIdx.x; wu < p.units && ok; wu += gridDim.x) {
         if (!mbar_wait(bar(&ctl->info_full[ib]), iphase, p.dev_status)) { ok = false; break; }
-        WCN_ACC(6, t_info, true);
         const uint32_t mk0 = ctl->info_mask[ib][0], mk1 = ctl->info_mask[ib][1];
         const uint32_t mk2 = ctl->info_mask[ib][2], mk3 = ctl->info_mask[ib][3];
         const uint32_t uni = mk0 | mk1 | mk2 | mk3;
         mbar_arrive(bar(&ctl->info_empty[ib]));  // only the masks were needed
         if (++ib == 2) { ib = 0; iphase ^= 1; }
         // the accumulator set must have been read out by the epilogue of its previous use
-        WCN_T0(t_acce);
         if (!mbar_wait(bar(&ctl->acc_empty[ab]), aphase ^ 1, p.dev_status)) { ok = false; break; }
-        WCN_ACC(8, t_acce, true);
         tc_fence_after();
         uint32_t started = 0;
         uint32_t rest = uni;
@@ -431,6 +453,7 @@ conv_tcgen05_kernel(const ConvTcParams p) {
               continue;
             }
             tc_fence_after();
+            fence_proxy_async_smem();  // the rows were written by cp.async, the MMAs read them through the async proxy
             const uint32_t a_slot = a_base + ra.slot * A_SLOT;
             const uint32_t d = tmem_base + (uint32_t)((ab * G + g) * p.cols);
             uint32_t acc = (started >> g) & 1u;
@@ -458,24 +481,21 @@ conv_tcgen05_kernel(const ConvTcParams p) {
           rest &= rest - 1;
           const uint32_t gbits = subtiles_at(mk0, mk1, mk2, mk3, k);
           for (int kb0 = 0; kb0 < KB && ok; kb0 += KBC) {
-            WCN_T0(t_bf);
             if (!mbar_wait(bar(&ctl->b_full[rb.slot]), rb.phase, p.dev_status)) { ok = false; break; }
-            WCN_ACC(4, t_bf, true);
             const uint32_t b_slot = b_base + rb.slot * B_SLOT;
             for (uint32_t gb = gbits; gb; gb &= gb - 1) {
               const int g = __ffs(gb) - 1;
               // Both issuers pass every row slot in step: a parity wait is only meaningful for a
               // thread that is never a whole ring lap away from the slot, so the issuer that does
               // not consume a slot still observes its fill and signs it off.
-              WCN_T0(t_af);
               if (!mbar_wait(bar(&ctl->a_full[ra.slot]), ra.phase, p.dev_status)) { ok = false; break; }
-              WCN_ACC(5, t_af, true);
               if (((uint32_t)g & 1u) != issuer) {  // the other issuer's slot
                 mbar_arrive(bar(&ctl->a_empty[ra.slot]));
                 ra.advance();
                 continue;
               }
               tc_fence_after();
+              fence_proxy_async_smem();
               const uint32_t a_slot = a_base + ra.slot * A_SLOT;
               const uint32_t d = tmem_base + (uint32_t)((ab * G + g) * p.cols);
               const uint32_t acc0 = (started >> g) & 1u;
@@ -500,7 +520,6 @@ conv_tcgen05_kernel(const ConvTcParams p) {
         else mbar_arrive(bar(&ctl->acc_full[ab]));
         if (++ab == NBUF) { ab = 0; aphase ^= 1; }
       }
-      WCN_ACC(7, t_mma, true);
     }
     __syncwarp();
   } else {
@@ -532,17 +551,16 @@ conv_tcgen05_kernel(const ConvTcParams p) {
       }
       OutVec<TO>::store(orow + c0, y);
     };
-    WCN_T0(t_epi);
-    for (int64_t st = blockIdx.x; st < p.supertiles; st += gridDim.x) {
-      WCN_T0(t_accf);
-      if (ok) ok = mbar_wait(bar(&ctl->info_full[ib]), iphase, p.dev_status, 256);
+    const bool sliced = p.S > 1;  // leave raw fp32 sums for the reduction kernel instead of finishing rows
+    for (int64_t wu = blockIdx.x; wu < p.units; wu += gridDim.x) {
+      const int64_t st = sliced ? wu / p.S : wu;
+      if (ok) ok = mbar_wait(bar(&ctl->info_full[ib]), iphase, p.dev_status);
       uint32_t gm[MAX_G];
 #pragma unroll
       for (int g = 0; g < MAX_G; ++g) gm[g] = ok ? ctl->info_mask[ib][g] : 0u;
       mbar_arrive(bar(&ctl->info_empty[ib]));  // only the masks were needed
       if (++ib == 2) { ib = 0; iphase ^= 1; }
-      if (ok) ok = mbar_wait(bar(&ctl->acc_full[ab]), aphase, p.dev_status, 256);
-      WCN_ACC(9, t_accf, tid == 0);
+      if (ok) ok = mbar_wait(bar(&ctl->acc_full[ab]), aphase, p.dev_status);
       // tcgen05.ld is warp-collective, so the decision to read must be warp-uniform
       if (!__all_sync(0xFFFFFFFFu, ok)) { ok = false; break; }
       tc_fence_after();
@@ -556,8 +574,10 @@ conv_tcgen05_kernel(const ConvTcParams p) {
         const int64_t m = (p.out_rows && slot < p.M) ? (int64_t)__ldg(&p.out_rows[slot]) : slot;
         const bool live = slot < p.M;
         const uint32_t trow = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)((ab * G + g) * p.cols);
-        TO* orow = reinterpret_cast<TO*>(p.out) + m * p.c_out + n0;
-        const TO* rrow = p.residual ? reinterpret_cast<const TO*>(p.residual) + m * p.c_out + n0 : nullptr;
+        TO* orow = reinterpret_cast<TO*>(p.out) + m * p.out_ld + n0;
+        const TO* rrow = p.residual ? reinterpret_cast<const TO*>(p.residual) + m * p.res_ld + n0 : nullptr;
+        // slice wu % S of this row block: [S][M][c_out] fp32, rows in table order (a slice owns all columns)
+        float* prow = sliced ? p.partial + (((wu - st * p.S) * p.M + slot) * p.c_out) : nullptr;
         int c0 = 0;
         for (; c0 + 32 <= BN; c0 += 32) {  // two TMEM loads in flight per wait
           float y0[16], y1[16];
@@ -572,7 +592,10 @@ conv_tcgen05_kernel(const ConvTcParams p) {
 #pragma unroll
             for (int i = 0; i < 16; ++i) y0[i] = y1[i] = 0.f;
           }
-          if (live) {
+          if (live && sliced) {
+            OutVec<float>::store(prow + c0, y0);
+            OutVec<float>::store(prow + c0 + 16, y1);
+          } else if (live) {
             finish16(y0, c0, orow, rrow);
             finish16(y1, c0 + 16, orow, rrow);
           }
@@ -589,14 +612,14 @@ conv_tcgen05_kernel(const ConvTcParams p) {
 #pragma unroll
             for (int i = 0; i < 16; ++i) y0[i] = 0.f;
           }
-          if (live) finish16(y0, c0, orow, rrow);
+          if (live && sliced) OutVec<float>::store(prow + c0, y0);
+          else if (live) finish16(y0, c0, orow, rrow);
         }
       }
       tc_fence_before();
       mbar_arrive(bar(&ctl->acc_empty[ab]));   // accumulator set may be overwritten
       if (++ab == NBUF) { ab = 0; aphase ^= 1; }
     }
-    WCN_ACC(10, t_epi, tid == 0);
   }
   tc_fence_before();
   __syncthreads();
@@ -624,28 +647,97 @@ __global__ void pack_weight_kernel(const T* __restrict__ w, T* __restrict__ pack
   packed[tile + off_bytes / 2 + within] = w[i];
 }
 
+// Second pass of a convolution whose kernel offsets were divided among S CTAs per row block:
+// adds the S fp32 slices of every output element in slice order (fixed, so the result has the
+// same bits on every run) and runs the epilogue.  One thread owns four consecutive columns
+// of one table row, so the slices are read and the rows written in full lines.
+template <typename TO>
+__global__ void conv_slice_reduce_kernel(const float* __restrict__ partial, int S, int64_t M, int c_out,
+                                         const int32_t* __restrict__ out_rows, const float* __restrict__ scale,
+                                         const float* __restrict__ shift, const TO* __restrict__ residual,
+                                         int64_t res_ld, int relu, TO* __restrict__ out, int64_t out_ld,
+                                         const int32_t* __restrict__ dev_status) {
+  const int quads = c_out >> 2;
+  const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= M * quads) return;
+  const int64_t slot = t / quads;
+  const int c = (int)(t - slot * quads) * 4;
+  const int64_t m = out_rows ? (int64_t)__ldg(&out_rows[slot]) : slot;
+  float y[4];
+  if (*dev_status != 0) {  // the first pass did not run (or gave up): no data to finish
+    y[0] = y[1] = y[2] = y[3] = __int_as_float(0x7FC00000);
+  } else {
+    const float4* src = reinterpret_cast<const float4*>(partial + slot * c_out + c);
+    const int64_t slice = M * (int64_t)c_out / 4;
+    float4 acc = __ldcg(src);
+    for (int s = 1; s < S; ++s) {
+      const float4 v = __ldcg(src + s * slice);
+      acc.x = __fadd_rn(acc.x, v.x); acc.y = __fadd_rn(acc.y, v.y);
+      acc.z = __fadd_rn(acc.z, v.z); acc.w = __fadd_rn(acc.w, v.w);
+    }
+    y[0] = acc.x; y[1] = acc.y; y[2] = acc.z; y[3] = acc.w;
+    if (scale || shift) {  // the recipe of the one-pass epilogue: one fused multiply-add
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        y[i] = fmaf(y[i], scale ? __ldg(&scale[c + i]) : 1.f, shift ? __ldg(&shift[c + i]) : 0.f);
+    }
+    if (residual) {
+      const TO* r = residual + m * res_ld + c;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) y[i] += wcn_to_float<TO>(r[i]);
+    }
+    if (relu) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) y[i] = fmaxf(y[i], 0.f);
+    }
+  }
+  __align__(16) TO o[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) o[i] = wcn_from_float<TO>(y[i]);
+  TO* dst = out + m * out_ld + c;
+  if (sizeof(TO) == 4) *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(o);
+  else *reinterpret_cast<uint2*>(dst) = *reinterpret_cast<const uint2*>(o);
+}
+
 inline int pick_bk(int c_in) { return c_in % 64 == 0 ? 64 : 32; }
 
-// Launch geometry.  Small problems do not have enough 128-row tiles to occupy
-// every SM, so their output columns are divided among CTAs (each re-gathers the
-// rows, which stay in L2) and they use fewer sub-tiles per supertile.
-bool plan_launch(ConvTcParams& p, int bk, size_t* smem, dim3* grid) {
+constexpr int MAX_SLICES = 16;
+
+// Launch geometry.  A problem with fewer 128-row tiles than multiprocessors cannot occupy the
+// GPU with one CTA per tile.  With a 3x3x3-sized window there is enough work per tile to divide
+// its kernel offsets among S CTAs (split_k: 0 = decide here, 1 = never, >= 2 = that many
+// slices); otherwise the output columns are divided among CTAs, each re-gathering the rows,
+// which stay in L2 (split_k < 0 forces -split_k column blocks).
+bool plan_launch(ConvTcParams& p, int bk, int split_k, size_t* smem, dim3* grid) {
   const int sms = num_sms();
   const int64_t tiles = (p.M + BLOCK_M - 1) / BLOCK_M;
+  int S = 1;
+  if (split_k >= 2) {
+    S = split_k;
+  } else if (split_k == 0 && p.K >= 9 && tiles * 2 <= sms) {
+    S = (int)(sms / tiles);
+    if (S > 8) S = 8;
+  }
+  if (S > p.K) S = p.K;
+  if (S > MAX_SLICES) S = MAX_SLICES;
   int split = 1;
-  while (tiles * split < sms && p.c_out % (16 * split * 2) == 0 && p.c_out / (split * 2) >= 32 && split < 8) split *= 2;
+  if (S == 1) {
+    if (split_k < 0) {
+      split = -split_k;
+      if (split > 16 || p.c_out % (16 * split) != 0) return false;
+    } else {
+      while (tiles * split < sms && p.c_out % (16 * split * 2) == 0 && p.c_out / (split * 2) >= 32 && split < 8) split *= 2;
+    }
+  }
+  p.S = S;
   p.block_n = p.c_out / split;
   int cols = 32;
   while (cols < p.block_n) cols <<= 1;
   p.cols = cols;
   int g = cols >= 128 ? 2 : 4;
-  while (g > 1 && ((tiles + g - 1) / g) * split < 2 * (int64_t)sms) g /= 2;
+  while (g > 1 && ((tiles + g - 1) / g) * split * S < 2 * (int64_t)sms) g /= 2;
   const size_t a_unit = (size_t)BLOCK_M * bk * 2, b_unit = (size_t)p.block_n * bk * 2;
-#ifdef WCN_EXP_SMEM_KB  // development builds only: a smaller shared-memory budget
-  const size_t limit = (size_t)WCN_EXP_SMEM_KB * 1024;
-#else
   const size_t limit = 226 * 1024;  // the kernels opt in to this much dynamic shared memory
-#endif
   const int kb_total = p.c_in / bk;
   // Channel slices per ring slot: as many as give a 32 KiB row slot, fewer if the rings would not fit.
   // (with a single slice per offset the slot spans that many active offsets instead)
@@ -672,6 +764,7 @@ bool plan_launch(ConvTcParams& p, int bk, size_t* smem, dim3* grid) {
   p.G = g;
   p.nbuf = (g * cols * 2 <= 512) ? 2 : 1;
   p.supertiles = (tiles + g - 1) / g;
+  p.units = p.supertiles * S;
   const size_t budget = limit - fixed;
   int sb = 3;
   while (sb > 2 && sb * b_stage > budget / 2) --sb;
@@ -683,7 +776,7 @@ bool plan_launch(ConvTcParams& p, int bk, size_t* smem, dim3* grid) {
   p.sa = sa;
   p.sb = sb;
   *smem = fixed + sa * a_stage + sb * b_stage;
-  int64_t gx = p.supertiles;
+  int64_t gx = p.units;
   const int64_t cap = sms / split > 0 ? sms / split : 1;
   if (gx > cap) gx = cap;
   *grid = dim3((unsigned)gx, (unsigned)split);
@@ -704,14 +797,28 @@ int launch_kbc(const ConvTcParams& p, size_t smem, dim3 grid, cudaStream_t st) {
     configured[dev] = true;
   }
   kern<<<grid, THREADS, smem, st>>>(p);
-  return cudaGetLastError() == cudaSuccess ? WCN_OK : WCN_ERR_EXECUTION;
+  if (cudaGetLastError() != cudaSuccess) return WCN_ERR_EXECUTION;
+  if (p.S > 1) {
+    const int64_t threads = p.M * (p.c_out >> 2);
+    conv_slice_reduce_kernel<TO><<<(unsigned)((threads + 255) / 256), 256, 0, st>>>(
+        p.partial, p.S, p.M, p.c_out, p.out_rows, p.scale, p.shift, reinterpret_cast<const TO*>(p.residual), p.res_ld,
+        p.relu, reinterpret_cast<TO*>(p.out), p.out_ld, p.dev_status);
+    if (cudaGetLastError() != cudaSuccess) return WCN_ERR_EXECUTION;
+  }
+  return WCN_OK;
 }
 
 template <int BK, bool BF16, typename TO>
-int launch_tc(ConvTcParams& p, cudaStream_t st) {
+int launch_tc(ConvTcParams& p, int split_k, void* workspace, int64_t workspace_bytes, cudaStream_t st) {
   size_t smem = 0;
   dim3 grid;
-  if (!plan_launch(p, BK, &smem, &grid)) return WCN_ERR_UNSUPPORTED_CONFIG;
+  if (!plan_launch(p, BK, split_k, &smem, &grid)) return WCN_ERR_UNSUPPORTED_CONFIG;
+  if (p.S > 1) {
+    const int64_t need = (int64_t)p.S * p.M * p.c_out * (int64_t)sizeof(float);
+    if (!workspace || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 15))
+      return WCN_ERR_INVALID_PARAMETERS;
+    p.partial = reinterpret_cast<float*>(workspace);
+  }
   switch (p.kbc) {
     case 1: return launch_kbc<BK, 1, BF16, TO>(p, smem, grid, st);
     case 2: return launch_kbc<BK, 2, BF16, TO>(p, smem, grid, st);
@@ -721,18 +828,29 @@ int launch_tc(ConvTcParams& p, cudaStream_t st) {
   }
 }
 
+// A barrier phase that cannot complete (one arrival of two), waited for with a short limit:
+// the wait has to give up, report WCN_ERR_WAIT_EXPIRED and let the kernel end normally.
+__global__ void bounded_wait_probe_kernel(long long limit_cycles, int32_t* dev_status, int32_t* gave_up) {
+  __shared__ uint64_t probe_bar;
+  if (threadIdx.x == 0) {
+    mbar_init(smem_u32(&probe_bar), 2);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) mbar_arrive(smem_u32(&probe_bar));
+  if (threadIdx.x == 32) {
+    const bool done = mbar_wait(smem_u32(&probe_bar), 0, dev_status, limit_cycles);
+    if (gave_up) *gave_up = done ? 0 : 1;
+  }
+}
+
 }  // namespace
 
-#ifdef WCN_WAIT_STATS
-extern "C" int wcn_debug_wait_stats(long long* host16, int reset) {
-  if (host16 && cudaMemcpyFromSymbol(host16, g_wait_stats, sizeof(long long) * 16) != cudaSuccess) return -3;
-  if (reset) {
-    long long z[16] = {};
-    if (cudaMemcpyToSymbol(g_wait_stats, z, sizeof(z)) != cudaSuccess) return -3;
-  }
-  return 0;
+extern "C" int wcn_selftest_bounded_wait(int64_t limit_cycles, int32_t* dev_status, int32_t* gave_up, void* stream) {
+  if (!dev_status || limit_cycles < 1000 || limit_cycles > 2000000000ll) return WCN_ERR_INVALID_PARAMETERS;
+  bounded_wait_probe_kernel<<<1, 64, 0, wcn_stream(stream)>>>((long long)limit_cycles, dev_status, gave_up);
+  return cudaGetLastError() == cudaSuccess ? WCN_OK : WCN_ERR_EXECUTION;
 }
-#endif
 
 bool wcn_conv_tcgen05_supported(int K, int c_in, int c_out, int dtype, int out_dtype) {
   return (dtype == WCN_F16 || dtype == WCN_BF16) && (out_dtype == dtype || out_dtype == WCN_F32) && K >= 1 &&
@@ -740,6 +858,16 @@ bool wcn_conv_tcgen05_supported(int K, int c_in, int c_out, int dtype, int out_d
 }
 
 int64_t wcn_conv_tcgen05_packed_bytes(int K, int c_in, int c_out) { return (int64_t)K * c_in * c_out * 2; }
+
+// Bytes of slice workspace wcn_conv_tcgen05_fwd needs for this problem (0: one pass).
+int64_t wcn_conv_tcgen05_workspace_bytes(int64_t M, int K, int c_in, int c_out, int split_k) {
+  ConvTcParams p = {};
+  p.M = M; p.K = K; p.c_in = c_in; p.c_out = c_out;
+  size_t smem = 0;
+  dim3 grid;
+  if (M <= 0 || !plan_launch(p, pick_bk(c_in), split_k, &smem, &grid) || p.S <= 1) return 0;
+  return (int64_t)p.S * M * c_out * (int64_t)sizeof(float);
+}
 
 int wcn_conv_tcgen05_pack(const void* weight, int K, int c_in, int c_out, void* packed, cudaStream_t st) {
   const int64_t total = (int64_t)K * c_in * c_out;
@@ -749,23 +877,29 @@ int wcn_conv_tcgen05_pack(const void* weight, int K, int c_in, int c_out, void* 
   return cudaGetLastError() == cudaSuccess ? WCN_OK : WCN_ERR_EXECUTION;
 }
 
-int wcn_conv_tcgen05_fwd(const void* feats, int64_t num_in, const void* packed, const int32_t* nbr,
-                         const int32_t* out_rows, int64_t M, int K, int c_in,
-                         int c_out, int dtype, const float* scale, const float* shift, const void* residual,
-                         int relu, void* out, int out_dtype, int32_t* dev_status, cudaStream_t st) {
+int wcn_conv_tcgen05_fwd(const void* feats, int64_t num_in, int64_t feats_ld, const void* packed, const int32_t* nbr,
+                         const int32_t* out_rows, int64_t M, int K, int c_in, int c_out, int dtype,
+                         const float* scale, const float* shift, const void* residual, int64_t residual_ld, int relu,
+                         void* out, int64_t out_ld, int out_dtype, int split_k, void* workspace,
+                         int64_t workspace_bytes, int32_t* dev_status, cudaStream_t st) {
   if (!wcn_conv_tcgen05_supported(K, c_in, c_out, dtype, out_dtype)) return WCN_ERR_UNSUPPORTED_CONFIG;
   if (!dev_status || !packed || num_in <= 0 || num_in >= 0x7FFFFFFFll) return WCN_ERR_INVALID_PARAMETERS;
+  const int64_t osz = out_dtype == WCN_F32 ? 4 : 2;
   if ((reinterpret_cast<uintptr_t>(feats) & 15) || (reinterpret_cast<uintptr_t>(packed) & 15) ||
-      (reinterpret_cast<uintptr_t>(out) & 15) || (reinterpret_cast<uintptr_t>(residual) & 15))
+      (reinterpret_cast<uintptr_t>(out) & 15) || (reinterpret_cast<uintptr_t>(residual) & 15) ||
+      feats_ld < c_in || (feats_ld * 2) % 16 || out_ld < c_out || (out_ld * osz) % 16 ||
+      (residual && (residual_ld < c_out || (residual_ld * osz) % 16)))
     return WCN_ERR_INVALID_PARAMETERS;
-  ConvTcParams p;
+  ConvTcParams p = {};
   p.feats = (const char*)feats; p.wpacked = (const char*)packed; p.nbr = nbr; p.out_rows = out_rows;
   p.M = M; p.num_in = num_in; p.K = K; p.c_in = c_in; p.c_out = c_out;
+  p.in_ld_bytes = feats_ld * 2; p.out_ld = out_ld; p.res_ld = residual_ld;
   p.scale = scale; p.shift = shift; p.residual = residual; p.relu = relu; p.out = out;
   p.dev_status = dev_status;
   const int bk = pick_bk(c_in);
   const bool bf = dtype == WCN_BF16;
-#define WCN_TC_CASE(BKV, BFV, TO) if (bk == BKV && bf == BFV) return launch_tc<BKV, BFV, TO>(p, st);
+#define WCN_TC_CASE(BKV, BFV, TO) \
+  if (bk == BKV && bf == BFV) return launch_tc<BKV, BFV, TO>(p, split_k, workspace, workspace_bytes, st);
   if (out_dtype == WCN_F32) {
     WCN_TC_CASE(64, false, float) WCN_TC_CASE(64, true, float) WCN_TC_CASE(32, false, float) WCN_TC_CASE(32, true, float)
   } else if (bf) {

@@ -129,7 +129,12 @@ conv_wgrad_tcgen05_kernel(const WgradParams p) {
 #pragma unroll
         for (int j = 0; j < NJ; ++j) {
           const int64_t m = m0 + pwarp * 16 + j * RPI + sub_row;
-          src[u][j] = (unit < total_units && m < p.M) ? __ldg(&p.nbr[(int64_t)k * p.M + m]) : -1;
+          int r = (unit < total_units && m < p.M) ? __ldg(&p.nbr[(int64_t)k * p.M + m]) : -1;
+          if (r >= (int)p.num_in) {  // not a feature row: counts as absent and is reported
+            r = -1;
+            atomicMin(p.dev_status, (int)WCN_ERR_BOUNDS);
+          }
+          src[u][j] = r;
         }
       }
       if (!mbar_wait(bar(&ctl->empty[slot]), phase ^ 1, p.dev_status)) { ok = false; break; }
@@ -172,6 +177,7 @@ conv_wgrad_tcgen05_kernel(const WgradParams p) {
         if (p.tile_masks && !(__ldg(&p.tile_masks[st]) & gmask)) continue;
         if (!mbar_wait(bar(&ctl->full[slot]), phase, p.dev_status)) { ok = false; break; }
         tc_fence_after();
+        fence_proxy_async_smem();  // the tiles were written by cp.async, the MMAs read them through the async proxy
         const uint32_t a_slot = base + slot * STAGE;
         const uint32_t b_slot = a_slot + A_STAGE;
 #pragma unroll
@@ -191,7 +197,7 @@ conv_wgrad_tcgen05_kernel(const WgradParams p) {
     __syncwarp();
   } else {
     // ================================================================ epilogue (warps 0..3)
-    ok = mbar_wait(bar(&ctl->acc_full), 0, p.dev_status, 256);
+    ok = mbar_wait(bar(&ctl->acc_full), 0, p.dev_status);
     if (__all_sync(0xFFFFFFFFu, ok) && ctl->any) {
       tc_fence_after();
       const int row = warp * 32 + lane;            // TMEM lane = position on the M side

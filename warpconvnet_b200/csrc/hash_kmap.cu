@@ -2,6 +2,8 @@
 // Morton code.  All of it is integer, bandwidth-bound work: one 16-byte key per
 // slot so a probe is one 32-byte sector, coalesced int4 query loads, warp-ballot
 // compaction, no host synchronisation inside the library.
+#include <atomic>
+
 #include "wcn_common.cuh"
 
 namespace {
@@ -66,6 +68,10 @@ __global__ void hash_insert_kernel(const int32_t* __restrict__ keys, int64_t n, 
   const int4 empty = make_int4(WCN_EMPTY_BATCH, 0, 0, 0);
   uint32_t slot = wcn_slot(wcn_hash4<METHOD>(key), cap);
   for (uint32_t p = 0; p < cap; ++p) {
+    // A plain 16-byte load may race with another thread's 128-bit CAS on the same slot.  It relies
+    // on an aligned 16-byte global load being single-copy atomic (it is one memory transaction on
+    // this architecture), so it sees either the empty marker or a whole key, never a mix; and a
+    // stale "empty" is harmless because the CAS below re-reads the slot and returns what is there.
     int4 cur = __ldcg(&tkeys[slot]);
     bool claimed = false;
     if (cur.x == WCN_EMPTY_BATCH) {
@@ -618,8 +624,8 @@ extern "C" int wcn_kmap_workspace_bytes(int64_t num_queries, int32_t num_offsets
 
 extern "C" int wcn_kmap_search_dilated(const void* table, int64_t capacity, int hash_method,
                                        const int32_t* queries, int64_t num_queries, const int32_t* stride,
-                                       const int32_t* kernel_size, const int32_t* dilation, int32_t num_offsets,
-                                       int32_t* nbr, void* workspace, void* stream) {
+                                       const int32_t* kernel_size, const int32_t* dilation, const int32_t* center,
+                                       int32_t num_offsets, int32_t* nbr, void* workspace, void* stream) {
   KernelGeom g;
   if (!table || !kernel_size || capacity <= 0 || capacity > 0x7FFFFFFFll || num_queries < 0 ||
       !parse_stride(stride, &g.sx, &g.sy, &g.sz) || !parse_stride(dilation, &g.dx, &g.dy, &g.dz))
@@ -631,6 +637,9 @@ extern "C" int wcn_kmap_search_dilated(const void* table, int64_t capacity, int 
   g.cx = (g.kx & 1) ? g.kx / 2 : 0;
   g.cy = (g.ky & 1) ? g.ky / 2 : 0;
   g.cz = (g.kz & 1) ? g.kz / 2 : 0;
+  if (center) {
+    g.cx = center[0]; g.cy = center[1]; g.cz = center[2];
+  }
   if (num_queries == 0) return WCN_OK;
   if (!queries || !nbr || (reinterpret_cast<uintptr_t>(queries) & 15)) return WCN_ERR_INVALID_PARAMETERS;
   const int4* tkeys = reinterpret_cast<const int4*>(table);
@@ -652,7 +661,7 @@ extern "C" int wcn_kmap_search(const void* table, int64_t capacity, int hash_met
                                int64_t num_queries, const int32_t* stride, const int32_t* kernel_size,
                                int32_t num_offsets, int32_t* nbr, void* workspace, void* stream) {
   return wcn_kmap_search_dilated(table, capacity, hash_method, queries, num_queries, stride, kernel_size, nullptr,
-                                 num_offsets, nbr, workspace, stream);
+                                 nullptr, num_offsets, nbr, workspace, stream);
 }
 
 extern "C" int wcn_kmap_search_self(const void* table, int64_t capacity, int hash_method, const int32_t* keys,
@@ -704,20 +713,24 @@ constexpr int64_t kStaticScratchInts = 1 << 20;
 static __device__ __align__(256) int g_kmap_static_scratch[kStaticScratchInts];
 
 // In host code the array's name is only a handle; the device address has to be asked for,
-// once per device, with that device current.
+// once per device, with that device current (the caller's stream must belong to it).  The
+// per-device cache is atomic, so concurrent first calls from several host threads are safe:
+// each resolves the same address.
 static int* kmap_static_scratch_ptr() {
-  static int* cached[64] = {};
+  static std::atomic<int*> cached[64];
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
-  if (!cached[dev]) {
+  int* p = cached[dev].load(std::memory_order_acquire);
+  if (!p) {
     void* ptr = nullptr;
     if (cudaGetSymbolAddress(&ptr, g_kmap_static_scratch) != cudaSuccess || !ptr) {
       (void)cudaGetLastError();
       return nullptr;
     }
-    cached[dev] = static_cast<int*>(ptr);
+    p = static_cast<int*>(ptr);
+    cached[dev].store(p, std::memory_order_release);
   }
-  return cached[dev];
+  return p;
 }
 
 extern "C" int wcn_kmap_search_static(const void* table, int64_t capacity, int hash_method,

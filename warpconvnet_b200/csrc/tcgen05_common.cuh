@@ -40,11 +40,11 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // reported a failure.  The status word lives in global memory and is looked at about
 // once per millisecond of waiting.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int32_t* dev_status,
-                                          unsigned unused_backoff = 0) {
-  (void)unused_backoff;
+                                          long long limit_cycles = kWaitCycles) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
-  long long next_check = t0 + kStatusPollCycles;
+  const long long poll = limit_cycles < kStatusPollCycles ? limit_cycles : kStatusPollCycles;
+  long long next_check = t0 + poll;
   for (;;) {
 #pragma unroll 1
     for (int i = 0; i < 16; ++i)
@@ -52,11 +52,11 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int32_t
     const long long now = clock64();
     if (now > next_check) {
       if (*(volatile int32_t*)dev_status != 0) return false;
-      if (now - t0 > kWaitCycles) {
+      if (now - t0 > limit_cycles) {
         atomicMin(dev_status, (int)WCN_ERR_WAIT_EXPIRED);
         return false;
       }
-      next_check = now + kStatusPollCycles;
+      next_check = now + poll;
     }
   }
 }
@@ -81,6 +81,10 @@ __device__ __forceinline__ void cp_async_arrive(uint32_t bar) {
 __device__ __forceinline__ void cp_async_drain() {
   asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");
 }
+// Shared-memory tiles filled by cp.async (generic proxy) are read by tcgen05.mma through the
+// async proxy: the issuing thread orders the two with this fence after it has observed the
+// tile's barrier and before it issues the instructions that read the tile.
+__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 

@@ -44,13 +44,17 @@ class ConvTrBlock(nn.Module):
         act = nn.ReLU(inplace=True) if activation == "relu" else (nn.Identity() if activation is None else activation)
         self.norm_act = Sequential(nn.BatchNorm1d(out_channels), act)
 
-    def forward(self, x: Voxels, out_spatial_sparsity: Voxels) -> Voxels:
+    def forward(self, x: Voxels, out_spatial_sparsity: Voxels, out: Optional[torch.Tensor] = None) -> Voxels:
+        """``out`` (inference only): preallocated destination of the result's features."""
         bn = self.norm_act[0]
         if not bn.training and not (torch.is_grad_enabled() and self.conv_tr.weight.requires_grad):
             scale, shift = fold_batchnorm(bn)
-            ep = ConvEpilogue(scale=scale, shift=shift, relu=isinstance(self.norm_act[1], nn.ReLU))
+            ep = ConvEpilogue(scale=scale, shift=shift, relu=isinstance(self.norm_act[1], nn.ReLU), out=out)
             return self.conv_tr(x, out_spatial_sparsity, epilogue=ep)
-        return self.norm_act(self.conv_tr(x, out_spatial_sparsity))
+        res = self.norm_act(self.conv_tr(x, out_spatial_sparsity))
+        if out is not None:
+            out.copy_(res.feature_tensor)
+        return res
 
 
 class BasicBlock(nn.Module):
@@ -69,11 +73,12 @@ class BasicBlock(nn.Module):
                                         bias=bias, compute_dtype=compute_dtype)
         self.relu = ReLU(inplace=True)
 
-    def forward(self, x: Voxels) -> Voxels:
+    def forward(self, x: Voxels, out: Optional[torch.Tensor] = None) -> Voxels:
+        """``out`` (inference only): preallocated destination of the block's features."""
         identity = x if self.downsample is None else self.downsample(x)
-        out = self.conv1(x)
-        # out = relu(conv2(out) + identity): residual add and ReLU ride in conv2's epilogue
-        return self.conv2(out, residual=identity.feature_tensor, final_relu=True)
+        y = self.conv1(x)
+        # relu(conv2(y) + identity): residual add and ReLU ride in conv2's epilogue
+        return self.conv2(y, residual=identity.feature_tensor, final_relu=True, out=out)
 
 
 class MinkUNetBase(nn.Module):
@@ -115,20 +120,63 @@ class MinkUNetBase(nn.Module):
         # all four coarse coordinate sets first: their size read-backs then wait for coordinate
         # kernels only, and the convolutions below queue without a host synchronisation
         prefetch_strided_coordinates(x, [2, 2, 2, 2])
-        out_p1 = self.conv0(x)
-        out_b1p2 = self.block1(self.conv1(out_p1))
-        out_b2p4 = self.block2(self.conv2(out_b1p2))
-        out_b3p8 = self.block3(self.conv3(out_b2p4))
-        out = self.block4(self.conv4(out_b3p8))
-        out = self.block5(cat(self.convtr4(out, out_b3p8), out_b3p8))
-        out = self.block6(cat(self.convtr5(out, out_b2p4), out_b2p4))
-        out = self.block7(cat(self.convtr6(out, out_b1p2), out_b1p2))
-        out = self.block8(cat(self.convtr7(out, out_p1), out_p1))
+        if self.training or torch.is_grad_enabled():
+            out_p1 = self.conv0(x)
+            out_b1p2 = self.block1(self.conv1(out_p1))
+            out_b2p4 = self.block2(self.conv2(out_b1p2))
+            out_b3p8 = self.block3(self.conv3(out_b2p4))
+            out = self.block4(self.conv4(out_b3p8))
+            out = self.block5(cat(self.convtr4(out, out_b3p8), out_b3p8))
+            out = self.block6(cat(self.convtr5(out, out_b2p4), out_b2p4))
+            out = self.block7(cat(self.convtr6(out, out_b1p2), out_b1p2))
+            out = self.block8(cat(self.convtr7(out, out_p1), out_p1))
+        else:
+            out = self._forward_joined(x)
         if restore_order:
             perm = x.extra_attributes.get("perm")
             assert perm is not None, "restore_order needs the permutation that Voxels.sort records"
             return self.final(out, epilogue=ConvEpilogue(out_rows=perm)).feature_tensor
         return self.final(out)
+
+    def _forward_joined(self, x: Voxels) -> Voxels:
+        """Inference body without concatenation copies.  Each skip connection ``cat(up, skip)`` is
+        one buffer ``[M, C_up + C_skip]`` allocated when the encoder reaches that level: the encoder
+        stage writes its result straight into the right-hand column block (and the next stage reads
+        it from there, rows ``C_up + C_skip`` elements apart), the transposed convolution of the
+        decoder later fills the left-hand block, and the decoder stage reads the whole buffer."""
+        P = self.PLANES
+        dtype, dev = x.feature_tensor.dtype, x.feature_tensor.device
+
+        def joined(rows: int, c_up: int, c_skip: int):
+            buf = torch.empty((rows, c_up + c_skip), dtype=dtype, device=dev)
+            return buf, buf[:, :c_up], buf[:, c_up:]
+
+        def stage(blocks: nn.Sequential, v: Voxels, out: torch.Tensor) -> Voxels:
+            n = len(blocks)
+            for i, blk in enumerate(blocks):
+                v = blk(v, out=out if i == n - 1 else None)
+            return v
+
+        buf8, up8, skip8 = joined(len(x), P[7], self.INIT_DIM)
+        out_p1 = self.conv0(x, out=skip8)
+        v = self.conv1(out_p1)
+        buf7, up7, skip7 = joined(len(v), P[6], P[0])
+        out_b1p2 = stage(self.block1, v, skip7)
+        v = self.conv2(out_b1p2)
+        buf6, up6, skip6 = joined(len(v), P[5], P[1])
+        out_b2p4 = stage(self.block2, v, skip6)
+        v = self.conv3(out_b2p4)
+        buf5, up5, skip5 = joined(len(v), P[4], P[2])
+        out_b3p8 = stage(self.block3, v, skip5)
+        v = self.block4(self.conv4(out_b3p8))
+        self.convtr4(v, out_b3p8, out=up5)
+        v = self.block5(out_b3p8._derive(buf5))
+        self.convtr5(v, out_b2p4, out=up6)
+        v = self.block6(out_b2p4._derive(buf6))
+        self.convtr6(v, out_b1p2, out=up7)
+        v = self.block7(out_b1p2._derive(buf7))
+        self.convtr7(v, out_p1, out=up8)
+        return self.block8(out_p1._derive(buf8))
 
 
 class MinkUNet18(MinkUNetBase):

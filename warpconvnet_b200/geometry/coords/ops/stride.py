@@ -13,7 +13,7 @@ from typing import Optional, Tuple
 import torch
 from torch import Tensor
 
-from ...._native import check, device_status, lib, ptr, query_bytes, stream_ptr
+from ...._native import check, device_status, lib, ptr, query_bytes, raise_for_status, stream_ptr
 from ....utils.ntuple import ntuple
 from ..search.torch_hashmap import HashMethod
 from .batch_index import offsets_from_batch_index
@@ -61,10 +61,20 @@ def unique_strided_rows(bcoords: Tensor, stride: Tuple[int, int, int] = (1, 1, 1
     if in_offsets is not None:
         # first occurrences are emitted in ascending source row, so the output batch boundaries are
         # the ranks of the input boundaries among the first-occurrence rows
-        out_offsets = torch.searchsorted(uidx, in_offsets.to(device=dev, dtype=torch.int32)).cpu().long()
+        # The device status word rides along in the same read: this is a point where the host waits
+        # for the device anyway, so a kernel failure recorded earlier surfaces here.
+        nb = len(in_offsets)
+        packed = torch.empty(nb + 1, dtype=torch.int64, device=dev)
+        torch.searchsorted(uidx, in_offsets.to(device=dev, dtype=torch.int32), out=packed[:nb])
+        packed[nb:].copy_(device_status(dev))
+        host = packed.cpu()
+        raise_for_status(int(host[nb]), dev)
+        out_offsets = host[:nb].clone()
         m = int(out_offsets[-1])
         return rows[:m], uidx[:m], parent, out_offsets
-    m = int(count.item())
+    both = torch.cat([count, device_status(dev).to(torch.int64)]).cpu()
+    raise_for_status(int(both[1]), dev)
+    m = int(both[0])
     return rows[:m], uidx[:m], parent
 
 

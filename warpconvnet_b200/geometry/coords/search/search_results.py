@@ -18,7 +18,7 @@ from typing import List, Literal, Optional, Tuple
 import torch
 from torch import Tensor
 
-from ...._native import check, lib, ptr, query_bytes, stream_ptr
+from ...._native import check, device_status, lib, ptr, query_bytes, raise_for_status, stream_ptr
 
 
 class IntSearchResult:
@@ -70,7 +70,10 @@ class IntSearchResult:
             check(lib().wcn_kmap_count(ptr(nbr), M, K, ptr(ws), stream_ptr(dev)), "wcn_kmap_count")
         offsets = torch.empty(K + 1, dtype=torch.int32, device=dev)
         check(lib().wcn_kmap_scan(ptr(ws), M, K, ptr(offsets), stream_ptr(dev)), "wcn_kmap_scan")
-        offsets_cpu = offsets.cpu()  # the one host synchronisation of a compact map
+        # the one host synchronisation of a compact map; the device status word is read with it
+        both = torch.cat([offsets, device_status(dev)]).cpu()
+        raise_for_status(int(both[-1]), dev)
+        offsets_cpu = both[:-1].clone()
         L = int(offsets_cpu[-1])
         in_maps = torch.empty(L, dtype=torch.int32, device=dev)
         out_maps = torch.empty(L, dtype=torch.int32, device=dev)

@@ -46,7 +46,8 @@ def _kernel_map_from_size(hashtable: TorchHashTable, batched_query_coords: Tenso
                           return_type: Literal["indices", "offsets"] = "offsets",
                           skip_symmetric_kernel_map: bool = False,
                           query_stride: Optional[Tuple[int, ...]] = None, num_in: Optional[int] = None,
-                          self_map: bool = False, kernel_dilation: Optional[Tuple[int, ...]] = None):
+                          self_map: bool = False, kernel_dilation: Optional[Tuple[int, ...]] = None,
+                          kernel_center_offset: Optional[Tuple[int, ...]] = None):
     """Search every position of a ``kernel_sizes`` window around each query.
 
     ``return_type="indices"`` returns ``found[K, M]`` (-1 = absent), "offsets" an
@@ -54,6 +55,7 @@ def _kernel_map_from_size(hashtable: TorchHashTable, batched_query_coords: Tenso
     K//2 positions are searched (torch_discrete.py:291-296).  ``self_map``: the queries are the
     rows the table was built from, in the same order (odd window, stride 1); the native call
     then probes half of the offsets and mirrors the rest when the rows are distinct.
+    ``kernel_center_offset`` moves the window: position (i, j, l) probes ``x + (i - cx) * dx`` ...
     """
     dev = hashtable.device
     assert str(dev) == str(batched_query_coords.device)
@@ -76,7 +78,11 @@ def _kernel_map_from_size(hashtable: TorchHashTable, batched_query_coords: Tenso
     dil = (ctypes.c_int32 * 3)(*[int(d) for d in (kernel_dilation or (1, 1, 1))])
     # hit counts are only needed by the compact form; IntSearchResult makes them on demand
     ws = None
-    if (self_map and not skip_symmetric_kernel_map and all(k % 2 == 1 for k in kernel_sizes)
+    ctr = None
+    if kernel_center_offset is not None:
+        assert len(kernel_center_offset) == 3
+        ctr = (ctypes.c_int32 * 3)(*[int(c) for c in kernel_center_offset])
+    if (self_map and ctr is None and not skip_symmetric_kernel_map and all(k % 2 == 1 for k in kernel_sizes)
             and all(int(s) == 1 for s in (query_stride or (1, 1, 1)))):
         assert M == len(hashtable.vector_keys), "self_map needs the table's own rows as queries"
         check(lib().wcn_kmap_search_self(ptr(hashtable._table), hashtable.capacity, hashtable.hash_method.value,
@@ -85,7 +91,8 @@ def _kernel_map_from_size(hashtable: TorchHashTable, batched_query_coords: Tenso
     else:
         check(lib().wcn_kmap_search_dilated(ptr(hashtable._table), hashtable.capacity, hashtable.hash_method.value,
                                             ptr(q), M, ctypes.addressof(strd), ctypes.addressof(ksz),
-                                            ctypes.addressof(dil), K, ptr(nbr), None, stream_ptr(dev)),
+                                            ctypes.addressof(dil), ctypes.addressof(ctr) if ctr is not None else None,
+                                            K, ptr(nbr), None, stream_ptr(dev)),
               "wcn_kmap_search_dilated")
     if return_type == "indices":
         return nbr
@@ -120,16 +127,22 @@ def generate_kernel_map(batch_indexed_in_coords: Tensor, batch_indexed_out_coord
 
     identity_map_index = None
     is_odd = all(k % 2 == 1 for k in kernel_size)
-    if is_odd and batch_indexed_in_coords.shape[0] == batch_indexed_out_coords.shape[0]:
+    default_center = kernel_center_offset is None or all(
+        int(c) == ((k - 1) // 2 if k % 2 == 1 else 0) for c, k in zip(kernel_center_offset, kernel_size))
+    if is_odd and default_center and batch_indexed_in_coords.shape[0] == batch_indexed_out_coords.shape[0]:
         identity_map_index = int(np.prod(kernel_size)) // 2
     if skip_symmetric_kernel_map and not is_odd:
         skip_symmetric_kernel_map = False
 
     if method not in ("size", "offset"):
         raise ValueError(f"Invalid method: {method}. Choose 'query', 'offset', or 'size'.")
-    # Both methods reduce to the window search (dilated when asked); a custom centre is not
-    # expressible by it.
-    assert kernel_center_offset is None, "Custom kernel_center_offset is not supported."
+    # Both methods reduce to the window search, which takes a dilation and a window centre.  The
+    # reference accepts those two only with method="offset" (torch_discrete.py:449-456).
+    if method == "size":
+        assert kernel_center_offset is None, \
+            "Custom kernel_center_offset is not supported with method='size'. Use method='offset' instead."
+    if kernel_center_offset is not None:
+        assert len(kernel_center_offset) == nd and not skip_symmetric_kernel_map
 
     if hashtable is None or hashtable.hash_method != hash_method:
         hashtable = TorchHashTable.from_keys(batch_indexed_in_coords, hash_method=hash_method, device=dev)
@@ -140,6 +153,7 @@ def generate_kernel_map(batch_indexed_in_coords: Tensor, batch_indexed_out_coord
                                  skip_symmetric_kernel_map=skip_symmetric_kernel_map, query_stride=stride,
                                  num_in=batch_indexed_in_coords.shape[0],
                                  kernel_dilation=(tuple(int(d) for d in kernel_dilation) if kernel_dilation else None),
+                                 kernel_center_offset=(None if default_center else tuple(int(c) for c in kernel_center_offset)),
                                  self_map=(batch_indexed_out_coords.data_ptr() == batch_indexed_in_coords.data_ptr()
                                            and batch_indexed_out_coords.shape == batch_indexed_in_coords.shape
                                            and batch_indexed_in_coords.is_contiguous()))

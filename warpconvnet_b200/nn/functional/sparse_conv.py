@@ -68,13 +68,18 @@ class ConvEpilogue:
     output dtype.  ``out_rows`` (a permutation of ``0..M-1``) stores result row
     ``s`` at row ``out_rows[s]`` of the output, e.g. the ``perm`` of a sorted
     ``Voxels`` to get the rows back in the order they had before the sort; it
-    cannot be combined with ``residual``."""
+    cannot be combined with ``residual``.  ``out`` is an optional preallocated
+    ``[M, C_out]`` destination whose rows may be further apart than ``C_out``
+    elements (``out.stride(1) == 1``), e.g. a column block of the buffer a later
+    layer reads as the concatenation of two tensors: the convolution then writes
+    its half in place and no ``cat`` copy is needed."""
 
     scale: Optional[Tensor] = None
     shift: Optional[Tensor] = None
     residual: Optional[Tensor] = None
     relu: bool = False
     out_rows: Optional[Tensor] = None
+    out: Optional[Tensor] = None
 
 
 def _normalize_fwd_algo(algo) -> SPARSE_CONV_FWD_ALGO_MODE:
@@ -106,14 +111,16 @@ def _normalize_fwd_algo(algo) -> SPARSE_CONV_FWD_ALGO_MODE:
 
 def _gather_rows(src: Tensor, idx: Tensor) -> Tensor:
     dst = torch.empty((idx.shape[0], src.shape[1]), dtype=src.dtype, device=src.device)
-    check(lib().wcn_gather_rows(ptr(src), ptr(idx), ptr(dst), idx.shape[0], src.shape[1], dtype_code(src.dtype),
-                                stream_ptr(src.device)), "wcn_gather_rows")
+    check(lib().wcn_gather_rows(ptr(src), src.shape[0], ptr(idx), ptr(dst), idx.shape[0], src.shape[1],
+                                dtype_code(src.dtype), ptr(device_status(src.device)), stream_ptr(src.device)),
+          "wcn_gather_rows")
     return dst
 
 
 def _scatter_add_rows(src: Tensor, idx: Tensor, dst: Tensor) -> None:
-    check(lib().wcn_scatter_add_rows(ptr(src), ptr(idx), ptr(dst), idx.shape[0], src.shape[1],
-                                     dtype_code(src.dtype), stream_ptr(src.device)), "wcn_scatter_add_rows")
+    check(lib().wcn_scatter_add_rows(ptr(src), ptr(idx), ptr(dst), dst.shape[0], idx.shape[0], src.shape[1],
+                                     dtype_code(src.dtype), ptr(device_status(src.device)), stream_ptr(src.device)),
+          "wcn_scatter_add_rows")
 
 
 def _explicit_gemm_forward_logic(in_features: Tensor, weight: Tensor, kernel_map: IntSearchResult,
@@ -178,21 +185,52 @@ TILE_ORDER_MIN_ROWS = 1024
 TILE_ORDER_MIN_OFFSETS = 9
 
 
+def _row_view(t: Tensor) -> Tensor:
+    """``t`` as a matrix whose rows are contiguous (any row stride), copying only if they are not."""
+    return t if t.dim() == 2 and t.stride(1) == 1 and t.stride(0) >= t.shape[1] else t.contiguous()
+
+
+_workspace_bytes_cache: dict = {}
+
+
+def _conv_workspace(algo: int, num_out: int, K: int, c_in: int, c_out: int, dtype_c: int, out_dtype_c: int,
+                    split_k: int, dev: torch.device) -> Optional[Tensor]:
+    """Scratch for the offset-sliced tensor-core convolution (None when the launch is one pass)."""
+    key = (algo, num_out, K, c_in, c_out, dtype_c, out_dtype_c, split_k, dev.index)
+    nbytes = _workspace_bytes_cache.get(key)
+    if nbytes is None:
+        nbytes = query_bytes("wcn_conv_workspace_bytes", algo, num_out, K, c_in, c_out, dtype_c, out_dtype_c, split_k)
+        if len(_workspace_bytes_cache) > 4096:
+            _workspace_bytes_cache.clear()
+        _workspace_bytes_cache[key] = nbytes
+    return torch.empty(nbytes, dtype=torch.uint8, device=dev) if nbytes else None
+
+
 def sparse_conv_fused(in_features: Tensor, weight: Tensor, kernel_map: IntSearchResult, num_out_coords: int,
                       epilogue: Optional[ConvEpilogue] = None, out_dtype: Optional[torch.dtype] = None,
-                      algo: int = CONV_AUTO, tile_order: Optional[bool] = None) -> Tensor:
+                      algo: int = CONV_AUTO, tile_order: Optional[bool] = None, split_k: int = 0) -> Tensor:
     """One launch: all kernel offsets + epilogue.  The weight is used in the
     feature dtype (fp32, fp16 or bf16); accumulation is fp32.  ``tile_order`` runs the
     output rows grouped by neighbour pattern (``IntSearchResult.tiled_neighbor_table``;
-    same numbers, fewer (tile, offset) pairs to compute); None = by size."""
+    same numbers, fewer (tile, offset) pairs to compute); None = by size.  ``split_k``
+    (the reference's ``split_k_slices``): 0 lets the library divide the kernel offsets of
+    small problems among CTAs, 1 forbids it, 2..16 asks for that many slices.  Features,
+    residual and ``epilogue.out`` may be column blocks of wider matrices."""
     require_cuda(in_features, "in_features")
-    x = in_features if in_features.is_contiguous() else in_features.contiguous()
+    x = _row_view(in_features)
     w, packed = _prepared_weight(weight, x.dtype, algo)
     K, c_in, c_out = w.shape
     assert x.shape[1] == c_in, f"features have {x.shape[1]} channels, weight expects {c_in}"
     dev = x.device
-    out_dtype = out_dtype or x.dtype
-    out = torch.empty((num_out_coords, c_out), dtype=out_dtype, device=dev)
+    ep = epilogue or ConvEpilogue()
+    if ep.out is not None:
+        out = ep.out
+        out_dtype = out_dtype or out.dtype
+        assert out.dtype == out_dtype and out.device == dev and tuple(out.shape) == (num_out_coords, c_out) \
+            and (out.stride(1) == 1 or num_out_coords == 0), "epilogue.out must be [M, C_out] with contiguous rows"
+    else:
+        out_dtype = out_dtype or x.dtype
+        out = torch.empty((num_out_coords, c_out), dtype=out_dtype, device=dev)
     if num_out_coords == 0:
         return out
     if tile_order is None:
@@ -202,7 +240,6 @@ def sparse_conv_fused(in_features: Tensor, weight: Tensor, kernel_map: IntSearch
     else:
         nbr, out_rows = kernel_map.neighbor_table(num_out_coords), None
     assert nbr.shape[0] == K, f"kernel map has {nbr.shape[0]} offsets, weight has {K}"
-    ep = epilogue or ConvEpilogue()
     if ep.out_rows is not None:
         assert ep.residual is None, "out_rows cannot be combined with a residual"
         assert ep.out_rows.shape == (num_out_coords,), "out_rows must have one entry per output row"
@@ -214,13 +251,15 @@ def sparse_conv_fused(in_features: Tensor, weight: Tensor, kernel_map: IntSearch
     residual = None
     if ep.residual is not None:
         residual = ep.residual if ep.residual.dtype == out_dtype else ep.residual.to(dtype=out_dtype)
-        if not residual.is_contiguous():
-            residual = residual.contiguous()
+        residual = _row_view(residual)
         assert residual.shape == out.shape, f"residual {tuple(residual.shape)} != output {tuple(out.shape)}"
-    check(lib().wcn_conv_fwd(algo, ptr(x), x.shape[0], ptr(w), ptr(packed), ptr(nbr), ptr(out_rows),
-                             num_out_coords, K, c_in,
-                             c_out, dtype_code(x.dtype), ptr(scale), ptr(shift), ptr(residual), int(ep.relu),
-                             ptr(out), dtype_code(out_dtype), ptr(device_status(dev)), stream_ptr(dev)),
+    dc, odc = dtype_code(x.dtype), dtype_code(out_dtype)
+    ws = _conv_workspace(algo, num_out_coords, K, c_in, c_out, dc, odc, split_k, dev) if packed is not None else None
+    check(lib().wcn_conv_fwd(algo, ptr(x), x.shape[0], x.stride(0), ptr(w), ptr(packed), ptr(nbr), ptr(out_rows),
+                             num_out_coords, K, c_in, c_out, dc, ptr(scale), ptr(shift), ptr(residual),
+                             residual.stride(0) if residual is not None else 0, int(ep.relu), ptr(out),
+                             out.stride(0), odc, split_k, ptr(ws), ws.numel() if ws is not None else 0,
+                             ptr(device_status(dev)), stream_ptr(dev)),
           "wcn_conv_fwd")
     return out
 
@@ -247,6 +286,25 @@ _cutlass_implicit_gemm_forward_logic = _implicit_gemm_forward_logic
 
 
 # --------------------------------------------------------------------------- output coordinates + kernel map
+
+
+def _with_z(bcoords: Tensor) -> Tensor:
+    """(batch, x, y) rows as (batch, x, y, 0): a 2-D grid is the z = 0 slab of a 3-D one, and a
+    kx x ky window on it is a kx x ky x 1 window, in the same offset order."""
+    return torch.cat([bcoords, torch.zeros((bcoords.shape[0], 1), dtype=bcoords.dtype, device=bcoords.device)], dim=1)
+
+
+def _generate_kernel_map_nd(in_coords: Tensor, out_coords: Tensor, stride, kernel_size, kernel_dilation,
+                            hashtable=None) -> IntSearchResult:
+    """``generate_kernel_map`` for 3 spatial dimensions as is, for 2 through the z = 0 slab."""
+    if in_coords.shape[1] == 4:
+        return generate_kernel_map(in_coords, out_coords, stride, kernel_size, kernel_dilation, hashtable=hashtable)
+    assert in_coords.shape[1] == 3 and out_coords.shape[1] == 3, "coordinates must have 2 or 3 spatial dimensions"
+    same = out_coords.data_ptr() == in_coords.data_ptr() and out_coords.shape == in_coords.shape
+    in4 = _with_z(in_coords)
+    out4 = in4 if same else _with_z(out_coords)
+    return generate_kernel_map(in4, out4, tuple(stride) + (1,), tuple(kernel_size) + (1,),
+                               tuple(kernel_dilation) + (1,))
 
 
 def generate_output_coords_and_kernel_map(input_sparse_tensor: Voxels, kernel_size: Tuple[int, ...],
@@ -276,6 +334,8 @@ def generate_output_coords_and_kernel_map(input_sparse_tensor: Voxels, kernel_si
         out_coords, out_offsets = down.batch_indexed_coordinates, down.offsets
     elif generative:
         assert not transposed, "Transposed and generative convolution is not supported yet"
+        if in_coords.shape[1] != 4:
+            raise NotImplementedError("generative convolution needs 3 spatial dimensions")
         grown = expanded_coordinates(input_sparse_tensor.batched_coordinates, kernel_size, kernel_dilation)
         out_coords, out_offsets = grown.batch_indexed_coordinates, grown.offsets
     else:
@@ -303,12 +363,12 @@ def generate_output_coords_and_kernel_map(input_sparse_tensor: Voxels, kernel_si
             fwd = cache.get(key_for(False, out_offsets, input_sparse_tensor.offsets))
         if fwd is None:
             # forward map: table on the (fine) output coordinates, (coarse) inputs * stride as queries
-            fwd = generate_kernel_map(out_coords, in_coords, stride, kernel_size, kernel_dilation,
-                                      hashtable=_cached_table(output_spatially_sparse_tensor, out_coords))
+            fwd = _generate_kernel_map_nd(out_coords, in_coords, stride, kernel_size, kernel_dilation,
+                                          hashtable=_cached_table(output_spatially_sparse_tensor, out_coords))
         kernel_map = fwd.swapped(num_in=out_coords.shape[0])
     else:
-        kernel_map = generate_kernel_map(in_coords, out_coords, stride, kernel_size, kernel_dilation,
-                                         hashtable=_cached_table(input_sparse_tensor, in_coords))
+        kernel_map = _generate_kernel_map_nd(in_coords, out_coords, stride, kernel_size, kernel_dilation,
+                                             hashtable=_cached_table(input_sparse_tensor, in_coords))
 
     if input_sparse_tensor.cache is None:
         input_sparse_tensor._extra_attributes["_cache"] = IntSearchCache()
@@ -328,7 +388,11 @@ def strided_coordinates(coords: IntCoords, stride: Tuple[int, ...]) -> IntCoords
         bc = coords.batch_indexed_coordinates
         if bc.dtype != torch.int32:
             bc = bc.to(torch.int32)
-        out_coords, out_offsets = stride_coords(bc, stride, in_offsets=coords.offsets)
+        if bc.shape[1] == 3:  # two spatial dimensions: stride the z = 0 slab, then drop z again
+            out4, out_offsets = stride_coords(_with_z(bc), stride + (1,), in_offsets=coords.offsets)
+            out_coords = out4[:, :3].contiguous()
+        else:
+            out_coords, out_offsets = stride_coords(bc, stride, in_offsets=coords.offsets)
         hit = IntCoords(out_coords[:, 1:], offsets=out_offsets)
         hit._bcoords = out_coords
         coords._shared[key] = hit
@@ -369,7 +433,7 @@ def prefetch_strided_coordinates(voxels: Voxels, strides) -> List[IntCoords]:
 def _cached_table(voxels: Optional[Voxels], coords: Tensor):
     """The hash table of a tensor's own coordinates (built once per coordinate set and shared
     by every layer that searches it), or None when ``coords`` is not that tensor's own array."""
-    if voxels is None:
+    if voxels is None or coords.shape[1] != 4:
         return None
     ic = voxels.batched_coordinates
     own = ic.batch_indexed_coordinates
@@ -519,7 +583,9 @@ def spatially_sparse_conv(
     _stride = ntuple(stride, ndim=nd)
     algo = _normalize_fwd_algo(fwd_algo)
     feats = input_sparse_tensor.feature_tensor
-    needs_grad = torch.is_grad_enabled() and (feats.requires_grad or weight.requires_grad)
+    # a trainable bias counts: it must reach autograd as a tensor, never folded into a detached epilogue
+    needs_grad = torch.is_grad_enabled() and (feats.requires_grad or weight.requires_grad
+                                              or (bias is not None and bias.requires_grad))
 
     if all(k == 1 for k in _kernel_size) and all(s == 1 for s in _stride):
         native = feats.is_cuda and feats.dtype in (torch.float32, torch.float16, torch.bfloat16)
@@ -554,8 +620,6 @@ def spatially_sparse_conv(
 
     if stride_mode == STRIDED_CONV_MODE.REDUCE_AND_STRIDE and any(s != 1 for s in _stride) and not transposed:
         # pool the stride window first, then convolve at stride 1 on the pooled tensor (:1753-1767)
-        if needs_grad:
-            raise NotImplementedError("stride_mode=reduce_and_stride is an inference path here")
         from .sparse_pool import sparse_reduce
         input_sparse_tensor = sparse_reduce(input_sparse_tensor, kernel_size=_stride, stride=_stride,
                                             reduction=stride_reduce)
@@ -579,16 +643,18 @@ def spatially_sparse_conv(
         if bias is not None:
             out = out + bias.to(out.dtype)
     else:
-        ep = _merge_bias(epilogue, bias)
         if needs_grad:
             if epilogue is not None:
                 raise RuntimeError("a fused epilogue is an inference feature; run under torch.no_grad()")
+            # the bias is added outside the Function, where autograd sees it (reference :1794-1795)
             out = _SparseConvFunction.apply(feats, weight, kernel_map, num_out,
-                                            SPARSE_CONV_FWD_ALGO_MODE.IMPLICIT_GEMM, effective_compute_dtype, ep,
+                                            SPARSE_CONV_FWD_ALGO_MODE.IMPLICIT_GEMM, effective_compute_dtype, None,
                                             _normalize_bwd_algo(bwd_algo))
+            if bias is not None:
+                out = out + bias.to(out.dtype)
         else:
             out = _implicit_gemm_forward_logic(feats, weight, kernel_map, num_out, effective_compute_dtype,
-                                               epilogue=ep)
+                                               epilogue=_merge_bias(epilogue, bias))
 
     # Output coordinates: the input's own coordinate object when they are unchanged, the target's for
     # a transposed convolution, the cached strided set otherwise; all of them already know their
@@ -626,12 +692,13 @@ def _merge_bias(epilogue: Optional[ConvEpilogue], bias: Optional[Tensor]) -> Opt
     if epilogue is None:
         return ConvEpilogue(shift=b)
     if epilogue.scale is None and epilogue.shift is None:
-        return ConvEpilogue(shift=b, residual=epilogue.residual, relu=epilogue.relu, out_rows=epilogue.out_rows)
+        return ConvEpilogue(shift=b, residual=epilogue.residual, relu=epilogue.relu, out_rows=epilogue.out_rows,
+                            out=epilogue.out)
     if epilogue.scale is not None:
         b = b * epilogue.scale.to(b.device).float()
     shift = b if epilogue.shift is None else epilogue.shift.to(b.device).float() + b
     return ConvEpilogue(scale=epilogue.scale, shift=shift, residual=epilogue.residual, relu=epilogue.relu,
-                        out_rows=epilogue.out_rows)
+                        out_rows=epilogue.out_rows, out=epilogue.out)
 
 
 _identity_maps: dict = {}

@@ -70,7 +70,8 @@ def sparse_unpool(pooled_voxels: Voxels, unpooled_voxels: Voxels, kernel_size, s
     assert all(k <= s for k, s in zip(kernel_size, stride)), "un-pooling needs non-overlapping windows"
     n = unpooled_voxels.coordinate_tensor.shape[0]
     up = kernel_map.swapped(num_in=n)
-    rep = neighbor_reduction(pooled_voxels.feature_tensor, up, n, REDUCTIONS.MAX)  # one neighbour per row: a copy
+    # one neighbour per row: the sum is a copy, and its backward is the native sum over the pooling map
+    rep = neighbor_reduction(pooled_voxels.feature_tensor, up, n, REDUCTIONS.SUM)
     if concat_unpooled_voxels:
         rep = torch.cat([unpooled_voxels.feature_tensor, rep], dim=-1)
     return unpooled_voxels.replace(batched_features=rep)

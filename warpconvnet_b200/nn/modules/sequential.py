@@ -68,10 +68,13 @@ def _is_relu(m) -> bool:
 
 
 class Sequential(nn.Sequential, BaseSpatialModule):
-    def forward(self, x: Geometry, residual: Optional[Tensor] = None, final_relu: bool = False):
+    def forward(self, x: Geometry, residual: Optional[Tensor] = None, final_relu: bool = False,
+                out: Optional[Tensor] = None):
         """``residual`` / ``final_relu`` (additions to the reference signature) are
         applied after the last layer: ``relu(out + residual)``; when the tail of the
-        sequence is a fusable conv-BN run they ride in its epilogue."""
+        sequence is a fusable conv-BN run they ride in its epilogue.  ``out`` (inference
+        only) is a preallocated ``[M, C]`` destination for the features of the result, e.g.
+        a column block of a concatenation buffer; it needs that fused tail."""
         assert isinstance(x, Geometry), f"Expected Geometry, got {type(x)}"
         mods = list(self)
         in_sf = x
@@ -94,6 +97,8 @@ class Sequential(nn.Sequential, BaseSpatialModule):
                 if j == len(mods) and (residual is not None or final_relu) and not relu:
                     ep.residual, ep.relu = residual, final_relu
                     fused_tail = True
+                if j == len(mods) and out is not None and (fused_tail or (residual is None and not final_relu)):
+                    ep.out, out = out, None
                 x = m(x, epilogue=ep)
                 i = j
                 continue
@@ -108,4 +113,7 @@ class Sequential(nn.Sequential, BaseSpatialModule):
             if final_relu:
                 f = torch.relu(f)
             x = x.replace(batched_features=f)
+        if out is not None:  # no fused tail took it: copy
+            out.copy_(x.feature_tensor)
+            x = x.replace(batched_features=out)
         return x
