@@ -5,6 +5,13 @@
     python bench.py --gpus N --steps K --warmup W          # this library
     python bench.py --impl reference --steps K --warmup W  # the reference's CPU path
 
+Besides the headline (MinkUNet-34 voxels/s) the line carries, measured outside the timed
+regions: ``kmap`` (kernel-map build alone over 4 x 250 000-voxel rooms, both generators:
+Mcoords/s, algorithmic GB/s and fraction of the HBM copy bandwidth per stage), ``layers`` (single
+layers on a 500 000-voxel room: 3x3x3 / stride-2 down / transposed up, widths 32..256, fp16 and
+bf16), ``strong`` (the SAME 8-room batch divided among the ranks) and, with two or more ranks,
+``config5`` (one 8 M-voxel LiDAR scene split by Morton range with a halo exchange).
+
 One step = one pass of the whole path over one batch held by a rank: Morton
 ordering of the voxels, coordinate hashing, kernel-map generation for every
 resolution level, the 46 3x3x3 / 4 down / 4 up / 1x1x1 convolutions with their
@@ -51,18 +58,23 @@ def parse_args():
     ap.add_argument("--cpu-sample-voxels", type=int, default=150000)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--layers", action="store_true", help="print a per-launch table of the convolutions to stderr")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="skip the kernel-map, single-layer, strong-scaling and partitioned-scene measurements")
+    ap.add_argument("--lidar-voxels", type=int, default=8000000, help="size of the partitioned scene (2+ ranks)")
     return ap.parse_args()
 
 
 # --------------------------------------------------------------------------- workload
 
 
-def make_batch(args, rank):
+def make_batch(args, rank, scene_ids=None):
+    """Rooms ``scene_ids`` (default: the rank's own group of ``--scenes`` rooms) as one batch."""
     from warpconvnet_b200.datasets import synthetic
-    scenes = [synthetic.room_scene(args.voxels, args.voxel_size, 200 + rank * args.scenes + s, args.mode)
-              for s in range(args.scenes)]
+    if scene_ids is None:
+        scene_ids = [rank * args.scenes + s for s in range(args.scenes)]
+    scenes = [synthetic.room_scene(args.voxels, args.voxel_size, 200 + s, args.mode) for s in scene_ids]
     coords, offsets = synthetic.batch_scenes(scenes)
-    feats = np.random.default_rng(1000 + rank).random((len(coords), 3), dtype=np.float32)
+    feats = np.random.default_rng(1000 + scene_ids[0]).random((len(coords), 3), dtype=np.float32)
     return coords, offsets, feats
 
 
@@ -232,6 +244,28 @@ class ConvProfile:
                 out["tc_launches"] += 1; out["tc_ms"] += ms; out["tc_flop"] += fl
         return out
 
+    def by_shape(self, steps, peak_tf, peak_gbs, top=8):
+        """The tensor-core launches of a step grouped by shape, slowest group first: launches and
+        milliseconds per step, useful TFLOP/s, and the fraction of the roofline that binds the
+        shape (max of FLOP time at the tensor peak and algorithmic-byte time at the HBM peak)."""
+        groups = {}
+        for ms, pairs, M, K, c_in, c_out, kind in self.records:
+            if kind != "tcgen05":
+                continue
+            g = groups.setdefault((K, M, c_in, c_out), [0, 0.0, 0.0, 0.0])
+            g[0] += 1
+            g[1] += ms
+            g[2] += 2.0 * pairs * c_in * c_out
+            g[3] += 2.0 * (M * c_in + M * c_out + K * c_in * c_out) + 4.0 * K * M  # fp16 rows in/out + weights + table
+        out = []
+        for (K, M, c_in, c_out), (cnt, ms, fl, by) in sorted(groups.items(), key=lambda kv: -kv[1][1])[:top]:
+            t_tc, t_hbm = fl / (peak_tf * 1e12), by / (peak_gbs * 1e9)
+            out.append({"offsets": K, "rows": M, "c_in": c_in, "c_out": c_out, "launches_per_step": cnt / steps,
+                        "ms_per_step": ms / steps, "useful_tflops": fl / ms / 1e9 if ms > 0 else 0.0,
+                        "bound": "tensor" if t_tc > t_hbm else "hbm",
+                        "roofline_frac": max(t_tc, t_hbm) / (ms * 1e-3) if ms > 0 else 0.0})
+        return out
+
     def table(self, last_n):
         rows = []
         for ms, pairs, M, K, c_in, c_out, kind in self.records[-last_n:]:
@@ -246,17 +280,70 @@ def install_conv_profiler(profile):
     from warpconvnet_b200._native import query_bytes, dtype_code
     orig = F.sparse_conv_fused
 
-    def wrapped(in_features, weight, kernel_map, num_out_coords, epilogue=None, out_dtype=None, algo=0):
-        out = orig(in_features, weight, kernel_map, num_out_coords, epilogue, out_dtype, algo)
+    def wrapped(in_features, weight, kernel_map, num_out_coords, *rest, **kw):
+        out = orig(in_features, weight, kernel_map, num_out_coords, *rest, **kw)
         K, c_in, c_out = weight.shape
         tc = in_features.dtype != torch.float32 and query_bytes(
             "wcn_conv_packed_weight_bytes", 0, K, c_in, c_out, dtype_code(in_features.dtype)) > 0
-        profile.calls.append((lambda: orig(in_features, weight, kernel_map, num_out_coords, epilogue, out_dtype, algo),
+        profile.calls.append((lambda: orig(in_features, weight, kernel_map, num_out_coords, *rest, **kw),
                               kernel_map.neighbor_table(num_out_coords), c_in, c_out, "tcgen05" if tc else "simt"))
         return out
 
     F.sparse_conv_fused = wrapped
     return lambda: setattr(F, "sparse_conv_fused", orig)
+
+
+# DRAM bytes (read + write) of one 3x3x3 C = 96 fp16 launch over 500 000 rows, from the ncu capture
+# summarised under profiles/ (153 MB read + 57 MB written; the algorithmic bytes are 248 MB).
+NCU_DRAM_BYTES_C96_500K = 210e6
+
+
+def measure_strong(args, rank, world, dev, model, forward_of, timed, flush, weak_ms_per_step, weak_voxels):
+    """Strong scaling of the batched workload: the SAME batch of ``--scenes`` rooms (1.2 M voxels)
+    divided among the ranks in contiguous scene groups, no communication; a rank without rooms
+    idles.  Reported as whole-job voxels/s with the slowest rank's time."""
+    import torch.distributed as dist
+    from warpconvnet_b200.dist.sharding import split_scene_groups
+    total = args.scenes * args.voxels
+    if world == 1:
+        return {"n_gpus": 1, "voxels_total": weak_voxels, "ms_per_step": weak_ms_per_step,
+                "value": weak_voxels / (weak_ms_per_step * 1e-3), "unit": UNIT, "scenes_per_rank": [args.scenes]}
+    groups = split_scene_groups([i * args.voxels for i in range(args.scenes + 1)], world)
+    first, last = groups[rank]
+    step = None
+    if last > first:
+        coords_np, offsets_np, feats_np = make_batch(args, rank, scene_ids=list(range(first, last)))
+        xyz = torch.from_numpy(np.ascontiguousarray(coords_np[:, 1:])).to(dev)
+        feats = torch.from_numpy(feats_np).half().to(dev)
+        fwd = forward_of(torch.from_numpy(offsets_np))
+
+        def step():
+            flush.zero_()
+            return fwd(xyz, feats)
+    run = step if step is not None else (lambda: None)
+    steps = max(args.steps, 5)
+    for _ in range(3):
+        run()
+    ms = timed(run, steps)
+    return {"n_gpus": world, "voxels_total": total, "ms_per_step": ms / steps, "value": total * steps / (ms * 1e-3),
+            "unit": UNIT, "scenes_per_rank": [g[1] - g[0] for g in groups],
+            "limit": "per-forward host work (one Python thread per rank) once a rank holds one room or less"}
+
+
+def measure_config5(args, rank, world, dev):
+    """One large LiDAR scene split by Morton range over the ranks: one 3x3x3 stride-1 bf16 convolution,
+    C = 128, with the one-voxel halo exchange; plus a 300 000-voxel scene on which the ranks' rows are
+    compared bit for bit with the single-GPU convolution."""
+    from warpconvnet_b200.examples import partitioned_conv_bench as pcb
+    coords, info = pcb.shared_scene(args.lidar_voxels, 4, 8192, dev, rank, world)
+    res = pcb.measure(coords, 128, torch.bfloat16, 10, rank, world)
+    del coords
+    small, _ = pcb.shared_scene(300000, 4, 2048, dev, rank, world)
+    chk = pcb.measure(small, 128, torch.bfloat16, 2, rank, world, check=True)
+    res["scene"] = info
+    res["check_scene_voxels"] = chk["voxels"]
+    res["max_abs_diff_vs_single_gpu"] = chk.get("max_abs_diff_vs_single_gpu")
+    return res
 
 
 def run_gpu_arm(args):
@@ -297,10 +384,14 @@ def run_gpu_arm(args):
     xyz_dev, feats_dev = xyz_host.to(dev), feats_host.to(dev)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
 
-    def forward(xyz, feats):
-        vox = Voxels(xyz, feats, offsets=offsets)
-        ordered = vox.sort(POINT_ORDERING.MORTON_XYZ)
-        return model(ordered, restore_order=True)  # logits in the caller's row order
+    def make_forward(batch_offsets):
+        def fwd(xyz, feats):
+            vox = Voxels(xyz, feats, offsets=batch_offsets)
+            ordered = vox.sort(POINT_ORDERING.MORTON_XYZ)
+            return model(ordered, restore_order=True)  # logits in the caller's row order
+        return fwd
+
+    forward = make_forward(offsets)
 
     def step_resident():
         flush.zero_()
@@ -351,12 +442,14 @@ def run_gpu_arm(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    def timed(fn, steps):
+    def timed(fn, steps, finish=None):
         barrier()
         s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         s.record()
         for _ in range(steps):
             fn()
+        if finish is not None:
+            finish()  # work on other streams that belongs to the timed steps
         e.record()
         barrier()
         ms = torch.tensor([s.elapsed_time(e)], device=dev, dtype=torch.float64)
@@ -376,7 +469,8 @@ def run_gpu_arm(args):
         launches = _native.launches_total() - before
         for _ in range(2):
             step_e2e()
-        ms_e2e = timed(step_e2e, args.steps)
+        # the last step's device-to-host copy runs on the copy stream: the end event follows it
+        ms_e2e = timed(step_e2e, args.steps, finish=lambda: torch.cuda.current_stream(dev).wait_stream(d2h))
         mark1 = sampler.mark()
         _native.check_device_status(dev)
         time.sleep(0.06)
@@ -401,8 +495,25 @@ def run_gpu_arm(args):
             share = (prof["ms"] / prof_steps) / (ms / args.steps)
             if 0.3 < share < 1.2:
                 break
+        profile_retaken = attempt
         if args.layers and rank == 0:
             print(profile.table(len(profile.records) // prof_steps), file=sys.stderr)
+
+        # ---- further measurements, each outside the two timed regions above
+        strong = config5 = kmap = layers = None
+        if not args.no_extras:
+            strong = measure_strong(args, rank, world, dev, model, forward_of=make_forward, timed=timed, flush=flush,
+                                    weak_ms_per_step=ms / args.steps, weak_voxels=n_vox)
+            if world > 1:
+                config5 = measure_config5(args, rank, world, dev)
+            if rank == 0:
+                from warpconvnet_b200.examples import kernel_map_bench, layer_sweep
+                kmap = []
+                for mode in ("raster_crop", "sample"):
+                    kmap += kernel_map_bench.measure(4, 250000, 0.02, mode, iters=6, dev=dev, flush=flush)
+                layers = layer_sweep.measure(500000, 0.01, "raster_crop", iters=5, dev=dev, flush=flush)
+            _native.check_device_status(dev)
+            barrier()
 
     total_vox = n_vox * world  # every rank holds a batch of the same size
     if world > 1:
@@ -417,16 +528,26 @@ def run_gpu_arm(args):
         if os.path.isfile(peaks_path):
             peaks = json.load(open(peaks_path))
             peak_tf, peak_src = float(peaks["bf16_tflops_sustained"]), "measured sustained bf16 (MEASURED_PEAKS.json)"
+            peak_gbs = float(peaks["hbm_gbs"])
         else:
-            peak_tf, peak_src = 1400.0, "fallback sustained figure"
+            peak_tf, peak_src, peak_gbs = 1400.0, "fallback sustained figure", 6650.0
         achieved_tf = prof["tc_flop"] / (prof["tc_ms"] * 1e-3) / 1e12 if prof["tc_ms"] > 0 else 0.0
+        shapes = profile.by_shape(prof_steps, peak_tf, peak_gbs)
+        dominant = shapes[0] if shapes else None
         roofline = {
             "bound": "tensor", "achieved": achieved_tf, "peak": peak_tf, "unit": "TFLOP/s",
-            "frac": achieved_tf / peak_tf, "traffic": None, "peak_source": peak_src,
+            "frac": achieved_tf / peak_tf,
+            # DRAM bytes per launch of the dominant shape (3x3x3, C = 96, the finest level): ncu's
+            # dram__bytes_read + dram__bytes_write on a 500 000-row launch of the same shape
+            # (profiles/), scaled to this launch's rows; traffic grows in proportion to the rows.
+            "traffic": (NCU_DRAM_BYTES_C96_500K * dominant["rows"] / 500000.0
+                        if dominant and (dominant["c_in"], dominant["c_out"], dominant["offsets"]) == (96, 96, 27) else None),
+            "traffic_of": "dominant shape, per launch", "peak_source": peak_src,
             "kernel": "conv_tcgen05_kernel (all tensor-core convolution launches of a step)",
             "useful_flop_per_step": prof["tc_flop"] / prof_steps, "launches_per_step": prof["tc_launches"] / prof_steps,
             "avg_launch_ms": prof["tc_ms"] / max(prof["tc_launches"], 1),
             "conv_share_of_step": (prof["ms"] / prof_steps) / (ms / args.steps),
+            "profile_retaken": profile_retaken, "by_shape": shapes,
         }
         cpu = None
         if not args.no_cpu_baseline:
@@ -443,7 +564,7 @@ def run_gpu_arm(args):
                     "h2d_bytes_per_step": int(xyz_host.numel() * 4 + feats_host.numel() * 2),
                     "d2h_bytes_per_step": int(logits_host.numel() * 2)},
             "gpu_launches": int(launches), "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu,
-            "voxels_per_gpu": n_vox,
+            "voxels_per_gpu": n_vox, "strong": strong, "kmap": kmap, "layers": layers, "config5": config5,
         }
         print(json.dumps(line), flush=True)
     if world > 1:

@@ -122,10 +122,20 @@ def _conv_tr_block(sd, prefix, g, skip):
     return _Geom(out.coords, torch.relu(_bn(sd, prefix + ".norm_act.0", out.feats)), g.cache)
 
 
+def basic_block(state_dict: Dict[str, torch.Tensor], prefix: str, coords: np.ndarray, feats: torch.Tensor) -> torch.Tensor:
+    """One residual block of the network (examples/mink_unet.py:86-141) on its own: the features it
+    produces for the rows of ``coords``.  ``prefix`` names the block in the state dict
+    ("block3.1"); parameters are used in the dtype of ``feats``."""
+    sd = {k: (v.detach().to("cpu").to(feats.dtype) if v.is_floating_point() else v.detach().to("cpu"))
+          for k, v in state_dict.items() if k.startswith(prefix + ".")}
+    return _basic_block(sd, prefix, _Geom(np.ascontiguousarray(coords, dtype=np.int32), feats, {})).feats
+
+
 def minkunet_forward(state_dict: Dict[str, torch.Tensor], coords: np.ndarray, feats: torch.Tensor,
-                     layers: Sequence[int] = (2, 3, 4, 6, 2, 2, 2, 2)) -> torch.Tensor:
+                     layers: Sequence[int] = (2, 3, 4, 6, 2, 2, 2, 2), trace: Optional[dict] = None) -> torch.Tensor:
     """MinkUNet forward (examples/mink_unet.py:324-361) on CPU tensors from a
-    ``state_dict`` whose parameter names follow the reference model."""
+    ``state_dict`` whose parameter names follow the reference model.  ``trace`` (a dict) receives,
+    per residual block name, ``(coords, input features, output features)``."""
     sd = {k: v.detach().to("cpu") for k, v in state_dict.items()}
     dtype = feats.dtype
     sd = {k: (v.to(dtype) if v.is_floating_point() else v) for k, v in sd.items()}
@@ -133,7 +143,10 @@ def minkunet_forward(state_dict: Dict[str, torch.Tensor], coords: np.ndarray, fe
 
     def blocks(name, g, n):
         for i in range(n):
-            g = _basic_block(sd, f"{name}.{i}", g)
+            out = _basic_block(sd, f"{name}.{i}", g)
+            if trace is not None:
+                trace[f"{name}.{i}"] = (g.coords, g.feats, out.feats)
+            g = out
         return g
 
     out_p1 = _conv_block(sd, "conv0", g, 1)

@@ -52,6 +52,11 @@ def _worker(rank, world, port, out_dir):
         lo, hi = bounds[rank], bounds[rank + 1]
         assert plan.num_owned == hi - lo and sum(plan.recv_counts) == plan.num_halo
         assert plan.recv_counts[rank] == 0 and plan.send_counts[rank] == 0
+        # the owned rows split into those whose window needs a halo row and those that do not
+        both = torch.cat([plan.interior_rows, plan.boundary_rows]).sort().values
+        assert torch.equal(both, torch.arange(plan.num_owned, dtype=torch.int32))
+        assert int((plan.nbr_local[:, plan.interior_rows.long()] >= plan.num_owned).sum()) == 0
+        assert bool((plan.nbr_local[:, plan.boundary_rows.long()] >= plan.num_owned).any(dim=0).all())
         local = plan.exchange(gf[lo:hi])
         # received halo rows are exactly the global rows the plan names
         assert torch.equal(local[plan.num_owned:], gf[plan.halo_global])

@@ -55,22 +55,49 @@ class HaloPlan:
     recv_counts: List[int]            # halo rows arriving from each peer (ascending peer = ascending row)
     send_counts: List[int]            # rows each peer wants from this rank
     send_index: Tensor                # int64 [sum(send_counts)] owned-local rows, grouped by peer
+    interior_rows: Optional[Tensor] = None   # int32: owned rows whose window holds no halo row
+    boundary_rows: Optional[Tensor] = None   # int32: the other owned rows
     kernel_map: object = field(default=None, repr=False)
+    _split_maps: object = field(default=None, repr=False)
+    _comm_stream: object = field(default=None, repr=False)
 
     @property
     def num_local(self) -> int:
         return self.num_owned + self.num_halo
 
+    def new_local(self, channels: int, dtype: torch.dtype, device) -> Tensor:
+        """A ``[owned ; halo]`` feature buffer.  A layer that writes its result into the first
+        ``num_owned`` rows of the next layer's buffer never copies the owned rows."""
+        return torch.empty((self.num_local, channels), dtype=dtype, device=device)
+
+    def exchange_into(self, local: Tensor, group=None) -> None:
+        """Fill the halo rows of ``local`` from the peers' owned rows: gather what they want from
+        ``local[:num_owned]``, one all-to-all with per-peer split sizes."""
+        if self.world_size <= 1 or (self.num_halo == 0 and len(self.send_index) == 0):
+            return
+        owned = local[:self.num_owned]
+        send = owned[self.send_index] if len(self.send_index) else owned[:0]
+        dist.all_to_all_single(local[self.num_owned:], send.contiguous(), self.recv_counts, self.send_counts,
+                               group=group)
+
     def exchange(self, owned_feats: Tensor, group=None) -> Tensor:
-        """[owned ; halo] feature rows: gather what the peers want, one all-to-all."""
-        c = owned_feats.shape[1]
-        local = torch.empty((self.num_local, c), dtype=owned_feats.dtype, device=owned_feats.device)
+        """[owned ; halo] feature rows in a new buffer (copies the owned rows)."""
+        local = self.new_local(owned_feats.shape[1], owned_feats.dtype, owned_feats.device)
         local[:self.num_owned] = owned_feats
-        send = owned_feats[self.send_index] if len(self.send_index) else owned_feats[:0]
-        recv = local[self.num_owned:]
-        if self.world_size > 1:
-            dist.all_to_all_single(recv, send.contiguous(), self.recv_counts, self.send_counts, group=group)
+        self.exchange_into(local, group=group)
         return local
+
+    def split_maps(self):
+        """(interior map, boundary map): the local neighbour table restricted to the owned rows that
+        need no halo row and to those that do.  Built once per plan."""
+        if self._split_maps is None:
+            from ..geometry.coords.search.search_results import IntSearchResult
+            maps = []
+            for rows in (self.interior_rows, self.boundary_rows):
+                nbr = self.nbr_local[:, rows.long()].contiguous()
+                maps.append(IntSearchResult.from_neighbor_table(nbr, self.num_local, None, None))
+            self._split_maps = tuple(maps)
+        return self._split_maps
 
 
 def plan_halo(global_coords_sorted: Tensor, bounds: List[int], rank: int, world_size: int, group=None,
@@ -103,15 +130,63 @@ def plan_halo(global_coords_sorted: Tensor, bounds: List[int], rank: int, world_
         send_index = wanted - lo
     else:
         send_counts, send_index = [0], torch.empty(0, dtype=torch.long, device=halo_global.device)
+    needs_halo = foreign.any(dim=0)
+    rows = torch.arange(hi - lo, device=nbr.device, dtype=torch.int32)
     return HaloPlan(rank, world_size, hi - lo, int(halo_global.numel()), nbr_local, halo_global, recv_counts,
-                    send_counts, send_index)
+                    send_counts, send_index, interior_rows=rows[~needs_halo].contiguous(),
+                    boundary_rows=rows[needs_halo].contiguous())
 
 
-def partitioned_conv(owned_feats: Tensor, weight: Tensor, plan: HaloPlan, epilogue=None, group=None) -> Tensor:
-    """3x3x3 stride-1 convolution of the rows this rank owns: halo exchange + fused kernel."""
+def partitioned_conv(feats: Tensor, weight: Tensor, plan: HaloPlan, epilogue=None, group=None,
+                     overlap: bool = True, out: Optional[Tensor] = None) -> Tensor:
+    """3x3x3 stride-1 convolution of the rows this rank owns.
+
+    ``feats`` is either the owned rows ``[num_owned, C]`` (copied into a new ``[owned ; halo]``
+    buffer) or such a buffer ``[num_local, C]`` from :meth:`HaloPlan.new_local` whose owned rows are
+    filled (nothing is copied; its halo rows are overwritten).  With ``overlap`` the halo exchange
+    runs on a stream of its own while the convolution of the interior rows — those whose window
+    holds no halo row — is already running; the few boundary rows follow once the halo has
+    arrived.  Every output row is computed by the same arithmetic either way, so the result is
+    bit-identical to the single-GPU convolution.  ``out`` (``[num_owned, C_out]``, may be the owned
+    rows of the next layer's buffer) receives the result."""
     from ..geometry.coords.search.search_results import IntSearchResult
-    from ..nn.functional.sparse_conv import sparse_conv_fused
-    if plan.kernel_map is None:
-        plan.kernel_map = IntSearchResult.from_neighbor_table(plan.nbr_local, plan.num_local, None, None)
-    local = plan.exchange(owned_feats, group=group)
-    return sparse_conv_fused(local, weight, plan.kernel_map, plan.num_owned, epilogue=epilogue)
+    from ..nn.functional.sparse_conv import ConvEpilogue, sparse_conv_fused
+    if feats.shape[0] == plan.num_local and plan.num_halo > 0:
+        local = feats
+    else:
+        assert feats.shape[0] == plan.num_owned, "features must be the owned rows or an [owned ; halo] buffer"
+        local = plan.new_local(feats.shape[1], feats.dtype, feats.device)
+        local[:plan.num_owned] = feats
+    ep = epilogue or ConvEpilogue()
+    assert ep.out_rows is None and ep.out is None, "use the out= argument"
+    c_out = weight.shape[2]
+    if out is None:
+        out = torch.empty((plan.num_owned, c_out), dtype=local.dtype, device=local.device)
+    # (a residual is read at the output row, which a launch over a subset of rows cannot say: one launch then)
+    use_overlap = (overlap and plan.world_size > 1 and plan.interior_rows is not None and ep.residual is None
+                   and len(plan.boundary_rows) > 0 and len(plan.interior_rows) > 0)
+    if not use_overlap:
+        plan.exchange_into(local, group=group)
+        if plan.kernel_map is None:
+            plan.kernel_map = IntSearchResult.from_neighbor_table(plan.nbr_local, plan.num_local, None, None)
+        sparse_conv_fused(local, weight, plan.kernel_map, plan.num_owned,
+                          epilogue=ConvEpilogue(ep.scale, ep.shift, ep.residual, ep.relu, None, out))
+        return out
+    if plan._comm_stream is None:
+        plan._comm_stream = torch.cuda.Stream(local.device)
+    main, side = torch.cuda.current_stream(local.device), plan._comm_stream
+    ready, arrived = torch.cuda.Event(), torch.cuda.Event()
+    ready.record(main)
+    # the exchange is enqueued first so that its (small) kernels get multiprocessors before the
+    # persistent convolution kernel occupies all of them
+    with torch.cuda.stream(side):
+        side.wait_event(ready)
+        plan.exchange_into(local, group=group)
+        arrived.record(side)
+    local.record_stream(side)
+    interior, boundary = plan.split_maps()
+    for kmap, rows, wait in ((interior, plan.interior_rows, False), (boundary, plan.boundary_rows, True)):
+        if wait:
+            main.wait_event(arrived)
+        sparse_conv_fused(local, weight, kmap, len(rows), epilogue=ConvEpilogue(ep.scale, ep.shift, None, ep.relu, rows, out))
+    return out

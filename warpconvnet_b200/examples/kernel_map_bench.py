@@ -45,35 +45,32 @@ def time_ms(fn, iters, flush):
     return total / iters
 
 
-def main():
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--scenes", type=int, default=4)
-    ap.add_argument("--voxels", type=int, default=250000)
-    ap.add_argument("--voxel-size", type=float, default=0.02)
-    ap.add_argument("--mode", default="raster_crop")
-    ap.add_argument("--iters", type=int, default=10)
-    ap.add_argument("--sort", action="store_true", help="Morton-sort the voxels first")
-    args = ap.parse_args()
-    dev = torch.device("cuda", 0)
+def measure(scenes: int = 4, voxels: int = 250000, voxel_size: float = 0.02, mode: str = "raster_crop",
+            iters: int = 10, sort: bool = False, dev=None, flush=None):
+    """One dict per stage of the kernel-map build over a batch of synthetic rooms."""
+    dev = dev or torch.device("cuda", 0)
     hbm, src = hbm_peak()
-    scenes = [synthetic.room_scene(args.voxels, args.voxel_size, 100 + s, args.mode) for s in range(args.scenes)]
-    coords, offsets = synthetic.batch_scenes(scenes)
+    rooms = [synthetic.room_scene(voxels, voxel_size, 100 + s, mode) for s in range(scenes)]
+    coords, offsets = synthetic.batch_scenes(rooms)
     fine = torch.from_numpy(coords).to(dev)
-    if args.sort:
+    if sort:
         v = Voxels(fine[:, 1:].contiguous(), torch.zeros(len(fine), 1, device=dev), offsets=torch.from_numpy(offsets))
         fine = v.sort(POINT_ORDERING.MORTON_XYZ).batch_indexed_coordinates.contiguous()
     n = fine.shape[0]
-    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    if flush is None:
+        flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     coarse, _ = stride_coords(fine, (2, 2, 2))
     m2 = coarse.shape[0]
+    lines = []
 
     def report(stage, ms, queries, byts, extra=None):
-        line = {"stage": stage, "ms": ms, "mcoords_per_s": queries / ms / 1e3, "alg_gbs": byts / ms / 1e6,
-                "hbm_frac": byts / ms / 1e6 / hbm, "peak": src, "queries": queries}
+        line = {"stage": stage, "generator": mode, "ms": ms, "mcoords_per_s": queries / ms / 1e3,
+                "alg_bytes": byts, "alg_gbs": byts / ms / 1e6, "hbm_frac": byts / ms / 1e6 / hbm, "peak": src,
+                "queries": queries}
         line.update(extra or {})
-        print(json.dumps(line), flush=True)
+        lines.append(line)
 
-    ms = time_ms(lambda: TorchHashTable.from_keys(fine), args.iters, flush)
+    ms = time_ms(lambda: TorchHashTable.from_keys(fine), iters, flush)
     report("hash_build", ms, n, 32.0 * n)
 
     def full_map(inc, outc, stride, ks):
@@ -86,14 +83,14 @@ def main():
         _, km = full_map(inc, outc, stride, ks)
         L, M = int(km.offsets[-1]), outc.shape[0]
         byts = 32.0 * inc.shape[0] + 16.0 * M + 8.0 * K * M + 24.0 * L + 4.0 * (K + 1)
-        ms = time_ms(lambda: full_map(inc, outc, stride, ks), args.iters, flush)
+        ms = time_ms(lambda: full_map(inc, outc, stride, ks), iters, flush)
         report(name + "_compact", ms, M, byts, {"pairs": L, "pairs_per_query": L / M})
-        ms = time_ms(lambda: generate_kernel_map(inc, outc, stride, ks), args.iters, flush)
+        ms = time_ms(lambda: generate_kernel_map(inc, outc, stride, ks), iters, flush)
         report(name + "_dense_only", ms, M, byts, {"pairs": L, "pairs_per_query": L / M})
-    ms = time_ms(lambda: stride_coords(fine, (2, 2, 2)), args.iters, flush)
+    ms = time_ms(lambda: stride_coords(fine, (2, 2, 2)), iters, flush)
     report("stride_coords_2", ms, n, 16.0 * n + 32.0 * n + 16.0 * m2, {"out": m2})
     down = generate_kernel_map(fine, coarse, (2, 2, 2), (2, 2, 2))
-    ms = time_ms(lambda: down.swapped(num_in=n).neighbor_table(n), args.iters, flush)
+    ms = time_ms(lambda: down.swapped(num_in=n).neighbor_table(n), iters, flush)
     report("transposed_from_forward", ms, n, 4.0 * 8 * (m2 + n))
     # tile order of the 3x3x3 table: read it twice (masks, copy), write it once, plus the row order
     km3 = generate_kernel_map(fine, fine, (1, 1, 1), (3, 3, 3))
@@ -102,9 +99,23 @@ def main():
         km3._tiled = None
         return km3.tiled_neighbor_table(n)
 
-    ms = time_ms(tile_order, args.iters, flush)
+    ms = time_ms(tile_order, iters, flush)
     report("tile_order_3x3x3", ms, n, 4.0 * 27 * n * 3 + 8.0 * n)
     check_device_status(dev)
+    return lines
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--scenes", type=int, default=4)
+    ap.add_argument("--voxels", type=int, default=250000)
+    ap.add_argument("--voxel-size", type=float, default=0.02)
+    ap.add_argument("--mode", default="raster_crop")
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--sort", action="store_true", help="Morton-sort the voxels first")
+    args = ap.parse_args()
+    for line in measure(args.scenes, args.voxels, args.voxel_size, args.mode, args.iters, args.sort):
+        print(json.dumps(line), flush=True)
 
 
 if __name__ == "__main__":

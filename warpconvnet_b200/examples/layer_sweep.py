@@ -51,6 +51,64 @@ def time_ms(fn, iters, flush):
     return total / iters
 
 
+def measure(voxels: int = 500000, voxel_size: float = 0.01, mode: str = "raster_crop", channels=(32, 64, 128, 256),
+            dtypes=("fp16", "bf16"), kinds=("conv3", "down2", "up2"), algo: str = "auto", iters: int = 10,
+            sort: bool = True, dev=None, flush=None):
+    """One dict per (kind, width, dtype) case of the single-layer sweep."""
+    dev = dev or torch.device("cuda", 0)
+    hbm, tflops, src = peaks()
+    xyz = synthetic.room_scene(voxels, voxel_size, 100, mode)
+    n = len(xyz)
+    vox = Voxels(torch.from_numpy(xyz).to(dev), torch.zeros(n, 1, device=dev), offsets=torch.tensor([0, n]))
+    if sort:
+        vox = vox.sort(POINT_ORDERING.MORTON_XYZ)
+    fine = vox.batch_indexed_coordinates.contiguous()
+    coarse, _ = stride_coords(fine, (2, 2, 2))
+    maps = {
+        "conv3": (generate_kernel_map(fine, fine, (1, 1, 1), (3, 3, 3)), n, n),
+        "down2": (generate_kernel_map(fine, coarse, (2, 2, 2), (2, 2, 2)), n, len(coarse)),
+    }
+    maps["up2"] = (maps["down2"][0].swapped(num_in=n), len(coarse), n)
+    if flush is None:
+        flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    g = torch.Generator(device="cpu").manual_seed(0)
+    lines = []
+    for kind_arg in kinds:
+        kind, _, which = kind_arg.partition(":")
+        kmap, n_in, n_out = maps[kind]
+        nbr = kmap.neighbor_table(n_out)
+        pairs = int((nbr >= 0).sum().item())
+        K = nbr.shape[0]
+        for c in channels:
+            for dname in dtypes:
+                dt = DT[dname]
+                x = torch.randn(n_in, c, generator=g).to(dev, dt)
+                bound = (3.0 / (K * c)) ** 0.5 * 1.73
+                w = ((torch.rand(K, c, c, generator=g) * 2 - 1) * bound).to(dev, dt)
+                if which == "dw":    # weight gradient: X^T dY over the rows, one launch
+                    gy = torch.randn(n_out, c, generator=g).to(dev, dt)
+                    fn = lambda: sparse_conv_wgrad(x, gy, kmap, n_out)
+                elif which == "dx":  # input gradient: the forward kernel over the transposed table
+                    gy = torch.randn(n_out, c, generator=g).to(dev, dt)
+                    wt, kt = w.transpose(1, 2).contiguous(), kmap.swapped(num_in=n_in)
+                    fn = lambda: sparse_conv_fused(gy, wt, kt, n_in, algo=ALGOS[algo])
+                else:
+                    fn = lambda: sparse_conv_fused(x, w, kmap, n_out, algo=ALGOS[algo])
+                ms = time_ms(fn, iters, flush)
+                check_device_status(dev)
+                es = 4 if dt == torch.float32 else 2
+                flop = 2.0 * pairs * c * c
+                byts = es * (n_in * c + n_out * c + K * c * c) + 4.0 * n_out * K
+                t_tc, t_hbm = flop / (tflops * 1e12), byts / (hbm * 1e9)
+                lines.append({
+                    "kind": kind_arg, "c": c, "dtype": dname, "voxels_in": n_in, "voxels_out": n_out, "pairs": pairs,
+                    "pairs_per_out": pairs / n_out, "ms": ms, "useful_tflops": flop / ms / 1e9,
+                    "alg_gbs": byts / ms / 1e6, "bound": "tensor" if t_tc > t_hbm else "hbm",
+                    "roofline_frac": max(t_tc, t_hbm) / (ms * 1e-3), "peaks": src,
+                    "mvoxels_per_s": n_in / ms / 1e3})
+    return lines
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--voxels", type=int, default=500000)
@@ -64,57 +122,10 @@ def main():
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--no-sort", action="store_true", help="keep the generator's random row order")
     args = ap.parse_args()
-    dev = torch.device("cuda", 0)
-    hbm, tflops, src = peaks()
-
-    xyz = synthetic.room_scene(args.voxels, args.voxel_size, 100, args.mode)
-    n = len(xyz)
-    vox = Voxels(torch.from_numpy(xyz).to(dev), torch.zeros(n, 1, device=dev), offsets=torch.tensor([0, n]))
-    if not args.no_sort:
-        vox = vox.sort(POINT_ORDERING.MORTON_XYZ)
-    fine = vox.batch_indexed_coordinates.contiguous()
-    coarse, _ = stride_coords(fine, (2, 2, 2))
-    maps = {
-        "conv3": (generate_kernel_map(fine, fine, (1, 1, 1), (3, 3, 3)), n, n),
-        "down2": (generate_kernel_map(fine, coarse, (2, 2, 2), (2, 2, 2)), n, len(coarse)),
-    }
-    maps["up2"] = (maps["down2"][0].swapped(num_in=n), len(coarse), n)
-    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
-    g = torch.Generator(device="cpu").manual_seed(0)
-
-    for kind_arg in args.kinds.split(","):
-        kind, _, which = kind_arg.partition(":")
-        kmap, n_in, n_out = maps[kind]
-        nbr = kmap.neighbor_table(n_out)
-        pairs = int((nbr >= 0).sum().item())
-        K = nbr.shape[0]
-        for c in [int(v) for v in args.channels.split(",")]:
-            for dname in args.dtypes.split(","):
-                dt = DT[dname]
-                x = torch.randn(n_in, c, generator=g).to(dev, dt)
-                bound = (3.0 / (K * c)) ** 0.5 * 1.73
-                w = ((torch.rand(K, c, c, generator=g) * 2 - 1) * bound).to(dev, dt)
-                if which == "dw":    # weight gradient: X^T dY over the rows, one launch
-                    gy = torch.randn(n_out, c, generator=g).to(dev, dt)
-                    fn = lambda: sparse_conv_wgrad(x, gy, kmap, n_out)
-                elif which == "dx":  # input gradient: the forward kernel over the transposed table
-                    gy = torch.randn(n_out, c, generator=g).to(dev, dt)
-                    wt, kt = w.transpose(1, 2).contiguous(), kmap.swapped(num_in=n_in)
-                    fn = lambda: sparse_conv_fused(gy, wt, kt, n_in, algo=ALGOS[args.algo])
-                else:
-                    fn = lambda: sparse_conv_fused(x, w, kmap, n_out, algo=ALGOS[args.algo])
-                ms = time_ms(fn, args.iters, flush)
-                check_device_status(dev)
-                es = 4 if dt == torch.float32 else 2
-                flop = 2.0 * pairs * c * c
-                byts = es * (n_in * c + n_out * c + K * c * c) + 4.0 * n_out * K
-                t_tc, t_hbm = flop / (tflops * 1e12), byts / (hbm * 1e9)
-                print(json.dumps({
-                    "kind": kind_arg, "c": c, "dtype": dname, "voxels_in": n_in, "voxels_out": n_out, "pairs": pairs,
-                    "pairs_per_out": pairs / n_out, "ms": ms, "useful_tflops": flop / ms / 1e9,
-                    "alg_gbs": byts / ms / 1e6, "bound": "tensor" if t_tc > t_hbm else "hbm",
-                    "roofline_frac": max(t_tc, t_hbm) / (ms * 1e-3), "peaks": src,
-                    "mvoxels_per_s": n_in / ms / 1e3}), flush=True)
+    lines = measure(args.voxels, args.voxel_size, args.mode, [int(v) for v in args.channels.split(",")],
+                    args.dtypes.split(","), args.kinds.split(","), args.algo, args.iters, not args.no_sort)
+    for line in lines:
+        print(json.dumps(line), flush=True)
 
 
 if __name__ == "__main__":

@@ -113,6 +113,22 @@ class BatchedTensor:
                 f"device={self.device}, dtype={self.dtype})")
 
 
+def _operator(name: str):
+    def apply(self: BatchedTensor, other):
+        """Element-wise on the stored tensor; ``other`` is a scalar, a tensor that broadcasts against
+        it, or another batch with the same offsets and shape (batched.py:183-229 of the reference)."""
+        if isinstance(other, BatchedTensor):
+            assert self.equal_shape(other), f"shapes do not match: {self} vs {other}"
+            other = other.batched_tensor
+        return self.__class__(getattr(self.batched_tensor, name)(other), self.offsets)
+    apply.__name__ = name
+    return apply
+
+
+for _name in ("__add__", "__sub__", "__mul__", "__truediv__", "__floordiv__", "__mod__", "__pow__"):
+    setattr(BatchedTensor, _name, _operator(_name))
+
+
 class Coords(BatchedTensor):
     def check(self):
         BatchedTensor.check(self)

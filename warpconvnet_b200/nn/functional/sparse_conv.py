@@ -68,7 +68,8 @@ class ConvEpilogue:
     output dtype.  ``out_rows`` (a permutation of ``0..M-1``) stores result row
     ``s`` at row ``out_rows[s]`` of the output, e.g. the ``perm`` of a sorted
     ``Voxels`` to get the rows back in the order they had before the sort; it
-    cannot be combined with ``residual``.  ``out`` is an optional preallocated
+    cannot be combined with ``residual``.  With ``out`` given, ``out_rows`` may
+    also be distinct rows of a taller ``out`` (a launch over a subset of its rows).  ``out`` is an optional preallocated
     ``[M, C_out]`` destination whose rows may be further apart than ``C_out``
     elements (``out.stride(1) == 1``), e.g. a column block of the buffer a later
     layer reads as the concatenation of two tensors: the convolution then writes
@@ -226,7 +227,9 @@ def sparse_conv_fused(in_features: Tensor, weight: Tensor, kernel_map: IntSearch
     if ep.out is not None:
         out = ep.out
         out_dtype = out_dtype or out.dtype
-        assert out.dtype == out_dtype and out.device == dev and tuple(out.shape) == (num_out_coords, c_out) \
+        # with out_rows the launch may cover a subset of the rows of a taller destination
+        rows_ok = out.shape[0] == num_out_coords or (ep.out_rows is not None and out.shape[0] >= num_out_coords)
+        assert out.dtype == out_dtype and out.device == dev and out.dim() == 2 and out.shape[1] == c_out and rows_ok \
             and (out.stride(1) == 1 or num_out_coords == 0), "epilogue.out must be [M, C_out] with contiguous rows"
     else:
         out_dtype = out_dtype or x.dtype
@@ -252,7 +255,8 @@ def sparse_conv_fused(in_features: Tensor, weight: Tensor, kernel_map: IntSearch
     if ep.residual is not None:
         residual = ep.residual if ep.residual.dtype == out_dtype else ep.residual.to(dtype=out_dtype)
         residual = _row_view(residual)
-        assert residual.shape == out.shape, f"residual {tuple(residual.shape)} != output {tuple(out.shape)}"
+        assert tuple(residual.shape) == (num_out_coords, c_out), \
+            f"residual {tuple(residual.shape)} != output {(num_out_coords, c_out)}"
     dc, odc = dtype_code(x.dtype), dtype_code(out_dtype)
     ws = _conv_workspace(algo, num_out_coords, K, c_in, c_out, dc, odc, split_k, dev) if packed is not None else None
     check(lib().wcn_conv_fwd(algo, ptr(x), x.shape[0], x.stride(0), ptr(w), ptr(packed), ptr(nbr), ptr(out_rows),
