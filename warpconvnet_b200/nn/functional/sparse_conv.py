@@ -26,7 +26,7 @@ import numpy as np
 import torch
 from torch import Tensor
 
-from ..._native import (CONV_AUTO, CONV_SIMT, CONV_TCGEN05, check, device_status, dtype_code, lib, ptr,
+from ..._native import (CONV_AUTO, CONV_SIMT, CONV_TCGEN05, LAUNCH_COUNTS, check, device_status, dtype_code, lib, ptr,
                         query_bytes, require_cuda, stream_ptr)
 from ...geometry.coords.integer import IntCoords
 from ...geometry.coords.ops.serialization import POINT_ORDERING, encode
@@ -265,6 +265,8 @@ def sparse_conv_fused(in_features: Tensor, weight: Tensor, kernel_map: IntSearch
                              out.stride(0), odc, split_k, ptr(ws), ws.numel() if ws is not None else 0,
                              ptr(device_status(dev)), stream_ptr(dev)),
           "wcn_conv_fwd")
+    if ws is not None:
+        LAUNCH_COUNTS["wcn_conv_fwd"] += 1  # the offset-sliced form is two kernels: slices, then their sum + epilogue
     return out
 
 
