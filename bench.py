@@ -509,8 +509,9 @@ def run_gpu_arm(args):
             if rank == 0:
                 from warpconvnet_b200.examples import kernel_map_bench, layer_sweep
                 kmap = []
-                for mode in ("raster_crop", "sample"):
+                for mode in ("raster_crop", "sample"):  # rows as generated (voxel table), then Morton-ordered (bricks)
                     kmap += kernel_map_bench.measure(4, 250000, 0.02, mode, iters=6, dev=dev, flush=flush)
+                    kmap += kernel_map_bench.measure(4, 250000, 0.02, mode, iters=6, sort=True, dev=dev, flush=flush)
                 layers = layer_sweep.measure(500000, 0.01, "raster_crop", iters=5, dev=dev, flush=flush)
             _native.check_device_status(dev)
             barrier()

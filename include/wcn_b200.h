@@ -14,11 +14,13 @@
  *  - conditions that can only be detected on the device (hash-table overflow, a bounded
  *    wait that ran out, an index that names no row) are reported through `dev_status`, a
  *    device int32 the caller zeroes beforehand and must read back (poll) when it wants to
- *    know: kernels only ever store a negative wcn_status code into it, the most negative
- *    one wins, and it stays set until the caller zeroes it again.  While it is set the
- *    tensor-core kernels do no work: a convolution fills the rows it was asked for with
- *    NaN, a weight gradient adds nothing.  An out-of-range index itself is never followed:
- *    the access is skipped (the neighbour counts as absent) and WCN_ERR_BOUNDS is stored.
+ *    know: kernels only ever store a negative wcn_status code into it and it stays set until
+ *    the caller zeroes it again.  WCN_ERR_WAIT_EXPIRED overrides the others (the kernel that
+ *    stored it gave up half-way): while the word holds it the tensor-core kernels do no work, a
+ *    convolution fills the rows it was asked for with NaN and a weight gradient adds nothing.
+ *    An out-of-range index is never followed: the access is skipped (the neighbour counts as
+ *    absent), the rest of the launch is computed normally and WCN_ERR_BOUNDS is stored if the
+ *    word was clean.
  *  - the device the stream belongs to must be the current device of the calling thread
  *    (launch geometry is taken from the current device's properties).
  *  - coordinates are int32 rows (batch, x, y, z).  The batch value INT32_MIN is reserved
@@ -214,6 +216,34 @@ int wcn_nbr_transpose(const int32_t* nbr_fwd, int32_t num_offsets, int64_t num_o
 int wcn_kmap_search_self(const void* table, int64_t capacity, int hash_method, const int32_t* keys,
                          int64_t num_keys, const int32_t* kernel_size, const int32_t* dilation, int32_t* nbr,
                          void* stream);
+
+/* Bytes of the brick table of a coordinate set of n rows (a 32-byte header and one 32-byte entry
+ * per slot, 2 n slots allocated, four per brick used). */
+int wcn_brick_table_bytes(int64_t n, int64_t* bytes);
+
+/* Brick table of keys[n,4]: one entry per 4x4x4 brick (aligned to `origin`, a DEVICE pointer to
+ * three int32, NULL = 0) holding the brick's 64-bit occupancy mask and the row of its first voxel.
+ * It is usable when the rows of every brick are consecutive and in Morton order inside the brick
+ * — what sorting by the Morton code of (coords - origin) gives (Voxels.sort) — and the rows are
+ * distinct; the build checks that on the device and marks the table unusable otherwise, in
+ * which case wcn_kmap_search_bricks answers from the voxel table instead.  No host
+ * synchronisation.
+ * No counterpart in the reference, whose kernel map probes one voxel key per offset
+ * (warpconvnet/csrc/discrete_kernels.cu:264-334) whatever the order of the rows; the ordering
+ * itself is the reference's (warpconvnet/geometry/types/voxels.py:255-267,
+ * warpconvnet/csrc/morton_code.cu:15-22). */
+int wcn_brick_build(const int32_t* keys, int64_t n, const int32_t* origin, void* table, void* stream);
+
+/* wcn_kmap_search (same nbr[k*M + m], same offset order and centre rule, dilation 1) answered
+ * from a brick table: one thread per query fetches the at most 2x2x2 brick entries its window
+ * touches and resolves every offset from them.  Window sizes up to 4 per axis
+ * (WCN_ERR_UNSUPPORTED_CONFIG beyond).  `table` / `capacity` / `hash_method` are the voxel table
+ * of the same keys (wcn_hash_build), used when the brick table was marked unusable.
+ * Replaces kernel_map_size_4d_{fnv1a,city,murmur}
+ * (warpconvnet/csrc/discrete_kernels.cu:264-334, 339-370) for Morton-ordered inputs. */
+int wcn_kmap_search_bricks(const void* brick_table, const void* table, int64_t capacity, int hash_method,
+                           const int32_t* queries, int64_t num_queries, const int32_t* stride,
+                           const int32_t* kernel_size, int32_t* nbr, void* stream);
 
 /* Per-block hit counts of a dense neighbour table into `workspace`, exactly what
  * wcn_kmap_search leaves there; for maps that were searched without counts.

@@ -296,3 +296,71 @@ def test_expand_coords_matches_oracle_set():
         assert np.array_equal(offs.numpy(), want_off)
         assert np.all(np.diff(got[:, 0]) >= 0)  # batch-sorted
     check_device_status(DEV)
+
+
+# --------------------------------------------------------------------------- brick tables
+
+
+def _sorted_voxels(coords, offsets):
+    from warpconvnet_b200 import POINT_ORDERING, Voxels
+    vox = Voxels(dev(coords[:, 1:]), torch.zeros(len(coords), 1, device=DEV), offsets=torch.from_numpy(np.asarray(offsets)))
+    return vox.sort(POINT_ORDERING.MORTON_XYZ)
+
+
+def test_brick_table_maps_match_oracle_on_every_level():
+    """Morton-ordered rooms (negative coordinates, ragged batch): the 3x3x3 map, the 2x2x2 stride-2
+    map and its transposed view come from the brick table on the finest level AND on its stride-2
+    and stride-4 down-samplings (the sort's corner is a multiple of 16, so every level stays
+    brick-ordered), bit-exact against the oracle."""
+    from warpconvnet_b200.nn.functional.sparse_conv import strided_coordinates
+    scenes = [synthetic.room_scene(n, 0.02, 510 + i, "raster_crop") - np.array([37, 5, 11], np.int32)
+              for i, n in enumerate((30000, 700, 12000))]
+    coords, offsets = synthetic.batch_scenes(scenes)
+    level = _sorted_voxels(coords, offsets).batched_coordinates
+    for depth in range(3):
+        bt = level.bricks
+        hdr = bt.header()
+        c_dev = level.batch_indexed_coordinates.contiguous()
+        c = c_dev.cpu().numpy()
+        assert hdr["valid"] and 0 < hdr["num_bricks"] < len(c) and hdr["cap"] >= 4 * hdr["num_bricks"]
+        res = generate_kernel_map(c_dev, c_dev, (1, 1, 1), (3, 3, 3), hashtable=level.hashmap, bricks=bt)
+        assert np.array_equal(res.neighbor_table(len(c)).cpu().numpy(), km.kernel_map_found(c, c, (1, 1, 1), (3, 3, 3)))
+        i, o, f, iden = km.generate_kernel_map(c, c, (1, 1, 1), (3, 3, 3))
+        assert_map_equal(res, i, o, f)
+        coarse = strided_coordinates(level, (2, 2, 2))
+        cc_dev = coarse.batch_indexed_coordinates.contiguous()
+        cc = cc_dev.cpu().numpy()
+        assert np.array_equal(cc, km.stride_coords(c, (2, 2, 2))[0])
+        down = generate_kernel_map(c_dev, cc_dev, (2, 2, 2), (2, 2, 2), hashtable=level.hashmap, bricks=bt)
+        want = km.kernel_map_found(c, cc, (2, 2, 2), (2, 2, 2))
+        assert np.array_equal(down.neighbor_table(len(cc)).cpu().numpy(), want)
+        odd = generate_kernel_map(c_dev, cc_dev, (2, 2, 2), (3, 2, 4), hashtable=level.hashmap, bricks=bt)
+        assert np.array_equal(odd.neighbor_table(len(cc)).cpu().numpy(), km.kernel_map_found(c, cc, (2, 2, 2), (3, 2, 4)))
+        level = coarse
+    check_device_status(DEV)
+
+
+def test_brick_table_falls_back_when_rows_are_not_brick_ordered():
+    """Generator (raster) order, rows with repeats, and a corner that does not match the sort:
+    the build marks the table unusable and the same call answers from the voxel table."""
+    from warpconvnet_b200.geometry.coords.search.brick_table import BrickTable
+    xyz = synthetic.room_scene(20000, 0.02, 77, "raster_crop")
+    coords = np.concatenate([np.zeros((len(xyz), 1), np.int32), xyz], 1)
+    dup = np.concatenate([coords, coords[:300]], 0)
+    srt = _sorted_voxels(coords, [0, len(coords)]).batched_coordinates
+    shifted_origin = srt.morton_origin + torch.tensor([1, 0, 2], dtype=torch.int32, device=DEV)
+    cases = [(coords, torch.from_numpy(coords[:, 1:].min(0).astype(np.int32)).to(DEV)),
+             (dup, torch.from_numpy(dup[:, 1:].min(0).astype(np.int32)).to(DEV)),
+             (srt.batch_indexed_coordinates.cpu().numpy(), shifted_origin)]
+    for rows, origin in cases:
+        c_dev = dev(rows)
+        ht = TorchHashTable.from_keys(c_dev)
+        bt = BrickTable(c_dev, origin, ht)
+        assert not bt.header()["valid"]
+        res = generate_kernel_map(c_dev, c_dev, (1, 1, 1), (3, 3, 3), hashtable=ht, bricks=bt)
+        assert np.array_equal(res.neighbor_table(len(rows)).cpu().numpy(),
+                              km.kernel_map_found(rows, rows, (1, 1, 1), (3, 3, 3)))
+    # a sorted set about its own corner is usable whatever the corner's parity
+    own = srt.batch_indexed_coordinates.contiguous()
+    assert BrickTable(own, srt.morton_origin, srt.hashmap).header()["valid"]
+    check_device_status(DEV)

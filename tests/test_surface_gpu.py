@@ -113,8 +113,18 @@ def test_encode_orders_every_batch_segment(voxels_and_sizes):
         sorted_codes = codes[seg]
         assert bool((sorted_codes[1:] >= sorted_codes[:-1]).all())
     assert torch.equal(res.inverse_perm[perm], torch.arange(len(perm), device=DEV))
+    # Voxels.sort takes its codes from the minimum rounded down to a multiple of 16: the same kind of
+    # order (per-segment, non-decreasing in its own codes, a permutation of the rows)
     sorted_vox = vox.sort(POINT_ORDERING.MORTON_XYZ)
-    assert torch.equal(sorted_vox.coordinate_tensor, coords[perm]) and sorted_vox.ordering == POINT_ORDERING.MORTON_XYZ
+    origin = sorted_vox.batched_coordinates.morton_origin
+    assert origin is not None and bool((origin % 16 == 0).all()) and bool((origin <= coords.min(0).values).all())
+    sperm, scode = sorted_vox.extra_attributes["perm"], sorted_vox.extra_attributes["code"]
+    assert torch.equal(sorted_vox.coordinate_tensor, coords[sperm]) and sorted_vox.ordering == POINT_ORDERING.MORTON_XYZ
+    assert torch.equal(scode, morton_code(coords, origin=origin))
+    for b in range(len(offsets) - 1):
+        s, e = int(offsets[b]), int(offsets[b + 1])
+        seg = scode[sperm[s:e]]
+        assert int(sperm[s:e].min()) >= s and int(sperm[s:e].max()) < e and bool((seg[1:] >= seg[:-1]).all())
     assert sorted_vox.sort(POINT_ORDERING.MORTON_XYZ) is sorted_vox
 
 

@@ -38,6 +38,9 @@ SIGNATURES = {
     "wcn_kmap_search_self": [_c_vp, _c_i64, _c_i32, _c_vp, _c_i64, _c_vp, _c_vp, _c_vp, _c_vp],
     "wcn_kmap_search_dilated": [_c_vp, _c_i64, _c_i32, _c_vp, _c_i64, _c_vp, _c_vp, _c_vp, _c_vp, _c_i32, _c_vp, _c_vp, _c_vp],
     "wcn_kmap_count": [_c_vp, _c_i64, _c_i32, _c_vp, _c_vp],
+    "wcn_brick_table_bytes": [_c_i64, _p_i64],
+    "wcn_brick_build": [_c_vp, _c_i64, _c_vp, _c_vp, _c_vp],
+    "wcn_kmap_search_bricks": [_c_vp, _c_vp, _c_i64, _c_i32, _c_vp, _c_i64, _c_vp, _c_vp, _c_vp, _c_vp],
     "wcn_kmap_scan": [_c_vp, _c_i64, _c_i32, _c_vp, _c_vp],
     "wcn_kmap_compact": [_c_vp, _c_i64, _c_i32, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp],
     "wcn_nbr_from_maps": [_c_vp, _c_vp, _c_vp, _c_i32, _c_i64, _c_i64, _c_vp, _c_vp],
@@ -66,7 +69,7 @@ KERNELS_PER_CALL = {
     "wcn_kmap_scan": 2, "wcn_kmap_compact": 1, "wcn_nbr_from_maps": 1, "wcn_nbr_transpose": 1, "wcn_morton20": 1,
     "wcn_kmap_tile_order": 3, "wcn_conv_wgrad": 1, "wcn_kmap_tile_masks": 1, "wcn_row_reduce": 1, "wcn_kmap_search_self": 1, "wcn_kmap_search_dilated": 1, "wcn_kmap_count": 1,
     "wcn_gather_rows": 1, "wcn_scatter_add_rows": 1, "wcn_conv_pack_weight": 1, "wcn_conv_fwd": 1,
-    "wcn_selftest_bounded_wait": 1,
+    "wcn_selftest_bounded_wait": 1, "wcn_brick_build": 3, "wcn_kmap_search_bricks": 1,
 }
 LAUNCH_COUNTS: Counter = Counter()
 

@@ -9,7 +9,7 @@ namespace {
 // applies and the status word, when there is one, receives WCN_ERR_BOUNDS.
 __device__ __forceinline__ bool row_in_range(int64_t i, int64_t limit, int32_t* dev_status) {
   if (i >= 0 && i < limit) return true;
-  if (dev_status) atomicMin(dev_status, (int)WCN_ERR_BOUNDS);
+  wcn_report_bounds(dev_status);
   return false;
 }
 
@@ -116,7 +116,7 @@ __global__ void row_reduce_kernel(const T* __restrict__ feats, int num_in, const
     const int src = __ldg(&nbr[(int64_t)k * M + m]);
     if (src < 0) continue;
     if (src >= num_in) {  // not a feature row: counts as absent and is reported
-      if (dev_status) atomicMin(dev_status, (int)WCN_ERR_BOUNDS);
+      wcn_report_bounds(dev_status);
       continue;
     }
     __align__(16) T v[VEC];

@@ -44,7 +44,7 @@ conv_simt_kernel(const T* __restrict__ feats, const T* __restrict__ weight, cons
       r = m < M ? __ldg(&nbr[(int64_t)k * M + m]) : -1;
       if (r >= lay.num_in) {  // not a feature row: treated as absent and reported
         r = -1;
-        if (lay.dev_status) atomicMin(lay.dev_status, (int)WCN_ERR_BOUNDS);
+        wcn_report_bounds(lay.dev_status);
       }
       rows[threadIdx.x] = r;
     }
@@ -144,7 +144,7 @@ conv_narrow_kernel(const T* __restrict__ feats, const T* __restrict__ weight, co
     const int src = __ldg(&nbr[(int64_t)k * M + slot]);
     if (src < 0) continue;
     if (src >= lay.num_in) {
-      if (lay.dev_status) atomicMin(lay.dev_status, (int)WCN_ERR_BOUNDS);
+      wcn_report_bounds(lay.dev_status);
       continue;
     }
     const T* x = feats + (int64_t)src * lay.in_ld;
@@ -218,7 +218,7 @@ conv_narrow_out_kernel(const T* __restrict__ feats, const T* __restrict__ weight
     const int src = __ldg(&nbr[(int64_t)k * M + slot]);
     if (src < 0) continue;
     if (src >= lay.num_in) {
-      if (lay.dev_status) atomicMin(lay.dev_status, (int)WCN_ERR_BOUNDS);
+      wcn_report_bounds(lay.dev_status);
       continue;
     }
     const uint4* x = reinterpret_cast<const uint4*>(feats + (int64_t)src * lay.in_ld);

@@ -81,7 +81,7 @@ conv_wgrad_tcgen05_kernel(const WgradParams p) {
 
   if (tid == 0) ctl->skip = *(volatile int32_t*)p.dev_status;  // an earlier launch on this status word failed
   __syncthreads();
-  if (ctl->skip != 0) return;
+  if (ctl->skip == (int)WCN_ERR_WAIT_EXPIRED) return;
 
   if (tid == 0) {
     for (int s = 0; s < p.stages; ++s) { mbar_init(bar(&ctl->full[s]), WG_PROD_THREADS); mbar_init(bar(&ctl->empty[s]), 1); }
@@ -132,7 +132,7 @@ conv_wgrad_tcgen05_kernel(const WgradParams p) {
           int r = (unit < total_units && m < p.M) ? __ldg(&p.nbr[(int64_t)k * p.M + m]) : -1;
           if (r >= (int)p.num_in) {  // not a feature row: counts as absent and is reported
             r = -1;
-            atomicMin(p.dev_status, (int)WCN_ERR_BOUNDS);
+            wcn_report_bounds(p.dev_status);
           }
           src[u][j] = r;
         }
@@ -177,7 +177,6 @@ conv_wgrad_tcgen05_kernel(const WgradParams p) {
         if (p.tile_masks && !(__ldg(&p.tile_masks[st]) & gmask)) continue;
         if (!mbar_wait(bar(&ctl->full[slot]), phase, p.dev_status)) { ok = false; break; }
         tc_fence_after();
-        fence_proxy_async_smem();  // the tiles were written by cp.async, the MMAs read them through the async proxy
         const uint32_t a_slot = base + slot * STAGE;
         const uint32_t b_slot = a_slot + A_STAGE;
 #pragma unroll

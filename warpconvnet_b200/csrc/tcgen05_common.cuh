@@ -36,9 +36,10 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return done != 0;
 }
-// Bounded wait.  Returns false when the deadline passed or another thread already
-// reported a failure.  The status word lives in global memory and is looked at about
-// once per millisecond of waiting.
+// Bounded wait.  Returns false when the deadline passed or another thread's wait already ran
+// out.  The status word lives in global memory and is looked at about once per millisecond of
+// waiting.  An expired wait overrides whatever the word held (a skipped out-of-range index is
+// reported with a compare-and-swap that never overrides anything, see wcn_report_bounds).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int32_t* dev_status,
                                           long long limit_cycles = kWaitCycles) {
   if (mbar_try_wait(bar, parity)) return true;
@@ -51,9 +52,9 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int32_t
       if (mbar_try_wait(bar, parity)) return true;
     const long long now = clock64();
     if (now > next_check) {
-      if (*(volatile int32_t*)dev_status != 0) return false;
+      if (*(volatile int32_t*)dev_status == (int)WCN_ERR_WAIT_EXPIRED) return false;
       if (now - t0 > limit_cycles) {
-        atomicMin(dev_status, (int)WCN_ERR_WAIT_EXPIRED);
+        atomicExch(dev_status, (int)WCN_ERR_WAIT_EXPIRED);
         return false;
       }
       next_check = now + poll;
@@ -81,10 +82,12 @@ __device__ __forceinline__ void cp_async_arrive(uint32_t bar) {
 __device__ __forceinline__ void cp_async_drain() {
   asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");
 }
-// Shared-memory tiles filled by cp.async (generic proxy) are read by tcgen05.mma through the
-// async proxy: the issuing thread orders the two with this fence after it has observed the
-// tile's barrier and before it issues the instructions that read the tile.
-__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+// Row tiles are written by cp.async whose completion is signalled through the tile's mbarrier
+// (cp.async.mbarrier.arrive); the MMA issuer waits on that barrier and then issues tcgen05.mma on
+// the tile.  No fence.proxy.async sits between the two: it is the sequence NVIDIA's CUTLASS uses
+// in its sm_100 cp.async + UMMA main loop (producer_commit with cpasync_barrier_arrive,
+// consumer_wait, then the MMAs), and a per-slot proxy fence in the single issuing thread
+// measured 4-8 % of the layer time here.
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 

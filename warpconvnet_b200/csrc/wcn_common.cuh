@@ -108,3 +108,9 @@ __device__ __forceinline__ float wcn_affine(float y, const float* scale, const f
 }
 
 static inline int wcn_dtype_size(int dtype) { return dtype == WCN_F32 ? 4 : 2; }
+
+// An index that names no row was skipped: say so in the status word, unless it already holds
+// something (the first report stays; an expired wait is stored unconditionally and wins).
+__device__ __forceinline__ void wcn_report_bounds(int32_t* dev_status) {
+  if (dev_status) atomicCAS(dev_status, 0, (int)WCN_ERR_BOUNDS);
+}

@@ -6,7 +6,9 @@ map, stride-2 coordinates + 2x2x2 stride-2 map and the matching transposed map.
 Prints one JSON line per stage: milliseconds (CUDA events, L2 flushed between
 iterations), query Mcoords/s, algorithmic GB/s (32 B per inserted key;
 16 + 8 K + 24 L/M bytes per query for a K-offset map with L pairs) and its
-fraction of the HBM copy bandwidth.
+fraction of the HBM copy bandwidth.  With --sort the rooms are Morton-ordered first
+(``Voxels.sort``, timed as its own stage) and the maps come from the brick table; every map
+stage includes building the tables it searches.
 """
 from __future__ import annotations
 
@@ -53,28 +55,49 @@ def measure(scenes: int = 4, voxels: int = 250000, voxel_size: float = 0.02, mod
     rooms = [synthetic.room_scene(voxels, voxel_size, 100 + s, mode) for s in range(scenes)]
     coords, offsets = synthetic.batch_scenes(rooms)
     fine = torch.from_numpy(coords).to(dev)
-    if sort:
-        v = Voxels(fine[:, 1:].contiguous(), torch.zeros(len(fine), 1, device=dev), offsets=torch.from_numpy(offsets))
-        fine = v.sort(POINT_ORDERING.MORTON_XYZ).batch_indexed_coordinates.contiguous()
     n = fine.shape[0]
     if flush is None:
         flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    origin = None
+    sort_ms = None
+    if sort:
+        v = Voxels(fine[:, 1:].contiguous(), torch.zeros(len(fine), 1, device=dev), offsets=torch.from_numpy(offsets))
+        sort_ms = time_ms(lambda: v.sort(POINT_ORDERING.MORTON_XYZ), iters, flush)
+        ordered = v.sort(POINT_ORDERING.MORTON_XYZ).batched_coordinates
+        fine, origin = ordered.batch_indexed_coordinates.contiguous(), ordered.morton_origin
     coarse, _ = stride_coords(fine, (2, 2, 2))
     m2 = coarse.shape[0]
     lines = []
 
     def report(stage, ms, queries, byts, extra=None):
-        line = {"stage": stage, "generator": mode, "ms": ms, "mcoords_per_s": queries / ms / 1e3,
+        line = {"stage": stage, "generator": mode, "order": "morton" if sort else "generator", "ms": ms,
+                "mcoords_per_s": queries / ms / 1e3,
                 "alg_bytes": byts, "alg_gbs": byts / ms / 1e6, "hbm_frac": byts / ms / 1e6 / hbm, "peak": src,
                 "queries": queries}
         line.update(extra or {})
         lines.append(line)
 
+    if sort_ms is not None:
+        report("morton_sort", sort_ms, n, 12.0 * n + 8.0 * n + 2 * 16.0 * n)
     ms = time_ms(lambda: TorchHashTable.from_keys(fine), iters, flush)
     report("hash_build", ms, n, 32.0 * n)
+    if sort:
+        from ..geometry.coords.search.brick_table import BrickTable
+        ht0 = TorchHashTable.from_keys(fine)
+        ms = time_ms(lambda: BrickTable(fine, origin, ht0), iters, flush)
+        hdr = BrickTable(fine, origin, ht0).header()
+        report("brick_build", ms, n, 16.0 * n + 32.0 * hdr["num_bricks"], {"bricks": hdr["num_bricks"], "usable": hdr["valid"]})
+
+    def build_map(inc, outc, stride, ks):
+        """Tables + dense neighbour table, as a forward pass builds them for one level."""
+        if not sort:
+            return generate_kernel_map(inc, outc, stride, ks)
+        from ..geometry.coords.search.brick_table import BrickTable
+        ht = TorchHashTable.from_keys(inc)
+        return generate_kernel_map(inc, outc, stride, ks, hashtable=ht, bricks=BrickTable(inc, origin, ht))
 
     def full_map(inc, outc, stride, ks):
-        km = generate_kernel_map(inc, outc, stride, ks)
+        km = build_map(inc, outc, stride, ks)
         return km.in_maps, km  # forces the compact form too
 
     for name, inc, outc, stride, ks in (("map_3x3x3_s1", fine, fine, (1, 1, 1), (3, 3, 3)),
@@ -85,7 +108,7 @@ def measure(scenes: int = 4, voxels: int = 250000, voxel_size: float = 0.02, mod
         byts = 32.0 * inc.shape[0] + 16.0 * M + 8.0 * K * M + 24.0 * L + 4.0 * (K + 1)
         ms = time_ms(lambda: full_map(inc, outc, stride, ks), iters, flush)
         report(name + "_compact", ms, M, byts, {"pairs": L, "pairs_per_query": L / M})
-        ms = time_ms(lambda: generate_kernel_map(inc, outc, stride, ks), iters, flush)
+        ms = time_ms(lambda: build_map(inc, outc, stride, ks), iters, flush)
         report(name + "_dense_only", ms, M, byts, {"pairs": L, "pairs_per_query": L / M})
     ms = time_ms(lambda: stride_coords(fine, (2, 2, 2)), iters, flush)
     report("stride_coords_2", ms, n, 16.0 * n + 32.0 * n + 16.0 * m2, {"out": m2})

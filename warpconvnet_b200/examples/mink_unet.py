@@ -15,7 +15,8 @@ import torch
 import torch.nn as nn
 
 from ..geometry.types.voxels import Voxels
-from ..nn.functional.sparse_conv import ConvEpilogue, prefetch_strided_coordinates
+from ..geometry.coords.search.search_results import IntSearchResult
+from ..nn.functional.sparse_conv import ConvEpilogue, _implicit_gemm_forward_logic, prefetch_strided_coordinates
 from ..nn.functional.transforms import cat
 from ..nn.modules.activations import ReLU
 from ..nn.modules.sequential import Sequential, fold_batchnorm
@@ -135,7 +136,16 @@ class MinkUNetBase(nn.Module):
         if restore_order:
             perm = x.extra_attributes.get("perm")
             assert perm is not None, "restore_order needs the permutation that Voxels.sort records"
-            return self.final(out, epilogue=ConvEpilogue(out_rows=perm)).feature_tensor
+            # sorted = original[perm], so original row r sits at sorted row inverse[r]: the head reads its
+            # input row THROUGH the inverse permutation (whole 192-byte rows from scattered places) and
+            # writes the logits in order, instead of scattering 40-byte rows
+            n = perm.shape[0]
+            inverse = torch.empty(n, dtype=torch.int32, device=perm.device)
+            inverse[perm] = torch.arange(n, dtype=torch.int32, device=perm.device)
+            unsort = IntSearchResult.from_neighbor_table(inverse.view(1, n), n, None, None)
+            bias = self.final.bias
+            ep = ConvEpilogue(shift=bias.detach().float()) if bias is not None else None
+            return _implicit_gemm_forward_logic(out.feature_tensor, self.final.weight, unsort, n, None, epilogue=ep)
         return self.final(out)
 
     def _forward_joined(self, x: Voxels) -> Voxels:

@@ -76,6 +76,28 @@ class IntCoords(Coords):
         return self._shared["hashmap"]
 
     @property
+    def morton_origin(self) -> Optional[Tensor]:
+        """int32 ``[3]`` device tensor: the corner from which the Morton codes these rows are sorted by
+        were taken, or None when the rows are in no such order (as far as is known)."""
+        return self._shared.get("morton_origin")
+
+    @morton_origin.setter
+    def morton_origin(self, value: Optional[Tensor]):
+        self._shared["morton_origin"] = value
+
+    @property
+    def bricks(self):
+        """Brick table of the batch-indexed coordinates (built once per set of rows), or None when
+        the rows are not known to be Morton-ordered or are not 3-D."""
+        if self._shared.get("morton_origin") is None or self.batched_tensor.shape[1] != 3:
+            return None
+        if self._shared.get("bricks") is None:
+            from .search.brick_table import BrickTable
+            self._shared["bricks"] = BrickTable(self.batch_indexed_coordinates.to(torch.int32),
+                                                self._shared["morton_origin"], self.hashmap)
+        return self._shared["bricks"]
+
+    @property
     def stride(self):
         return self.tensor_stride
 

@@ -48,8 +48,11 @@ class SerializationResult(NamedTuple):
 
 @torch.no_grad()
 def morton_code(coords: Tensor, threads_per_block: int = 256,
-                order: Union[POINT_ORDERING, str] = POINT_ORDERING.MORTON_XYZ) -> Tensor:
-    """int64 Morton codes of ``coords [N,3]`` (integer voxel coordinates)."""
+                order: Union[POINT_ORDERING, str] = POINT_ORDERING.MORTON_XYZ,
+                origin: Optional[Tensor] = None) -> Tensor:
+    """int64 Morton codes of ``coords [N,3]`` (integer voxel coordinates).  ``origin`` (an addition
+    to the reference signature): the per-axis minimum of ``coords`` as an int32 ``[3]`` device
+    tensor, when the caller already has it."""
     if isinstance(order, str):
         order = POINT_ORDERING(order)
     assert order in POINT_ORDERING_TO_MORTON_PERMUTATIONS, f"Order '{order}' not supported for morton code"
@@ -62,7 +65,10 @@ def morton_code(coords: Tensor, threads_per_block: int = 256,
     if perm != [0, 1, 2]:
         c = c[:, perm]
     c = c.contiguous()
-    mins = c.min(dim=0).values.contiguous()  # stays on the device: no host synchronisation
+    if origin is not None and perm == [0, 1, 2]:
+        mins = origin.to(torch.int32).contiguous()
+    else:
+        mins = c.min(dim=0).values.contiguous()  # stays on the device: no host synchronisation
     codes = torch.empty(c.shape[0], dtype=torch.int64, device=c.device)
     check(lib().wcn_morton20(ptr(c), c.shape[0], 3, 0, ptr(mins), ptr(codes), stream_ptr(c.device)),
           "wcn_morton20")
@@ -72,13 +78,13 @@ def morton_code(coords: Tensor, threads_per_block: int = 256,
 @torch.no_grad()
 def encode(grid_coord: Tensor, batch_offsets: Optional[Tensor] = None,
            order: Union[POINT_ORDERING, str] = POINT_ORDERING.MORTON_XYZ, return_perm: bool = False,
-           return_inverse: bool = False, size=None, num_buckets=None):
+           return_inverse: bool = False, size=None, num_buckets=None, origin: Optional[Tensor] = None):
     if isinstance(order, str):
         order = STR2POINT_ORDERING[order.lower()]
     if grid_coord.shape[0] == 0:
         codes = torch.empty(0, dtype=torch.int64)
     elif order in POINT_ORDERING_TO_MORTON_PERMUTATIONS:
-        codes = morton_code(grid_coord[:, -3:], order=order)
+        codes = morton_code(grid_coord[:, -3:], order=order, origin=origin)
     elif order == POINT_ORDERING.RANDOM:
         codes = torch.randperm(grid_coord.shape[0], device=grid_coord.device)
     else:

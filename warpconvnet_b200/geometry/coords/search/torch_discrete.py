@@ -47,7 +47,7 @@ def _kernel_map_from_size(hashtable: TorchHashTable, batched_query_coords: Tenso
                           skip_symmetric_kernel_map: bool = False,
                           query_stride: Optional[Tuple[int, ...]] = None, num_in: Optional[int] = None,
                           self_map: bool = False, kernel_dilation: Optional[Tuple[int, ...]] = None,
-                          kernel_center_offset: Optional[Tuple[int, ...]] = None):
+                          kernel_center_offset: Optional[Tuple[int, ...]] = None, bricks=None):
     """Search every position of a ``kernel_sizes`` window around each query.
 
     ``return_type="indices"`` returns ``found[K, M]`` (-1 = absent), "offsets" an
@@ -56,6 +56,8 @@ def _kernel_map_from_size(hashtable: TorchHashTable, batched_query_coords: Tenso
     rows the table was built from, in the same order (odd window, stride 1); the native call
     then probes half of the offsets and mirrors the rest when the rows are distinct.
     ``kernel_center_offset`` moves the window: position (i, j, l) probes ``x + (i - cx) * dx`` ...
+    ``bricks``: a :class:`BrickTable` of the table's keys; windows up to 4 wide without dilation are
+    then answered from it (same result).
     """
     dev = hashtable.device
     assert str(dev) == str(batched_query_coords.device)
@@ -82,7 +84,14 @@ def _kernel_map_from_size(hashtable: TorchHashTable, batched_query_coords: Tenso
     if kernel_center_offset is not None:
         assert len(kernel_center_offset) == 3
         ctr = (ctypes.c_int32 * 3)(*[int(c) for c in kernel_center_offset])
-    if (self_map and ctr is None and not skip_symmetric_kernel_map and all(k % 2 == 1 for k in kernel_sizes)
+    undilated = all(int(d) == 1 for d in (kernel_dilation or (1, 1, 1)))
+    if (bricks is not None and ctr is None and undilated and not skip_symmetric_kernel_map
+            and all(1 <= int(k) <= 4 for k in kernel_sizes)):
+        assert bricks.hashtable is hashtable, "brick table belongs to another hash table"
+        check(lib().wcn_kmap_search_bricks(ptr(bricks._table), ptr(hashtable._table), hashtable.capacity,
+                                           hashtable.hash_method.value, ptr(q), M, ctypes.addressof(strd),
+                                           ctypes.addressof(ksz), ptr(nbr), stream_ptr(dev)), "wcn_kmap_search_bricks")
+    elif (self_map and ctr is None and not skip_symmetric_kernel_map and all(k % 2 == 1 for k in kernel_sizes)
             and all(int(s) == 1 for s in (query_stride or (1, 1, 1)))):
         assert M == len(hashtable.vector_keys), "self_map needs the table's own rows as queries"
         check(lib().wcn_kmap_search_self(ptr(hashtable._table), hashtable.capacity, hashtable.hash_method.value,
@@ -109,10 +118,11 @@ def generate_kernel_map(batch_indexed_in_coords: Tensor, batch_indexed_out_coord
                         method: Literal["offset", "size"] = "size",
                         hash_method: HashMethod = HashMethod.CITY,
                         skip_symmetric_kernel_map: bool = False,
-                        hashtable: Optional[TorchHashTable] = None) -> IntSearchResult:
+                        hashtable: Optional[TorchHashTable] = None, bricks=None) -> IntSearchResult:
     """Kernel map between input and output coordinates ([N,4] / [M,4] int32).
     ``hashtable`` (an addition to the reference signature): a table already built over
-    ``batch_indexed_in_coords``, to skip rebuilding it."""
+    ``batch_indexed_in_coords``, to skip rebuilding it.  ``bricks`` (likewise): the
+    :class:`BrickTable` of Morton-ordered input coordinates (``IntCoords.bricks``)."""
     dev = batch_indexed_in_coords.device
     assert dev == batch_indexed_out_coords.device
     assert batch_indexed_in_coords.dtype == torch.int32
@@ -148,7 +158,9 @@ def generate_kernel_map(batch_indexed_in_coords: Tensor, batch_indexed_out_coord
         hashtable = TorchHashTable.from_keys(batch_indexed_in_coords, hash_method=hash_method, device=dev)
     else:
         assert len(hashtable.vector_keys) == batch_indexed_in_coords.shape[0], "hashtable was built over other keys"
-    return _kernel_map_from_size(hashtable, batch_indexed_out_coords, kernel_size,
+    if bricks is not None and bricks.hashtable is not hashtable:
+        bricks = None
+    return _kernel_map_from_size(hashtable, batch_indexed_out_coords, kernel_size, bricks=bricks,
                                  identity_map_index=identity_map_index, return_type="offsets",
                                  skip_symmetric_kernel_map=skip_symmetric_kernel_map, query_stride=stride,
                                  num_in=batch_indexed_in_coords.shape[0],

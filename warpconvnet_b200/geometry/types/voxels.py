@@ -68,20 +68,34 @@ class Voxels(Geometry):
 
     # -- whole-tensor transforms
     def sort(self, ordering: POINT_ORDERING = POINT_ORDERING.MORTON_XYZ) -> "Voxels":
-        """Rows of every batch item sorted by Morton code (voxels.py:255-267)."""
+        """Rows of every batch item sorted by Morton code (voxels.py:255-267).
+
+        For ``MORTON_XYZ`` on a CUDA device the codes are taken from the per-axis minimum rounded
+        DOWN to a multiple of 16 (the reference subtracts the minimum itself,
+        coords/ops/serialization.py:224-225; :func:`encode` and :func:`morton_code` still do).  Both are
+        Morton orders of the same rows; with the rounded corner the 4x4x4 bricks of this
+        coordinate set and of its stride-2, 4, 8 and 16 down-samplings are all aligned with the order,
+        which is what lets the kernel maps of every level use a brick table."""
         if ordering == self.ordering:
             return self
         assert isinstance(ordering, POINT_ORDERING), f"Invalid ordering: {ordering}"
-        res = encode(self.coordinate_tensor, batch_offsets=self.offsets, order=ordering, return_perm=True)
+        origin = None
+        coords = self.coordinate_tensor
+        if ordering == POINT_ORDERING.MORTON_XYZ and coords.is_cuda and coords.shape[0] > 0 and coords.shape[1] == 3:
+            lowest = coords.min(dim=0).values.to(torch.int32)
+            origin = (torch.div(lowest, 16, rounding_mode="floor") * 16).contiguous()  # the corner the codes are taken from
+        res = encode(coords, batch_offsets=self.offsets, order=ordering, return_perm=True, origin=origin)
         kwargs = self.extra_attributes
         kwargs["ordering"] = ordering
         kwargs["code"] = res.codes
         kwargs["perm"] = res.perm  # sorted = original[perm]
         kwargs.pop("_cache", None)  # cached maps index the old row order
-        return self.__class__(
-            batched_coordinates=IntCoords(self.coordinate_tensor[res.perm], self.offsets,
-                                          tensor_stride=self.tensor_stride),
-            batched_features=CatFeatures(self.feature_tensor[res.perm], self.offsets), **kwargs)
+        sorted_coords = IntCoords(coords[res.perm], self.offsets, tensor_stride=self.tensor_stride)
+        if origin is not None:
+            # rows sorted by the Morton code of (coords - origin): kernel maps may use a brick table
+            sorted_coords.morton_origin = origin
+        return self.__class__(batched_coordinates=sorted_coords,
+                              batched_features=CatFeatures(self.feature_tensor[res.perm], self.offsets), **kwargs)
 
     def unique(self) -> "Voxels":
         """One voxel per distinct coordinate, keeping its first occurrence (voxels.py:269-276)."""

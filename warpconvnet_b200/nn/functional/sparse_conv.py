@@ -301,10 +301,11 @@ def _with_z(bcoords: Tensor) -> Tensor:
 
 
 def _generate_kernel_map_nd(in_coords: Tensor, out_coords: Tensor, stride, kernel_size, kernel_dilation,
-                            hashtable=None) -> IntSearchResult:
+                            hashtable=None, bricks=None) -> IntSearchResult:
     """``generate_kernel_map`` for 3 spatial dimensions as is, for 2 through the z = 0 slab."""
     if in_coords.shape[1] == 4:
-        return generate_kernel_map(in_coords, out_coords, stride, kernel_size, kernel_dilation, hashtable=hashtable)
+        return generate_kernel_map(in_coords, out_coords, stride, kernel_size, kernel_dilation, hashtable=hashtable,
+                                   bricks=bricks)
     assert in_coords.shape[1] == 3 and out_coords.shape[1] == 3, "coordinates must have 2 or 3 spatial dimensions"
     same = out_coords.data_ptr() == in_coords.data_ptr() and out_coords.shape == in_coords.shape
     in4 = _with_z(in_coords)
@@ -370,11 +371,13 @@ def generate_output_coords_and_kernel_map(input_sparse_tensor: Voxels, kernel_si
         if fwd is None:
             # forward map: table on the (fine) output coordinates, (coarse) inputs * stride as queries
             fwd = _generate_kernel_map_nd(out_coords, in_coords, stride, kernel_size, kernel_dilation,
-                                          hashtable=_cached_table(output_spatially_sparse_tensor, out_coords))
+                                          hashtable=_cached_table(output_spatially_sparse_tensor, out_coords),
+                                          bricks=_cached_bricks(output_spatially_sparse_tensor, out_coords))
         kernel_map = fwd.swapped(num_in=out_coords.shape[0])
     else:
         kernel_map = _generate_kernel_map_nd(in_coords, out_coords, stride, kernel_size, kernel_dilation,
-                                             hashtable=_cached_table(input_sparse_tensor, in_coords))
+                                             hashtable=_cached_table(input_sparse_tensor, in_coords),
+                                             bricks=_cached_bricks(input_sparse_tensor, in_coords))
 
     if input_sparse_tensor.cache is None:
         input_sparse_tensor._extra_attributes["_cache"] = IntSearchCache()
@@ -401,6 +404,13 @@ def strided_coordinates(coords: IntCoords, stride: Tuple[int, ...]) -> IntCoords
             out_coords, out_offsets = stride_coords(bc, stride, in_offsets=coords.offsets)
         hit = IntCoords(out_coords[:, 1:], offsets=out_offsets)
         hit._bcoords = out_coords
+        origin = coords.morton_origin
+        if origin is not None and bc.shape[1] == 4:
+            # First occurrences of floor(c / s) in Morton order are themselves in Morton order about
+            # floor(origin / s) whenever the origin is a multiple of the stride; the brick table's build
+            # checks the order on the device, so a misaligned origin only costs the fallback search.
+            s_t = stride[0] if len(set(stride)) == 1 else torch.tensor(stride, dtype=torch.int32, device=origin.device)
+            hit.morton_origin = torch.div(origin, s_t, rounding_mode="floor").to(torch.int32)
         coords._shared[key] = hit
     return hit
 
@@ -446,6 +456,13 @@ def _cached_table(voxels: Optional[Voxels], coords: Tensor):
     if own.dtype != torch.int32 or own.data_ptr() != coords.data_ptr() or own.shape != coords.shape:
         return None
     return ic.hashmap
+
+
+def _cached_bricks(voxels: Optional[Voxels], coords: Tensor):
+    """The brick table of a tensor's own Morton-ordered coordinates (None when they are not)."""
+    if _cached_table(voxels, coords) is None:
+        return None
+    return voxels.batched_coordinates.bricks
 
 
 # --------------------------------------------------------------------------- autograd
