@@ -194,6 +194,8 @@ def workload_config(args, note=None):
                        "one scene group per GPU, no communication",
            "scenes_per_gpu": args.scenes, "voxels_per_scene": args.voxels, "generator": args.mode,
            "l2": "flushed between steps (256 MiB write); per-step working set is also far larger than L2",
+           "pipelining": "two steps in flight on alternating CUDA streams (a step's coordinate front overlaps the "
+                         "previous step's convolutions); every step does all of its work inside the timed region",
            "step": "morton sort + hash/kernel maps (rebuilt every step) + all convolutions + unpermute"}
     if note:
         cfg["note"] = note
@@ -393,9 +395,23 @@ def run_gpu_arm(args):
 
     forward = make_forward(offsets)
 
+    # Consecutive steps are independent, so two are kept in flight on alternating streams: the front
+    # of a step (Morton sort, coordinate pyramid with its four size read-backs) synchronises the host
+    # with ITS stream only and runs while the other stream still executes the previous step's
+    # convolutions.  Every tensor of a step is allocated, used and freed on the step's own stream.
+    lanes = [torch.cuda.Stream(dev), torch.cuda.Stream(dev)]
+    lane = {"i": 0}
+
     def step_resident():
-        flush.zero_()
-        return forward(xyz_dev, feats_dev)
+        lane["i"] ^= 1
+        with torch.cuda.stream(lanes[lane["i"]]):
+            flush.zero_()
+            return forward(xyz_dev, feats_dev)
+
+    def join_lanes():
+        cur = torch.cuda.current_stream(dev)
+        for s in lanes:
+            cur.wait_stream(s)
 
     # End-to-end step: the host->device copy of step i+1 and the device->host copy of step i run
     # on their own streams and overlap the compute of the neighbouring step (double-buffered
@@ -419,22 +435,23 @@ def run_gpu_arm(args):
 
     def step_e2e():
         i = e2e["i"]
-        b = i % 2
+        b = i % 2  # input buffer b, output buffer b and stream b belong together
         if e2e["in_ready"][b] is None:
             prefetch(i)
-        main = torch.cuda.current_stream(dev)
-        main.wait_event(e2e["in_ready"][b])
-        e2e["in_ready"][b] = None
-        prefetch(i + 1)  # overlaps this step's compute
-        flush.zero_()
-        logits = forward(in_buf[b][0], in_buf[b][1])
-        done = torch.cuda.Event()
-        done.record(main)
-        e2e["done"][b] = done
-        logits.record_stream(d2h)
-        with torch.cuda.stream(d2h):
-            d2h.wait_event(done)
-            out_host[b].copy_(logits, non_blocking=True)  # overlaps the next step's compute
+        main = lanes[b]
+        with torch.cuda.stream(main):
+            main.wait_event(e2e["in_ready"][b])
+            e2e["in_ready"][b] = None
+            prefetch(i + 1)  # overlaps this step's compute
+            flush.zero_()
+            logits = forward(in_buf[b][0], in_buf[b][1])
+            done = torch.cuda.Event()
+            done.record(main)
+            e2e["done"][b] = done
+            logits.record_stream(d2h)
+            with torch.cuda.stream(d2h):
+                d2h.wait_event(done)
+                out_host[b].copy_(logits, non_blocking=True)  # overlaps the next step's compute
         e2e["i"] = i + 1
 
     def barrier():
@@ -446,6 +463,8 @@ def run_gpu_arm(args):
         barrier()
         s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         s.record()
+        for ln in lanes:
+            ln.wait_event(s)  # nothing of the timed steps starts before the start event
         for _ in range(steps):
             fn()
         if finish is not None:
@@ -465,12 +484,16 @@ def run_gpu_arm(args):
         _native.check_device_status(dev)
         mark0 = sampler.mark()
         before = _native.launches_total()
-        ms = timed(step_resident, args.steps)
+        ms = timed(step_resident, args.steps, finish=join_lanes)
         launches = _native.launches_total() - before
         for _ in range(2):
             step_e2e()
         # the last step's device-to-host copy runs on the copy stream: the end event follows it
-        ms_e2e = timed(step_e2e, args.steps, finish=lambda: torch.cuda.current_stream(dev).wait_stream(d2h))
+        def join_e2e():
+            join_lanes()
+            torch.cuda.current_stream(dev).wait_stream(d2h)
+
+        ms_e2e = timed(step_e2e, args.steps, finish=join_e2e)
         mark1 = sampler.mark()
         _native.check_device_status(dev)
         time.sleep(0.06)

@@ -15,8 +15,11 @@ import torch
 import torch.nn as nn
 
 from ..geometry.types.voxels import Voxels
+from ..geometry.coords.search.cache import IntSearchCache
 from ..geometry.coords.search.search_results import IntSearchResult
-from ..nn.functional.sparse_conv import ConvEpilogue, _implicit_gemm_forward_logic, prefetch_strided_coordinates
+from ..nn.functional.sparse_conv import (STRIDED_CONV_MODE, TILE_ORDER_MIN_OFFSETS, TILE_ORDER_MIN_ROWS, ConvEpilogue,
+                                         FusedConvLaunch, _identity_map, _implicit_gemm_forward_logic, _merge_bias,
+                                         generate_output_coords_and_kernel_map, prefetch_strided_coordinates)
 from ..nn.functional.transforms import cat
 from ..nn.modules.activations import ReLU
 from ..nn.modules.sequential import Sequential, fold_batchnorm
@@ -120,6 +123,9 @@ class MinkUNetBase(nn.Module):
         return value is the ``[N, classes]`` tensor in that order, with no separate un-permute."""
         # all four coarse coordinate sets first: their size read-backs then wait for coordinate
         # kernels only, and the convolutions below queue without a host synchronisation
+        plan = self._launch_plan(x)
+        if plan is not None:
+            return plan.run(x, restore_order)
         prefetch_strided_coordinates(x, [2, 2, 2, 2])
         if self.training or torch.is_grad_enabled():
             out_p1 = self.conv0(x)
@@ -147,6 +153,21 @@ class MinkUNetBase(nn.Module):
             ep = ConvEpilogue(shift=bias.detach().float()) if bias is not None else None
             return _implicit_gemm_forward_logic(out.feature_tensor, self.final.weight, unsort, n, None, epilogue=ep)
         return self.final(out)
+
+    def _launch_plan(self, x: Voxels):
+        """The network as a list of launch records (:class:`_LaunchPlan`) when it can run that way:
+        inference, CUDA, three spatial dimensions, features and every parameter in one of the native
+        dtypes.  Rebuilt when a parameter or buffer changes."""
+        if self.training or torch.is_grad_enabled() or not isinstance(x, Voxels):
+            return None
+        feats = x.feature_tensor
+        if not feats.is_cuda or x.num_spatial_dims != 3 or feats.dtype != self.final.weight.dtype \
+                or feats.dtype not in (torch.float32, torch.float16, torch.bfloat16):
+            return None
+        plan = self.__dict__.get("_plan")
+        if plan is None or not plan.current(feats.dtype, feats.device):
+            plan = self.__dict__["_plan"] = _LaunchPlan(self, feats.dtype, feats.device)
+        return plan
 
     def _forward_joined(self, x: Voxels) -> Voxels:
         """Inference body without concatenation copies.  Each skip connection ``cat(up, skip)`` is
@@ -187,6 +208,128 @@ class MinkUNetBase(nn.Module):
         v = self.block7(out_b1p2._derive(buf7))
         self.convtr7(v, out_p1, out=up8)
         return self.block8(out_p1._derive(buf8))
+
+
+class _LaunchPlan:
+    """Inference forward of a :class:`MinkUNetBase` as a fixed sequence of
+    :class:`FusedConvLaunch` records over per-level neighbour tables.
+
+    The module tree is walked once; per forward only the coordinate work (pyramid, kernel maps)
+    and one foreign call per convolution remain, instead of the ``Module`` -> ``Sequential`` ->
+    ``spatially_sparse_conv`` stack for each of the 60-odd layers.  The numbers are those of the
+    module-by-module path (same kernels, same epilogues, same buffers without concatenation
+    copies), and the kernel maps land in the input's shared cache under the same keys."""
+
+    def __init__(self, model: "MinkUNetBase", dtype: torch.dtype, device: torch.device):
+        self.dtype, self.device = dtype, device
+        self.planes, self.init_dim = model.PLANES, model.INIT_DIM
+        self._tensors = list(model.parameters()) + list(model.buffers())
+        self._versions = [t._version for t in self._tensors]
+        self._ptrs = [t.data_ptr() for t in self._tensors]
+
+        def conv_block(seq) -> FusedConvLaunch:
+            conv, bn = seq[0], seq[1]
+            scale, shift = fold_batchnorm(bn)
+            ep = _merge_bias(ConvEpilogue(scale=scale, shift=shift), conv.bias)
+            return FusedConvLaunch(conv.weight, dtype, ep.scale, ep.shift, relu=isinstance(seq[2], (nn.ReLU, ReLU)))
+
+        def basic_block(blk: BasicBlock):
+            last = conv_block(blk.conv2)
+            last.relu = 1  # relu(conv2 + identity)
+            return conv_block(blk.conv1), last, conv_block(blk.downsample) if blk.downsample is not None else None
+
+        def tr_block(blk: ConvTrBlock) -> FusedConvLaunch:
+            scale, shift = fold_batchnorm(blk.norm_act[0])
+            ep = _merge_bias(ConvEpilogue(scale=scale, shift=shift), blk.conv_tr.bias)
+            return FusedConvLaunch(blk.conv_tr.weight, dtype, ep.scale, ep.shift,
+                                   relu=isinstance(blk.norm_act[1], (nn.ReLU, ReLU)))
+
+        assert tuple(model.conv0[0].kernel_size) == (1, 1, 1), "the stem is a 1x1x1 convolution in this plan"
+        self.stem = conv_block(model.conv0)
+        self.down = [conv_block(m) for m in (model.conv1, model.conv2, model.conv3, model.conv4)]
+        self.enc = [[basic_block(b) for b in st] for st in (model.block1, model.block2, model.block3, model.block4)]
+        self.up = [tr_block(m) for m in (model.convtr4, model.convtr5, model.convtr6, model.convtr7)]
+        self.dec = [[basic_block(b) for b in st] for st in (model.block5, model.block6, model.block7, model.block8)]
+        head = model.final
+        self.head = FusedConvLaunch(head.weight, dtype, None, head.bias.detach().float() if head.bias is not None else None)
+
+    def current(self, dtype, device) -> bool:
+        if dtype != self.dtype or device != self.device:
+            return False
+        for t, v, p in zip(self._tensors, self._versions, self._ptrs):
+            if t._version != v or t.data_ptr() != p:
+                return False
+        return True
+
+    @staticmethod
+    def _blocks(stage, x: torch.Tensor, nbr, rows, n: int, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        last = len(stage) - 1
+        for i, (c1, c2, proj) in enumerate(stage):
+            identity = x if proj is None else proj(x, _identity_map(n, x.device).neighbor_table(n), None, n)
+            x = c2(c1(x, nbr, rows, n), nbr, rows, n, residual=identity, out=out if i == last else None)
+        return x
+
+    def run(self, x: Voxels, restore_order: bool):
+        P, dtype, dev = self.planes, self.dtype, self.device
+        ics = [x.batched_coordinates] + prefetch_strided_coordinates(x, [2, 2, 2, 2])
+        n = [ic.batched_tensor.shape[0] for ic in ics]
+        if x.cache is None:  # one kernel-map cache for the whole forward, as the module path shares it
+            x._extra_attributes["_cache"] = IntSearchCache()
+        vox = [x] + [x._derive(x.feature_tensor[:0], ic) for ic in ics[1:]]  # coordinate carriers for the map builder
+        k3, k2, one = (3, 3, 3), (2, 2, 2), (1, 1, 1)
+
+        def conv3_table(level: int):
+            _, _, km = generate_output_coords_and_kernel_map(vox[level], k3, one, one, False, False, None,
+                                                             STRIDED_CONV_MODE.STRIDE_ONLY)
+            if n[level] >= TILE_ORDER_MIN_ROWS and TILE_ORDER_MIN_OFFSETS <= 27:
+                return km.tiled_neighbor_table(n[level])
+            return km.neighbor_table(n[level]), None
+
+        def down_table(level: int):  # level -> level + 1
+            _, _, km = generate_output_coords_and_kernel_map(vox[level], k2, one, k2, False, False, None,
+                                                             STRIDED_CONV_MODE.STRIDE_ONLY)
+            return km.neighbor_table(n[level + 1])
+
+        def up_table(level: int):    # level + 1 -> level
+            _, _, km = generate_output_coords_and_kernel_map(vox[level + 1], k2, one, k2, False, True, vox[level],
+                                                             STRIDED_CONV_MODE.STRIDE_ONLY)
+            return km.neighbor_table(n[level])
+
+        def joined(rows: int, c_up: int, c_skip: int):
+            buf = torch.empty((rows, c_up + c_skip), dtype=dtype, device=dev)
+            return buf, buf[:, :c_up], buf[:, c_up:]
+
+        feats = x.feature_tensor
+        if feats.stride(1) != 1:
+            feats = feats.contiguous()
+        # encoder: every stage writes its result into the right-hand block of its level's skip buffer
+        bufs = [joined(n[0], P[7], self.init_dim), joined(n[1], P[6], P[0]), joined(n[2], P[5], P[1]),
+                joined(n[3], P[4], P[2])]
+        cur = self.stem(feats, _identity_map(n[0], dev).neighbor_table(n[0]), None, n[0], out=bufs[0][2])
+        tables = [None] * 5
+        for level in range(4):
+            cur = self.down[level](cur, down_table(level), None, n[level + 1])
+            tables[level + 1] = conv3_table(level + 1)
+            nbr, rows = tables[level + 1]
+            cur = self._blocks(self.enc[level], cur, nbr, rows, n[level + 1], out=bufs[level + 1][2] if level < 3 else None)
+        # decoder: the transposed convolution fills the left-hand block, the stage reads the whole buffer
+        for i, level in enumerate((3, 2, 1, 0)):
+            buf, left, _ = bufs[level]
+            self.up[i](cur, up_table(level), None, n[level], out=left)
+            if tables[level] is None:
+                tables[level] = conv3_table(level)
+            nbr, rows = tables[level]
+            cur = self._blocks(self.dec[i], buf, nbr, rows, n[level])
+        if restore_order:
+            perm = x.extra_attributes.get("perm")
+            assert perm is not None, "restore_order needs the permutation that Voxels.sort records"
+            # sorted = original[perm], so original row r sits at sorted row inverse[r]: the head reads its
+            # input row THROUGH the inverse permutation (whole rows from scattered places) and writes the
+            # logits in order, instead of scattering 40-byte rows
+            inverse = torch.empty(n[0], dtype=torch.int32, device=dev)
+            inverse[perm] = torch.arange(n[0], dtype=torch.int32, device=dev)
+            return self.head(cur, inverse.view(1, n[0]), None, n[0])
+        return x._derive(self.head(cur, _identity_map(n[0], dev).neighbor_table(n[0]), None, n[0]))
 
 
 class MinkUNet18(MinkUNetBase):

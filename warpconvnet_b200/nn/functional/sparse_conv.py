@@ -270,6 +270,65 @@ def sparse_conv_fused(in_features: Tensor, weight: Tensor, kernel_map: IntSearch
     return out
 
 
+class FusedConvLaunch:
+    """One fused convolution with everything that does not change between calls resolved once:
+    the weight in the compute dtype and its tensor-core re-tiling, the folded scale / shift vectors
+    on the device, the shape and dtype codes, the native entry point.  Calling it enqueues the
+    launch with a handful of attribute reads and one foreign call — the per-layer launch record of
+    an inference loop (the reference re-derives all of it in Python on every call,
+    nn/modules/sequential.py:14-62, nn/functional/sparse_conv.py:1662-1805).
+
+    Arguments are trusted: ``feats`` / ``residual`` / ``out`` are 2-D tensors of the record's dtype
+    with contiguous rows on its device (any row stride), ``nbr`` is the ``[K, num_out]`` int32
+    neighbour table (tiled, with its ``out_rows``, or plain with ``out_rows=None``)."""
+
+    __slots__ = ("weight", "packed", "scale", "shift", "relu", "K", "c_in", "c_out", "dtype", "device", "_dc",
+                 "_w_ptr", "_packed_ptr", "_scale_ptr", "_shift_ptr", "_status_ptr", "_ws_bytes", "_dev_index", "_fn")
+
+    def __init__(self, weight: Tensor, dtype: torch.dtype, scale: Optional[Tensor] = None,
+                 shift: Optional[Tensor] = None, relu: bool = False):
+        w, packed = _prepared_weight(weight, dtype, CONV_AUTO)
+        dev = w.device
+        self.weight, self.packed = w, packed
+        self.scale, self.shift = _as_f32_on(scale, dev), _as_f32_on(shift, dev)
+        self.relu = int(bool(relu))
+        self.K, self.c_in, self.c_out = (int(v) for v in w.shape)
+        self.dtype, self.device, self._dc = dtype, dev, dtype_code(dtype)
+        self._w_ptr, self._packed_ptr = ptr(w), ptr(packed)
+        self._scale_ptr, self._shift_ptr = ptr(self.scale), ptr(self.shift)
+        self._status_ptr = ptr(device_status(dev))
+        self._ws_bytes = {}
+        self._dev_index = dev.index if dev.index is not None else torch.cuda.current_device()
+        self._fn = lib().wcn_conv_fwd
+
+    def __call__(self, feats: Tensor, nbr: Tensor, out_rows: Optional[Tensor], num_out: int,
+                 residual: Optional[Tensor] = None, out: Optional[Tensor] = None) -> Tensor:
+        if out is None:
+            out = torch.empty((num_out, self.c_out), dtype=self.dtype, device=self.device)
+        if num_out == 0:
+            return out
+        ws = None
+        if self._packed_ptr:
+            nbytes = self._ws_bytes.get(num_out)
+            if nbytes is None:
+                nbytes = self._ws_bytes[num_out] = query_bytes("wcn_conv_workspace_bytes", CONV_AUTO, num_out, self.K,
+                                                               self.c_in, self.c_out, self._dc, self._dc, 0)
+            if nbytes:
+                ws = torch.empty(nbytes, dtype=torch.uint8, device=self.device)
+        rc = self._fn(CONV_AUTO, feats.data_ptr(), feats.shape[0], feats.stride(0), self._w_ptr, self._packed_ptr,
+                      nbr.data_ptr(), out_rows.data_ptr() if out_rows is not None else None, num_out, self.K,
+                      self.c_in, self.c_out, self._dc, self._scale_ptr, self._shift_ptr,
+                      residual.data_ptr() if residual is not None else None,
+                      residual.stride(0) if residual is not None else 0, self.relu, out.data_ptr(), out.stride(0),
+                      self._dc, 0, ws.data_ptr() if ws is not None else None, nbytes if ws is not None else 0,
+                      self._status_ptr, torch._C._cuda_getCurrentRawStream(self._dev_index))
+        if rc != 0:
+            check(rc, "wcn_conv_fwd")
+        if ws is not None:
+            LAUNCH_COUNTS["wcn_conv_fwd"] += 1
+        return out
+
+
 def _implicit_gemm_forward_logic(in_features: Tensor, weight: Tensor, kernel_map: IntSearchResult,
                                  num_out_coords: int, compute_dtype: Optional[torch.dtype],
                                  fwd_block_size: Optional[int] = None,
