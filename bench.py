@@ -277,10 +277,12 @@ class ConvProfile:
 
 
 def install_conv_profiler(profile):
-    """Wrap the fused-convolution entry so that each call of a step is recorded for replay."""
+    """Wrap the two fused-convolution entries (the functional one and the launch record the network
+    plan uses) so that each call of a step is recorded for replay."""
     import warpconvnet_b200.nn.functional.sparse_conv as F
     from warpconvnet_b200._native import query_bytes, dtype_code
     orig = F.sparse_conv_fused
+    orig_launch = F.FusedConvLaunch.__call__
 
     def wrapped(in_features, weight, kernel_map, num_out_coords, *rest, **kw):
         out = orig(in_features, weight, kernel_map, num_out_coords, *rest, **kw)
@@ -291,8 +293,19 @@ def install_conv_profiler(profile):
                               kernel_map.neighbor_table(num_out_coords), c_in, c_out, "tcgen05" if tc else "simt"))
         return out
 
+    def launch(self, feats, nbr, out_rows, num_out, residual=None, out=None):
+        res = orig_launch(self, feats, nbr, out_rows, num_out, residual, out)
+        profile.calls.append((lambda: orig_launch(self, feats, nbr, out_rows, num_out, residual, res),
+                              nbr, self.c_in, self.c_out, "tcgen05" if self.packed is not None else "simt"))
+        return res
+
     F.sparse_conv_fused = wrapped
-    return lambda: setattr(F, "sparse_conv_fused", orig)
+    F.FusedConvLaunch.__call__ = launch
+
+    def restore():
+        F.sparse_conv_fused = orig
+        F.FusedConvLaunch.__call__ = orig_launch
+    return restore
 
 
 # DRAM bytes (read + write) of one 3x3x3 C = 96 fp16 launch over 500 000 rows, from the ncu capture

@@ -147,6 +147,17 @@ def stream_ptr(device: torch.device) -> int:
     return torch._C._cuda_getCurrentRawStream(idx)
 
 
+def small_to_device(t: torch.Tensor, device, dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """A small host tensor (batch offsets, a few sizes) on ``device`` WITHOUT synchronising the
+    stream: staged through pinned memory and copied asynchronously.  (A plain ``.to(device)`` of
+    pageable memory waits for everything queued on the stream before it returns.)"""
+    if t.device.type != "cpu":
+        return t.to(device=device, dtype=dtype)
+    if dtype is not None and t.dtype != dtype:
+        t = t.to(dtype)
+    return t.pin_memory().to(device, non_blocking=True)
+
+
 def dtype_code(dtype: torch.dtype) -> int:
     try:
         return _DTYPE_CODE[dtype]

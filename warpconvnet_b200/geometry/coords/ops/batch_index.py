@@ -15,7 +15,9 @@ def batch_index_from_offset(offsets: Tensor) -> Tensor:
 def batch_index_on(offsets: Tensor, n: int, device, dtype=torch.int32) -> Tensor:
     """Batch index of rows 0..n-1 on ``device``: one bucketize of an arange against the
     batch boundaries (no host synchronisation, no repeat_interleave)."""
-    bounds = offsets[1:].to(device=device, dtype=torch.int64)
+    from ...._native import small_to_device
+    bounds = (small_to_device(offsets[1:], device, torch.int64) if torch.device(device).type == "cuda"
+              else offsets[1:].to(device=device, dtype=torch.int64))
     return torch.bucketize(torch.arange(n, device=device, dtype=torch.int64), bounds, right=True).to(dtype)
 
 

@@ -13,7 +13,8 @@ from typing import Optional, Tuple
 import torch
 from torch import Tensor
 
-from ...._native import check, device_status, lib, ptr, query_bytes, raise_for_status, stream_ptr
+from ...._native import (check, device_status, lib, ptr, query_bytes, raise_for_status, small_to_device,
+                         stream_ptr)
 from ....utils.ntuple import ntuple
 from ..search.torch_hashmap import HashMethod
 from .batch_index import offsets_from_batch_index
@@ -65,7 +66,7 @@ def unique_strided_rows(bcoords: Tensor, stride: Tuple[int, int, int] = (1, 1, 1
         # for the device anyway, so a kernel failure recorded earlier surfaces here.
         nb = len(in_offsets)
         packed = torch.empty(nb + 1, dtype=torch.int64, device=dev)
-        torch.searchsorted(uidx, in_offsets.to(device=dev, dtype=torch.int32), out=packed[:nb])
+        torch.searchsorted(uidx, small_to_device(in_offsets, dev, torch.int32), out=packed[:nb])
         packed[nb:].copy_(device_status(dev))
         host = packed.cpu()
         raise_for_status(int(host[nb]), dev)

@@ -18,7 +18,7 @@ from typing import List, Literal, Optional, Tuple
 import torch
 from torch import Tensor
 
-from ...._native import check, device_status, lib, ptr, query_bytes, raise_for_status, stream_ptr
+from ...._native import check, device_status, lib, ptr, query_bytes, raise_for_status, small_to_device, stream_ptr
 
 
 class IntSearchResult:
@@ -105,7 +105,7 @@ class IntSearchResult:
         dev = self._in_maps.device
         K = self._num_offsets
         nbr = torch.empty((K, num_out), dtype=torch.int32, device=dev)
-        offs = self._offsets.to(device=dev, dtype=torch.int32)
+        offs = small_to_device(self._offsets, dev, torch.int32)
         check(lib().wcn_nbr_from_maps(ptr(self._in_maps.contiguous()), ptr(self._out_maps.contiguous()), ptr(offs),
                                       K, len(self._in_maps), num_out, ptr(nbr), stream_ptr(dev)),
               "wcn_nbr_from_maps")
