@@ -364,3 +364,26 @@ def test_brick_table_falls_back_when_rows_are_not_brick_ordered():
     own = srt.batch_indexed_coordinates.contiguous()
     assert BrickTable(own, srt.morton_origin, srt.hashmap).header()["valid"]
     check_device_status(DEV)
+
+
+def test_pyramid_in_one_sync_equals_chained_levels(monkeypatch):
+    """The coordinate pyramid computed from the finest rows with one read-back (small batches) gives,
+    level by level, the rows, order and batch offsets of chaining stride_coords, and both equal the
+    oracle."""
+    import warpconvnet_b200.nn.functional.sparse_conv as F
+    scenes = [synthetic.room_scene(n, 0.02, 530 + i, "raster_crop") - np.array([3, 41, 7], np.int32)
+              for i, n in enumerate((20000, 300, 9000))]
+    coords, offsets = synthetic.batch_scenes(scenes)
+    fast = _sorted_voxels(coords, offsets)
+    levels_fast = F.prefetch_strided_coordinates(fast, [2, 2, 2, 2])
+    monkeypatch.setattr(F, "PYRAMID_ONE_SYNC_MAX_ROWS", 0)
+    slow = _sorted_voxels(coords, offsets)
+    levels_slow = F.prefetch_strided_coordinates(slow, [2, 2, 2, 2])
+    want = fast.batch_indexed_coordinates.cpu().numpy()
+    for a, b in zip(levels_fast, levels_slow):
+        want, want_off = km.stride_coords(want, (2, 2, 2))
+        assert np.array_equal(a.batch_indexed_coordinates.cpu().numpy(), want)
+        assert np.array_equal(b.batch_indexed_coordinates.cpu().numpy(), want)
+        assert np.array_equal(a.offsets.numpy(), want_off) and np.array_equal(b.offsets.numpy(), want_off)
+        assert torch.equal(a.morton_origin, b.morton_origin) and a.bricks.header()["valid"]
+    check_device_status(DEV)

@@ -80,6 +80,55 @@ def unique_strided_rows(bcoords: Tensor, stride: Tuple[int, int, int] = (1, 1, 1
 
 
 @torch.no_grad()
+def strided_pyramid(bcoords: Tensor, total_strides, in_offsets: Tensor, hash_method: HashMethod = HashMethod.CITY):
+    """Distinct rows of ``floor(bcoords / s)`` for SEVERAL strides ``s`` of the same rows, with ONE
+    host synchronisation for all of them: ``[(rows [M_i, 4], CPU offsets [B+1]), ...]``.
+
+    Chaining ``stride_coords`` level by level reads a row count back per level, and each read-back
+    waits for the device; for small batches those waits are most of the cost of the whole
+    coordinate pyramid.  Here every level is computed straight from the finest rows (more hashing,
+    no dependency between levels) and the counts come back together.  Rows come out in
+    first-occurrence order, which is the order the chained computation gives:
+    ``floor(floor(c / 2) / 2) = floor(c / 4)``, and the first occurrence of a coarse cell among the
+    finest rows is the first occurrence of its first child."""
+    assert bcoords.is_cuda and bcoords.dtype == torch.int32 and bcoords.ndim == 2 and bcoords.shape[1] == 4
+    dev = bcoords.device
+    c = bcoords.contiguous()
+    n = c.shape[0]
+    nb = len(in_offsets)
+    if n == 0:
+        return [(c.clone(), torch.zeros(nb, dtype=torch.long)) for _ in total_strides]
+    st = stream_ptr(dev)
+    cap = max(16, 2 * n)
+    table_bytes = query_bytes("wcn_hash_table_bytes", cap)
+    ws_bytes = query_bytes("wcn_unique_workspace_bytes", n)
+    offs_dev = small_to_device(in_offsets, dev, torch.int32)
+    packed = torch.empty((len(total_strides), nb) if total_strides else (0, nb), dtype=torch.int64, device=dev)
+    status = torch.empty(1, dtype=torch.int64, device=dev)
+    outs = []
+    for i, stride in enumerate(total_strides):
+        strd = (ctypes.c_int32 * 3)(*[int(s) for s in stride])
+        sp = ctypes.addressof(strd)
+        table = torch.empty(table_bytes, dtype=torch.uint8, device=dev)
+        check(lib().wcn_hash_build(ptr(c), n, sp, ptr(table), cap, hash_method.value, ptr(device_status(dev)), st),
+              "wcn_hash_build")
+        ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
+        count = torch.empty(1, dtype=torch.int64, device=dev)
+        check(lib().wcn_unique_mark(ptr(c), n, sp, ptr(table), cap, hash_method.value, ptr(ws), ptr(count), st),
+              "wcn_unique_mark")
+        rows = torch.empty((n, 4), dtype=torch.int32, device=dev)
+        uidx = torch.full((n,), torch.iinfo(torch.int32).max, dtype=torch.int32, device=dev)
+        check(lib().wcn_unique_emit(ptr(c), n, sp, ptr(ws), ptr(rows), ptr(uidx), None, st), "wcn_unique_emit")
+        torch.searchsorted(uidx, offs_dev, out=packed[i])
+        outs.append(rows)
+    status.copy_(device_status(dev))
+    host = torch.cat([packed.reshape(-1), status]).cpu()  # the one synchronisation
+    raise_for_status(int(host[-1]), dev)
+    host = host[:-1].reshape(len(total_strides), nb)
+    return [(rows[:int(host[i, -1])], host[i].clone()) for i, rows in enumerate(outs)]
+
+
+@torch.no_grad()
 def stride_coords(batch_indexed_coords: Tensor, stride: Tuple[int, ...], order=None,
                   in_offsets: Optional[Tensor] = None):
     """Down-sample coordinates by ``stride``; returns (coords [M,4], CPU offsets [B+1]).

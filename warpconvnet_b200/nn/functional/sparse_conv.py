@@ -498,11 +498,42 @@ def prefetch_strided_coordinates(voxels: Voxels, strides) -> List[IntCoords]:
     addition to the reference surface; results are identical with or without the call.)"""
     nd = voxels.num_spatial_dims
     level = voxels.batched_coordinates
+    steps = [ntuple(s, ndim=nd) for s in strides]
+    bc = level.batch_indexed_coordinates
+    if (nd == 3 and bc.is_cuda and bc.dtype == torch.int32 and 0 < bc.shape[0] <= PYRAMID_ONE_SYNC_MAX_ROWS
+            and steps and ("strided", steps[0]) not in level._shared):
+        _pyramid_in_one_sync(level, steps)
     out = []
-    for s in strides:
-        level = strided_coordinates(level, ntuple(s, ndim=nd))
+    for s in steps:
+        level = strided_coordinates(level, s)
         out.append(level)
     return out
+
+
+# Below this many rows the whole coordinate pyramid is computed from the finest level with a single
+# host synchronisation (every level hashes all the fine rows); above it the levels are chained
+# (each hashes only the rows of the level before it, one synchronisation per level).
+PYRAMID_ONE_SYNC_MAX_ROWS = 700_000
+
+
+def _pyramid_in_one_sync(level: IntCoords, steps) -> None:
+    """Fill the ``strided`` entries of ``level`` and of every coarser level it leads to, so that the
+    ``strided_coordinates`` calls that follow find them."""
+    from ...geometry.coords.ops.stride import strided_pyramid
+    totals, acc = [], (1, 1, 1)
+    for s in steps:
+        acc = tuple(a * b for a, b in zip(acc, s))
+        totals.append(acc)
+    results = strided_pyramid(level.batch_indexed_coordinates, totals, level.offsets)
+    origin = level.morton_origin
+    for s, total, (rows, offsets) in zip(steps, totals, results):
+        hit = IntCoords(rows[:, 1:], offsets=offsets)
+        hit._bcoords = rows
+        if origin is not None:
+            t = total[0] if len(set(total)) == 1 else torch.tensor(total, dtype=torch.int32, device=origin.device)
+            hit.morton_origin = torch.div(origin, t, rounding_mode="floor").to(torch.int32)
+        level._shared[("strided", s)] = hit
+        level = hit
 
 
 def _cached_table(voxels: Optional[Voxels], coords: Tensor):
