@@ -313,7 +313,8 @@ def install_conv_profiler(profile):
 NCU_DRAM_BYTES_C96_500K = 210e6
 
 
-def measure_strong(args, rank, world, dev, model, forward_of, timed, flush, weak_ms_per_step, weak_voxels):
+def measure_strong(args, rank, world, dev, model, forward_of, timed, flush, weak_ms_per_step, weak_voxels, lanes, lane,
+                   join_lanes):
     """Strong scaling of the batched workload: the SAME batch of ``--scenes`` rooms (1.2 M voxels)
     divided among the ranks in contiguous scene groups, no communication; a rank without rooms
     idles.  Reported as whole-job voxels/s with the slowest rank's time."""
@@ -333,13 +334,15 @@ def measure_strong(args, rank, world, dev, model, forward_of, timed, flush, weak
         fwd = forward_of(torch.from_numpy(offsets_np))
 
         def step():
-            flush.zero_()
-            return fwd(xyz, feats)
+            lane["i"] ^= 1
+            with torch.cuda.stream(lanes[lane["i"]]):  # two steps in flight, as in the headline loop
+                flush.zero_()
+                return fwd(xyz, feats)
     run = step if step is not None else (lambda: None)
     steps = max(args.steps, 5)
     for _ in range(3):
         run()
-    ms = timed(run, steps)
+    ms = timed(run, steps, finish=join_lanes)
     return {"n_gpus": world, "voxels_total": total, "ms_per_step": ms / steps, "value": total * steps / (ms * 1e-3),
             "unit": UNIT, "scenes_per_rank": [g[1] - g[0] for g in groups],
             "limit": "per-forward host work (one Python thread per rank) once a rank holds one room or less"}
@@ -539,7 +542,8 @@ def run_gpu_arm(args):
         strong = config5 = kmap = layers = None
         if not args.no_extras:
             strong = measure_strong(args, rank, world, dev, model, forward_of=make_forward, timed=timed, flush=flush,
-                                    weak_ms_per_step=ms / args.steps, weak_voxels=n_vox)
+                                    weak_ms_per_step=ms / args.steps, weak_voxels=n_vox, lanes=lanes, lane=lane,
+                                    join_lanes=join_lanes)
             if world > 1:
                 config5 = measure_config5(args, rank, world, dev)
             if rank == 0:

@@ -147,7 +147,9 @@ def partitioned_conv(feats: Tensor, weight: Tensor, plan: HaloPlan, epilogue=Non
     runs on a stream of its own while the convolution of the interior rows — those whose window
     holds no halo row — is already running; the few boundary rows follow once the halo has
     arrived.  Every output row is computed by the same arithmetic either way, so the result is
-    bit-identical to the single-GPU convolution.  ``out`` (``[num_owned, C_out]``, may be the owned
+    bit-identical to the single-GPU convolution run in one pass (``split_k=1``: the launches here
+    never divide the kernel offsets among CTAs, which would regroup the fp32 sums of small launches
+    such as the boundary rows).  ``out`` (``[num_owned, C_out]``, may be the owned
     rows of the next layer's buffer) receives the result."""
     from ..geometry.coords.search.search_results import IntSearchResult
     from ..nn.functional.sparse_conv import ConvEpilogue, sparse_conv_fused
@@ -169,7 +171,7 @@ def partitioned_conv(feats: Tensor, weight: Tensor, plan: HaloPlan, epilogue=Non
         plan.exchange_into(local, group=group)
         if plan.kernel_map is None:
             plan.kernel_map = IntSearchResult.from_neighbor_table(plan.nbr_local, plan.num_local, None, None)
-        sparse_conv_fused(local, weight, plan.kernel_map, plan.num_owned,
+        sparse_conv_fused(local, weight, plan.kernel_map, plan.num_owned, split_k=1,
                           epilogue=ConvEpilogue(ep.scale, ep.shift, ep.residual, ep.relu, None, out))
         return out
     if plan._comm_stream is None:
@@ -188,5 +190,6 @@ def partitioned_conv(feats: Tensor, weight: Tensor, plan: HaloPlan, epilogue=Non
     for kmap, rows, wait in ((interior, plan.interior_rows, False), (boundary, plan.boundary_rows, True)):
         if wait:
             main.wait_event(arrived)
-        sparse_conv_fused(local, weight, kmap, len(rows), epilogue=ConvEpilogue(ep.scale, ep.shift, None, ep.relu, rows, out))
+        sparse_conv_fused(local, weight, kmap, len(rows), split_k=1,
+                          epilogue=ConvEpilogue(ep.scale, ep.shift, None, ep.relu, rows, out))
     return out

@@ -93,7 +93,7 @@ def measure(coords: torch.Tensor, channels: int, dtype: torch.dtype, iters: int,
     from ..geometry.coords.search.search_results import IntSearchResult
     if plan.kernel_map is None:
         plan.kernel_map = IntSearchResult.from_neighbor_table(plan.nbr_local, plan.num_local, None, None)
-    ms_conv = timed(lambda: sparse_conv_fused(local, w, plan.kernel_map, plan.num_owned))
+    ms_conv = timed(lambda: sparse_conv_fused(local, w, plan.kernel_map, plan.num_owned, split_k=1))
     halo = torch.tensor([plan.num_halo, len(plan.boundary_rows) if plan.boundary_rows is not None else 0],
                         device=dev, dtype=torch.float64)
     if world > 1:
@@ -115,7 +115,7 @@ def measure(coords: torch.Tensor, channels: int, dtype: torch.dtype, iters: int,
             outs = [result]
         if rank == 0:
             km = generate_kernel_map(gc, gc, (1, 1, 1), (3, 3, 3))
-            full = sparse_conv_fused(_features(0, n, c, dtype, dev), w, km, n)
+            full = sparse_conv_fused(_features(0, n, c, dtype, dev), w, km, n, split_k=1)
             res["max_abs_diff_vs_single_gpu"] = float((full.float() - torch.cat(outs, 0).float()).abs().max())
     return res
 
