@@ -85,10 +85,15 @@ int wcn_hash_table_bytes(int64_t capacity, int64_t* bytes);
 /* Clear the table and insert keys[n,4]; the value of a key is its row index (the smallest
  * one when a key occurs more than once).  stride = {sx,sy,sz} floor-divides x,y,z before
  * insertion ({1,1,1} or NULL: keys as given).  Needs n <= capacity.
+ * skip_if (device int32, may be NULL): when it holds a non-zero value at the time the kernels run,
+ * they do nothing and the table is left unbuilt — for a table that only backs up a brick table
+ * (pass wcn_brick_usable_flag(brick_table), built earlier on the same stream): it is filled exactly
+ * when wcn_kmap_search_bricks will need it.  A caller that later wants to probe the table itself
+ * builds it again with skip_if = NULL.
  * Replaces prepare_key_value_pairs_kernel + insert_kernel_{fnv1a,city,murmur}
  * (warpconvnet/csrc/hashmap_kernels.cu:182-234, 258-270). */
 int wcn_hash_build(const int32_t* keys, int64_t n, const int32_t* stride, void* table,
-                   int64_t capacity, int hash_method, int32_t* dev_status, void* stream);
+                   int64_t capacity, int hash_method, const int32_t* skip_if, int32_t* dev_status, void* stream);
 
 /* results[i] = value of queries[i] in the table, or -1.
  * Replaces search_kernel_{fnv1a,city,murmur} (warpconvnet/csrc/hashmap_kernels.cu:237-301). */
@@ -233,6 +238,11 @@ int wcn_brick_table_bytes(int64_t n, int64_t* bytes);
  * itself is the reference's (warpconvnet/geometry/types/voxels.py:255-267,
  * warpconvnet/csrc/morton_code.cu:15-22). */
 int wcn_brick_build(const int32_t* keys, int64_t n, const int32_t* origin, void* table, void* stream);
+
+/* Device address of the word of a brick table that is non-zero when the table is usable (valid
+ * after wcn_brick_build has run on the stream); what wcn_hash_build takes as skip_if.  Host-only,
+ * launches nothing.  No counterpart in the reference. */
+const int32_t* wcn_brick_usable_flag(const void* brick_table);
 
 /* wcn_kmap_search (same nbr[k*M + m], same offset order and centre rule, dilation 1) answered
  * from a brick table: one thread per query fetches the at most 2x2x2 brick entries its window

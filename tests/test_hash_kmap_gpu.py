@@ -357,12 +357,47 @@ def test_brick_table_falls_back_when_rows_are_not_brick_ordered():
         ht = TorchHashTable.from_keys(c_dev)
         bt = BrickTable(c_dev, origin, ht)
         assert not bt.header()["valid"]
+        want = km.kernel_map_found(rows, rows, (1, 1, 1), (3, 3, 3))
         res = generate_kernel_map(c_dev, c_dev, (1, 1, 1), (3, 3, 3), hashtable=ht, bricks=bt)
-        assert np.array_equal(res.neighbor_table(len(rows)).cpu().numpy(),
-                              km.kernel_map_found(rows, rows, (1, 1, 1), (3, 3, 3)))
+        assert np.array_equal(res.neighbor_table(len(rows)).cpu().numpy(), want)
+        # a stand-by voxel table (insert kernels that only work when the bricks are unusable) was filled
+        lone = BrickTable(c_dev, origin)
+        res = generate_kernel_map(c_dev, c_dev, (1, 1, 1), (3, 3, 3), hashtable=lone.hashtable, bricks=lone)
+        assert np.array_equal(res.neighbor_table(len(rows)).cpu().numpy(), want)
     # a sorted set about its own corner is usable whatever the corner's parity
     own = srt.batch_indexed_coordinates.contiguous()
     assert BrickTable(own, srt.morton_origin, srt.hashmap).header()["valid"]
+    check_device_status(DEV)
+
+
+def test_standby_voxel_table_is_filled_when_something_probes_it():
+    """With usable bricks the voxel table behind them is left unbuilt (its buffer is poisoned here to
+    make that visible); a direct search, a dilated map and a custom-centred map fill it first."""
+    from warpconvnet_b200.geometry.coords.search.brick_table import BrickTable
+    xyz = synthetic.room_scene(15000, 0.02, 78, "raster_crop")
+    coords = np.concatenate([np.zeros((len(xyz), 1), np.int32), xyz], 1)
+    srt = _sorted_voxels(coords, [0, len(coords)]).batched_coordinates
+    own = srt.batch_indexed_coordinates.contiguous()
+    rows = own.cpu().numpy()
+    for probe in ("map", "search", "dilated"):
+        bt = BrickTable(own, srt.morton_origin)
+        ht = bt.hashtable
+        assert bt.header()["valid"] and ht._standby
+        ht._table.fill_(0x5A)  # whatever the skipped kernels left behind must not matter
+        if probe == "map":
+            res = generate_kernel_map(own, own, (1, 1, 1), (3, 3, 3), hashtable=ht, bricks=bt)
+            assert ht._standby  # still not needed
+            got, want = res.neighbor_table(len(rows)).cpu().numpy(), km.kernel_map_found(rows, rows, (1, 1, 1), (3, 3, 3))
+        elif probe == "search":
+            got, want = ht.search(own).cpu().numpy(), np.arange(len(rows), dtype=np.int32)
+        else:
+            res = generate_kernel_map(own, own, (1, 1, 1), (3, 3, 3), kernel_dilation=(2, 2, 2), hashtable=ht, bricks=bt)
+            got = res.neighbor_table(len(rows)).cpu().numpy()
+            want = km.kernel_map_found(rows, rows, (1, 1, 1), (3, 3, 3), kernel_dilation=(2, 2, 2))
+        assert np.array_equal(got, want), probe
+        assert ht._standby == (probe == "map")
+    # IntCoords hands out the pair: the table of sorted coordinates is the stand-by of their bricks
+    assert srt.hashmap is srt.bricks.hashtable
     check_device_status(DEV)
 
 

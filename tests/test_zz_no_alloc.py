@@ -28,7 +28,7 @@ def _build_table(coords):
     n = coords.shape[0]
     cap = max(16, 2 * n)
     table = torch.empty(_native.query_bytes("wcn_hash_table_bytes", cap), dtype=torch.uint8, device=DEV)
-    _native.check(_native.lib().wcn_hash_build(coords.data_ptr(), n, None, table.data_ptr(), cap, 1,
+    _native.check(_native.lib().wcn_hash_build(coords.data_ptr(), n, None, table.data_ptr(), cap, 1, None,
                                                _native.device_status(DEV).data_ptr(), _native.stream_ptr(torch.device(DEV))))
     return table, cap
 

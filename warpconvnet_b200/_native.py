@@ -27,7 +27,7 @@ _p_i64 = ctypes.POINTER(ctypes.c_int64)
 SIGNATURES = {
     "wcn_version": [],
     "wcn_hash_table_bytes": [_c_i64, _p_i64],
-    "wcn_hash_build": [_c_vp, _c_i64, _c_vp, _c_vp, _c_i64, _c_i32, _c_vp, _c_vp],
+    "wcn_hash_build": [_c_vp, _c_i64, _c_vp, _c_vp, _c_i64, _c_i32, _c_vp, _c_vp, _c_vp],
     "wcn_hash_search": [_c_vp, _c_i64, _c_i32, _c_vp, _c_i64, _c_vp, _c_vp],
     "wcn_unique_workspace_bytes": [_c_i64, _p_i64],
     "wcn_unique_mark": [_c_vp, _c_i64, _c_vp, _c_vp, _c_i64, _c_i32, _c_vp, _c_vp, _c_vp],
@@ -122,6 +122,8 @@ def lib():
             fn.restype = ctypes.c_int
         handle.wcn_status_string.argtypes = [ctypes.c_int]
         handle.wcn_status_string.restype = ctypes.c_char_p
+        handle.wcn_brick_usable_flag.argtypes = [ctypes.c_void_p]
+        handle.wcn_brick_usable_flag.restype = ctypes.c_void_p
         _lib = _CountingLib(handle)
     return _lib
 

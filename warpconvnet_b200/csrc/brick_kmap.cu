@@ -172,14 +172,17 @@ __device__ __forceinline__ void brick_lookup(const BrickSlot* __restrict__ slots
 // One thread per output row: the window of the row (kx x ky x kz positions, each axis at most four
 // wide, dilation 1) lies in at most 2 x 2 x 2 bricks; their entries are fetched once and every
 // offset is answered from them.  nbr[k * M + m] as wcn_kmap_search writes it.
-template <int METHOD>
+// KS: the window's width when it is the same along the three axes and known at compile time (2 or
+// 3: the loops unroll and the positions inside a brick become constants), 0: kx, ky, kz as given.
+template <int METHOD, int KS>
 __global__ void __launch_bounds__(kBrickThreads)
 kmap_search_bricks_kernel(const BrickHeader* __restrict__ hdr, const BrickSlot* __restrict__ slots,
                           const int4* __restrict__ tkeys, const int* __restrict__ tvals, uint32_t vcap,
-                          const int32_t* __restrict__ queries, int64_t M, int sx, int sy, int sz, int kx, int ky,
-                          int kz, int32_t* __restrict__ nbr) {
+                          const int32_t* __restrict__ queries, int64_t M, int sx, int sy, int sz, int kx_, int ky_,
+                          int kz_, int32_t* __restrict__ nbr) {
   __shared__ unsigned long long s_mask[8][kBrickThreads];
   __shared__ int s_base[8][kBrickThreads];
+  const int kx = KS ? KS : kx_, ky = KS ? KS : ky_, kz = KS ? KS : kz_;
   const int64_t m = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (m >= M) return;
   const int4 q = __ldg(reinterpret_cast<const int4*>(queries) + m);
@@ -208,17 +211,23 @@ kmap_search_bricks_kernel(const BrickHeader* __restrict__ hdr, const BrickSlot* 
     s_mask[t][threadIdx.x] = mk;
     s_base[t][threadIdx.x] = bs;
   }
+  int32_t* dst = nbr + m;  // offsets in the order (i, j, l), M apart
+#pragma unroll
   for (int i = 0; i < kx; ++i) {
     const int x = rx + i, tx = (x >> 2) - bx0;
+    const uint32_t px = brick_pos(x & 3, 0, 0);
+#pragma unroll
     for (int j = 0; j < ky; ++j) {
-      const int y = ry + j, ty = (y >> 2) - by0;
-      for (int l = 0; l < kz; ++l) {
-        const int z = rz + l, t = tx | (ty << 1) | (((z >> 2) - bz0) << 2);
+      const int y = ry + j, txy = tx | (((y >> 2) - by0) << 1);
+      const uint32_t pxy = px | brick_pos(0, y & 3, 0);
+#pragma unroll
+      for (int l = 0; l < kz; ++l, dst += M) {
+        const int z = rz + l, t = txy | (((z >> 2) - bz0) << 2);
         const unsigned long long mk = s_mask[t][threadIdx.x];
-        const uint32_t p = brick_pos(x & 3, y & 3, z & 3);
+        const uint32_t p = pxy | brick_pos(0, 0, z & 3);
         int found = -1;
         if ((mk >> p) & 1ull) found = s_base[t][threadIdx.x] + __popcll(mk & ((1ull << p) - 1ull));
-        nbr[(int64_t)((i * ky + j) * kz + l) * M + m] = found;
+        *dst = found;
       }
     }
   }
@@ -227,6 +236,11 @@ kmap_search_bricks_kernel(const BrickHeader* __restrict__ hdr, const BrickSlot* 
 inline unsigned brick_grid(int64_t n) { return (unsigned)((n + kBrickThreads - 1) / kBrickThreads); }
 
 }  // namespace
+
+// Device address of the table's "usable" word, for wcn_hash_build's skip_if argument.
+extern "C" const int32_t* wcn_brick_usable_flag(const void* brick_table) {
+  return brick_table ? &reinterpret_cast<const BrickHeader*>(brick_table)->valid : nullptr;
+}
 
 extern "C" int wcn_brick_table_bytes(int64_t n, int64_t* bytes) {
   if (n < 0 || !bytes) return WCN_ERR_INVALID_PARAMETERS;
@@ -267,10 +281,15 @@ extern "C" int wcn_kmap_search_bricks(const void* brick_table, const void* table
   const int4* tkeys = reinterpret_cast<const int4*>(table);
   const int* tvals = reinterpret_cast<const int*>(tkeys + capacity);
   cudaStream_t st = wcn_stream(stream);
+  const int ks = (kx == ky && ky == kz && (kx == 2 || kx == 3)) ? kx : 0;
+#define WCN_BRICK_LAUNCH(HM, KS)                                                                                    \
+  kmap_search_bricks_kernel<HM, KS><<<brick_grid(num_queries), kBrickThreads, 0, st>>>(                             \
+      hdr, slots, tkeys, tvals, (uint32_t)capacity, queries, num_queries, sx, sy, sz, kx, ky, kz, nbr)
 #define WCN_BRICK_CASE(HM)                                                                                          \
   case HM:                                                                                                          \
-    kmap_search_bricks_kernel<HM><<<brick_grid(num_queries), kBrickThreads, 0, st>>>(                               \
-        hdr, slots, tkeys, tvals, (uint32_t)capacity, queries, num_queries, sx, sy, sz, kx, ky, kz, nbr);           \
+    if (ks == 3) WCN_BRICK_LAUNCH(HM, 3);                                                                           \
+    else if (ks == 2) WCN_BRICK_LAUNCH(HM, 2);                                                                      \
+    else WCN_BRICK_LAUNCH(HM, 0);                                                                                   \
     break;
   switch (hash_method) {
     WCN_BRICK_CASE(WCN_HASH_FNV1A)
@@ -279,6 +298,7 @@ extern "C" int wcn_kmap_search_bricks(const void* brick_table, const void* table
     default: return WCN_ERR_INVALID_PARAMETERS;
   }
 #undef WCN_BRICK_CASE
+#undef WCN_BRICK_LAUNCH
   WCN_CHECK_LAUNCH();
   return WCN_OK;
 }

@@ -192,11 +192,13 @@ int launch_narrow(const void* feats, const void* weight, const int32_t* nbr, con
 // ------------------------------------------------------------------ narrow outputs
 //
 // Layers with at most 32 output channels that the tensor-core kernel does not take (a
-// 96 -> 20 classification head): one thread owns one output row, reads its input rows with
-// 16-byte loads, keeps all outputs in registers and takes the weights (fp32, padded to NP
-// columns) from shared memory, where every lane reads the same address.  Accumulation order
+// 96 -> 20 classification head): one thread owns ROWS consecutive output rows, reads their input
+// rows with 16-byte loads, keeps all outputs in registers and takes the weights (fp32, padded to NP
+// columns) from shared memory, where every lane reads the same address.  A weight quad fetched
+// from shared memory feeds ROWS x 4 multiply-adds, which is what keeps the kernel off the
+// shared-memory pipe (with one row per thread it was bound by it).  Accumulation order per output
 // is the one of conv_simt_kernel.
-template <typename T, typename TO, int NP>
+template <typename T, typename TO, int NP, int ROWS>
 __global__ void __launch_bounds__(NT)
 conv_narrow_out_kernel(const T* __restrict__ feats, const T* __restrict__ weight, const int32_t* __restrict__ nbr,
                        const int32_t* __restrict__ out_rows, int64_t M, int K, int c_in, int c_out,
@@ -208,65 +210,86 @@ conv_narrow_out_kernel(const T* __restrict__ feats, const T* __restrict__ weight
     w_s[i] = n < c_out ? wcn_to_float<T>(weight[(int64_t)kc * c_out + n]) : 0.f;
   }
   __syncthreads();
-  const int64_t slot = (int64_t)blockIdx.x * NT + threadIdx.x;
-  if (slot >= M) return;
+  const int64_t slot0 = ((int64_t)blockIdx.x * NT + threadIdx.x) * ROWS;
+  if (slot0 >= M) return;
   constexpr int EPV = 16 / (int)sizeof(T);  // input elements per 16-byte load
-  float acc[NP];
+  float acc[ROWS][NP];
 #pragma unroll
-  for (int j = 0; j < NP; ++j) acc[j] = 0.f;
+  for (int r = 0; r < ROWS; ++r)
+#pragma unroll
+    for (int j = 0; j < NP; ++j) acc[r][j] = 0.f;
   for (int k = 0; k < K; ++k) {
-    const int src = __ldg(&nbr[(int64_t)k * M + slot]);
-    if (src < 0) continue;
-    if (src >= lay.num_in) {
-      wcn_report_bounds(lay.dev_status);
-      continue;
+    const uint4* x[ROWS];
+    bool any = false;
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) {
+      int src = slot0 + r < M ? __ldg(&nbr[(int64_t)k * M + slot0 + r]) : -1;
+      if (src >= lay.num_in) {
+        wcn_report_bounds(lay.dev_status);
+        src = -1;
+      }
+      x[r] = src >= 0 ? reinterpret_cast<const uint4*>(feats + (int64_t)src * lay.in_ld) : nullptr;
+      any = any || src >= 0;
     }
-    const uint4* x = reinterpret_cast<const uint4*>(feats + (int64_t)src * lay.in_ld);
+    if (!any) continue;
     const float* wk = w_s + (int64_t)k * c_in * NP;
     for (int c0 = 0; c0 < c_in; c0 += EPV) {
-      const uint4 raw = __ldg(x + c0 / EPV);
-      const T* xv = reinterpret_cast<const T*>(&raw);
+      uint4 raw[ROWS];
+#pragma unroll
+      for (int r = 0; r < ROWS; ++r) raw[r] = x[r] ? __ldg(x[r] + c0 / EPV) : make_uint4(0, 0, 0, 0);
 #pragma unroll
       for (int e = 0; e < EPV; ++e) {
-        const float xf = wcn_to_float<T>(xv[e]);
+        float xf[ROWS];
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) xf[r] = wcn_to_float<T>(reinterpret_cast<const T*>(&raw[r])[e]);
         const float4* w4 = reinterpret_cast<const float4*>(wk + (c0 + e) * NP);
 #pragma unroll
         for (int q = 0; q < NP / 4; ++q) {
           const float4 w = w4[q];
-          acc[4 * q + 0] = fmaf(xf, w.x, acc[4 * q + 0]);
-          acc[4 * q + 1] = fmaf(xf, w.y, acc[4 * q + 1]);
-          acc[4 * q + 2] = fmaf(xf, w.z, acc[4 * q + 2]);
-          acc[4 * q + 3] = fmaf(xf, w.w, acc[4 * q + 3]);
+#pragma unroll
+          for (int r = 0; r < ROWS; ++r) {
+            if (x[r]) {  // an absent neighbour adds nothing (and keeps -0.0 sums exactly as the row-wise kernel does)
+              acc[r][4 * q + 0] = fmaf(xf[r], w.x, acc[r][4 * q + 0]);
+              acc[r][4 * q + 1] = fmaf(xf[r], w.y, acc[r][4 * q + 1]);
+              acc[r][4 * q + 2] = fmaf(xf[r], w.z, acc[r][4 * q + 2]);
+              acc[r][4 * q + 3] = fmaf(xf[r], w.w, acc[r][4 * q + 3]);
+            }
+          }
         }
       }
     }
   }
-  const int64_t m = out_rows ? (int64_t)__ldg(&out_rows[slot]) : slot;
-  TO* orow = out + m * lay.out_ld;
-  const TO* rrow = residual ? residual + m * lay.res_ld : nullptr;
   constexpr int PER8 = (int)(8 / sizeof(TO));  // outputs per 8-byte store
   const bool wide = (c_out % PER8) == 0 && (lay.out_ld % PER8) == 0 &&
                     (reinterpret_cast<uintptr_t>(out) & 7) == 0;  // rows start 8-byte aligned
 #pragma unroll
-  for (int j0 = 0; j0 < NP; j0 += PER8) {
-    __align__(8) TO o[PER8];
+  for (int r = 0; r < ROWS; ++r) {
+    const int64_t slot = slot0 + r;
+    if (slot >= M) break;
+    const int64_t m = out_rows ? (int64_t)__ldg(&out_rows[slot]) : slot;
+    TO* orow = out + m * lay.out_ld;
+    const TO* rrow = residual ? residual + m * lay.res_ld : nullptr;
 #pragma unroll
-    for (int i = 0; i < PER8; ++i) {
-      const int j = j0 + i;
-      float y = acc[j];
-      if (j < c_out) {
-        y = wcn_affine(y, scale, shift, j);
-        if (rrow) y = __fadd_rn(y, wcn_to_float<TO>(rrow[j]));
-        if (relu) y = fmaxf(y, 0.f);
+    for (int j0 = 0; j0 < NP; j0 += PER8) {
+      __align__(8) TO o[PER8];
+#pragma unroll
+      for (int i = 0; i < PER8; ++i) {
+        const int j = j0 + i;
+        float y = acc[r][j];
+        if (j < c_out) {
+          y = wcn_affine(y, scale, shift, j);
+          if (rrow) y = __fadd_rn(y, wcn_to_float<TO>(rrow[j]));
+          if (relu) y = fmaxf(y, 0.f);
+        }
+        o[i] = wcn_from_float<TO>(y);
       }
-      o[i] = wcn_from_float<TO>(y);
-    }
-    if (wide) {
-      if (j0 < c_out) *reinterpret_cast<uint2*>(orow + j0) = *reinterpret_cast<const uint2*>(o);
-    } else {
+      if (wide) {
+        if (j0 < c_out) *reinterpret_cast<uint2*>(orow + j0) = *reinterpret_cast<const uint2*>(o);
+      } else {
 #pragma unroll
-      for (int i = 0; i < PER8; ++i)
-        if (j0 + i < c_out) orow[j0 + i] = o[i];
+        for (int i = 0; i < PER8; ++i)
+          if (j0 + i < c_out) orow[j0 + i] = o[i];
+      }
     }
   }
 }
@@ -275,14 +298,14 @@ template <typename T, typename TO>
 int launch_narrow_out(const void* feats, const void* weight, const int32_t* nbr, const int32_t* out_rows, int64_t M,
                       int K, int c_in, int c_out, const float* scale, const float* shift, const void* residual,
                       int relu, void* out, const RowLayout& lay, cudaStream_t st) {
-  const unsigned blocks = (unsigned)((M + NT - 1) / NT);
-#define WCN_NOUT(NPV) \
-  conv_narrow_out_kernel<T, TO, NPV><<<blocks, NT, 0, st>>>((const T*)feats, (const T*)weight, nbr, out_rows, M, K, c_in, \
-                                                            c_out, scale, shift, (const TO*)residual, relu, (TO*)out, lay)
-  if (c_out <= 8) WCN_NOUT(8);
-  else if (c_out <= 16) WCN_NOUT(16);
-  else if (c_out <= 24) WCN_NOUT(24);
-  else WCN_NOUT(32);
+#define WCN_NOUT(NPV, ROWSV)                                                                                        \
+  conv_narrow_out_kernel<T, TO, NPV, ROWSV><<<(unsigned)((M + (int64_t)NT * ROWSV - 1) / ((int64_t)NT * ROWSV)), NT, 0, st>>>( \
+      (const T*)feats, (const T*)weight, nbr, out_rows, M, K, c_in, c_out, scale, shift, (const TO*)residual, relu,   \
+      (TO*)out, lay)
+  if (c_out <= 8) WCN_NOUT(8, 4);
+  else if (c_out <= 16) WCN_NOUT(16, 4);
+  else if (c_out <= 24) WCN_NOUT(24, 4);
+  else WCN_NOUT(32, 2);
 #undef WCN_NOUT
   return cudaGetLastError() == cudaSuccess ? WCN_OK : WCN_ERR_EXECUTION;
 }

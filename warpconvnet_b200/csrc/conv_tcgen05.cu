@@ -840,7 +840,7 @@ __global__ void bounded_wait_probe_kernel(long long limit_cycles, int32_t* dev_s
   __syncthreads();
   if (threadIdx.x == 0) mbar_arrive(smem_u32(&probe_bar));
   if (threadIdx.x == 32) {
-    const bool done = mbar_wait(smem_u32(&probe_bar), 0, dev_status, limit_cycles);
+    const bool done = mbar_wait_limit(smem_u32(&probe_bar), 0, dev_status, limit_cycles);
     if (gave_up) *gave_up = done ? 0 : 1;
   }
 }

@@ -50,7 +50,8 @@ __device__ __forceinline__ int4 load_key(const int32_t* __restrict__ keys, int64
 
 // The table buffer ends with one flag word behind the values: tvals[cap] != 0 when a key was
 // inserted more than once.
-__global__ void hash_clear_kernel(int4* tkeys, int* tvals, int64_t cap) {
+__global__ void hash_clear_kernel(int4* tkeys, int* tvals, int64_t cap, const int32_t* __restrict__ skip_if) {
+  if (skip_if && __ldg(skip_if) != 0) return;  // the caller's brick table is usable: this table will not be probed
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i < cap) {
     tkeys[i] = make_int4(WCN_EMPTY_BATCH, 0, 0, 0);
@@ -61,7 +62,9 @@ __global__ void hash_clear_kernel(int4* tkeys, int* tvals, int64_t cap) {
 
 template <int METHOD>
 __global__ void hash_insert_kernel(const int32_t* __restrict__ keys, int64_t n, int sx, int sy, int sz,
-                                   int4* tkeys, int* tvals, uint32_t cap, int32_t* dev_status) {
+                                   int4* tkeys, int* tvals, uint32_t cap, int32_t* dev_status,
+                                   const int32_t* __restrict__ skip_if) {
+  if (skip_if && __ldg(skip_if) != 0) return;
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   const int4 key = load_key(keys, i, sx, sy, sz);
@@ -537,7 +540,8 @@ static inline bool parse_stride(const int32_t* stride, int* sx, int* sy, int* sz
 }
 
 extern "C" int wcn_hash_build(const int32_t* keys, int64_t n, const int32_t* stride, void* table,
-                              int64_t capacity, int hash_method, int32_t* dev_status, void* stream) {
+                              int64_t capacity, int hash_method, const int32_t* skip_if, int32_t* dev_status,
+                              void* stream) {
   int sx, sy, sz;
   if (!table || capacity <= 0 || capacity > 0x7FFFFFFFll || n < 0 || n > capacity || (n > 0 && !keys) ||
       !parse_stride(stride, &sx, &sy, &sz))
@@ -547,10 +551,10 @@ extern "C" int wcn_hash_build(const int32_t* keys, int64_t n, const int32_t* str
   cudaStream_t st = wcn_stream(stream);
   int4* tkeys = reinterpret_cast<int4*>(table);
   int* tvals = reinterpret_cast<int*>(tkeys + capacity);
-  hash_clear_kernel<<<grid_for(capacity), kThreads, 0, st>>>(tkeys, tvals, capacity);
+  hash_clear_kernel<<<grid_for(capacity), kThreads, 0, st>>>(tkeys, tvals, capacity, skip_if);
   if (n > 0) {
     WCN_DISPATCH_HASH(hash_method, (hash_insert_kernel<HM><<<grid_for(n), kThreads, 0, st>>>(
-                                       keys, n, sx, sy, sz, tkeys, tvals, (uint32_t)capacity, dev_status)));
+                                       keys, n, sx, sy, sz, tkeys, tvals, (uint32_t)capacity, dev_status, skip_if)));
   }
   WCN_CHECK_LAUNCH();
   return WCN_OK;

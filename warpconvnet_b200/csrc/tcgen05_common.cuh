@@ -40,11 +40,12 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // out.  The status word lives in global memory and is looked at about once per millisecond of
 // waiting.  An expired wait overrides whatever the word held (a skipped out-of-range index is
 // reported with a compare-and-swap that never overrides anything, see wcn_report_bounds).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int32_t* dev_status,
-                                          long long limit_cycles = kWaitCycles) {
+template <bool CUSTOM_LIMIT>
+__device__ __forceinline__ bool mbar_wait_impl(uint32_t bar, uint32_t parity, int32_t* dev_status, long long limit_cycles) {
   if (mbar_try_wait(bar, parity)) return true;
+  const long long limit = CUSTOM_LIMIT ? limit_cycles : kWaitCycles;
+  const long long poll = (CUSTOM_LIMIT && limit_cycles < kStatusPollCycles) ? limit_cycles : kStatusPollCycles;
   const long long t0 = clock64();
-  const long long poll = limit_cycles < kStatusPollCycles ? limit_cycles : kStatusPollCycles;
   long long next_check = t0 + poll;
   for (;;) {
 #pragma unroll 1
@@ -53,13 +54,21 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int32_t
     const long long now = clock64();
     if (now > next_check) {
       if (*(volatile int32_t*)dev_status == (int)WCN_ERR_WAIT_EXPIRED) return false;
-      if (now - t0 > limit_cycles) {
+      if (now - t0 > limit) {
         atomicExch(dev_status, (int)WCN_ERR_WAIT_EXPIRED);
         return false;
       }
       next_check = now + poll;
     }
   }
+}
+// The wait every kernel role uses: the limit is a compile-time constant (about two seconds).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int32_t* dev_status) {
+  return mbar_wait_impl<false>(bar, parity, dev_status, 0);
+}
+// The same wait with a caller-chosen limit (the self test of the expiry path).
+__device__ __forceinline__ bool mbar_wait_limit(uint32_t bar, uint32_t parity, int32_t* dev_status, long long limit_cycles) {
+  return mbar_wait_impl<true>(bar, parity, dev_status, limit_cycles);
 }
 
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {

@@ -93,8 +93,8 @@ def measure(scenes: int = 4, voxels: int = 250000, voxel_size: float = 0.02, mod
         if not sort:
             return generate_kernel_map(inc, outc, stride, ks)
         from ..geometry.coords.search.brick_table import BrickTable
-        ht = TorchHashTable.from_keys(inc)
-        return generate_kernel_map(inc, outc, stride, ks, hashtable=ht, bricks=BrickTable(inc, origin, ht))
+        bt = BrickTable(inc, origin)  # with its stand-by voxel table: filled only if the bricks are unusable
+        return generate_kernel_map(inc, outc, stride, ks, hashtable=bt.hashtable, bricks=bt)
 
     def full_map(inc, outc, stride, ks):
         km = build_map(inc, outc, stride, ks)

@@ -72,7 +72,10 @@ class IntCoords(Coords):
     def hashmap(self) -> TorchHashTable:
         """Hash table of the batch-indexed int32 coordinates; built once per set of rows."""
         if self._shared.get("hashmap") is None:
-            self._shared["hashmap"] = TorchHashTable.from_keys(self.batch_indexed_coordinates.to(torch.int32))
+            if self._shared.get("morton_origin") is not None and self.batched_tensor.shape[1] == 3:
+                self._shared["hashmap"] = self.bricks.hashtable  # a stand-by table, filled only if the bricks are unusable
+            else:
+                self._shared["hashmap"] = TorchHashTable.from_keys(self.batch_indexed_coordinates.to(torch.int32))
         return self._shared["hashmap"]
 
     @property
@@ -94,7 +97,8 @@ class IntCoords(Coords):
         if self._shared.get("bricks") is None:
             from .search.brick_table import BrickTable
             self._shared["bricks"] = BrickTable(self.batch_indexed_coordinates.to(torch.int32),
-                                                self._shared["morton_origin"], self.hashmap)
+                                                self._shared["morton_origin"], self._shared.get("hashmap"))
+            self._shared["hashmap"] = self._shared["bricks"].hashtable
         return self._shared["bricks"]
 
     @property

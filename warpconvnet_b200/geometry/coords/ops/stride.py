@@ -46,7 +46,7 @@ def unique_strided_rows(bcoords: Tensor, stride: Tuple[int, int, int] = (1, 1, 1
     strd = (ctypes.c_int32 * 3)(*[int(s) for s in stride])
     sp = ctypes.addressof(strd)
     st = stream_ptr(dev)
-    check(lib().wcn_hash_build(ptr(c), n, sp, ptr(table), cap, hash_method.value, ptr(device_status(dev)), st),
+    check(lib().wcn_hash_build(ptr(c), n, sp, ptr(table), cap, hash_method.value, None, ptr(device_status(dev)), st),
           "wcn_hash_build")
     ws = torch.empty(query_bytes("wcn_unique_workspace_bytes", n), dtype=torch.uint8, device=dev)
     count = torch.empty(1, dtype=torch.int64, device=dev)
@@ -110,7 +110,7 @@ def strided_pyramid(bcoords: Tensor, total_strides, in_offsets: Tensor, hash_met
         strd = (ctypes.c_int32 * 3)(*[int(s) for s in stride])
         sp = ctypes.addressof(strd)
         table = torch.empty(table_bytes, dtype=torch.uint8, device=dev)
-        check(lib().wcn_hash_build(ptr(c), n, sp, ptr(table), cap, hash_method.value, ptr(device_status(dev)), st),
+        check(lib().wcn_hash_build(ptr(c), n, sp, ptr(table), cap, hash_method.value, None, ptr(device_status(dev)), st),
               "wcn_hash_build")
         ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
         count = torch.empty(1, dtype=torch.int64, device=dev)

@@ -17,16 +17,19 @@ import torch
 from torch import Tensor
 
 from ...._native import check, lib, ptr, query_bytes, stream_ptr
-from .torch_hashmap import TorchHashTable
+from .torch_hashmap import HashMethod, TorchHashTable
 
 
 class BrickTable:
-    def __init__(self, keys: Tensor, origin: Optional[Tensor], hashtable: TorchHashTable):
-        """``keys``: int32 ``[N, 4]`` rows (batch, x, y, z) on a CUDA device, the rows ``hashtable`` was
-        built from; ``origin``: int32 ``[3]`` on the same device, the corner the Morton codes were
-        taken from (bricks are aligned to it), or None for the coordinate origin."""
+    def __init__(self, keys: Tensor, origin: Optional[Tensor], hashtable: Optional[TorchHashTable] = None,
+                 hash_method: HashMethod = HashMethod.CITY):
+        """``keys``: int32 ``[N, 4]`` rows (batch, x, y, z) on a CUDA device; ``origin``: int32 ``[3]`` on
+        the same device, the corner the Morton codes were taken from (bricks are aligned to it), or
+        None for the coordinate origin.  ``hashtable``: a voxel table already built over ``keys``; without
+        one, a stand-by table is made whose insert kernels only do work when this brick table turns
+        out unusable (``TorchHashTable.insert(standby_for=...)``)."""
         assert keys.is_cuda and keys.dtype == torch.int32 and keys.ndim == 2 and keys.shape[1] == 4
-        assert len(hashtable.vector_keys) == keys.shape[0], "hashtable was built over other keys"
+        assert hashtable is None or len(hashtable.vector_keys) == keys.shape[0], "hashtable was built over other keys"
         keys = keys.contiguous()
         dev = keys.device
         if origin is not None:
@@ -36,6 +39,8 @@ class BrickTable:
         self._table = torch.empty(query_bytes("wcn_brick_table_bytes", keys.shape[0]), dtype=torch.uint8, device=dev)
         check(lib().wcn_brick_build(ptr(keys), keys.shape[0], ptr(origin), ptr(self._table), stream_ptr(dev)),
               "wcn_brick_build")
+        if hashtable is None:
+            self.hashtable = TorchHashTable.from_keys(keys, hash_method=hash_method, standby_for=self)
 
     @property
     def device(self) -> torch.device:

@@ -94,10 +94,12 @@ def _kernel_map_from_size(hashtable: TorchHashTable, batched_query_coords: Tenso
     elif (self_map and ctr is None and not skip_symmetric_kernel_map and all(k % 2 == 1 for k in kernel_sizes)
             and all(int(s) == 1 for s in (query_stride or (1, 1, 1)))):
         assert M == len(hashtable.vector_keys), "self_map needs the table's own rows as queries"
+        hashtable.ensure_built()
         check(lib().wcn_kmap_search_self(ptr(hashtable._table), hashtable.capacity, hashtable.hash_method.value,
                                          ptr(q), M, ctypes.addressof(ksz), ctypes.addressof(dil), ptr(nbr),
                                          stream_ptr(dev)), "wcn_kmap_search_self")
     else:
+        hashtable.ensure_built()
         check(lib().wcn_kmap_search_dilated(ptr(hashtable._table), hashtable.capacity, hashtable.hash_method.value,
                                             ptr(q), M, ctypes.addressof(strd), ctypes.addressof(ksz),
                                             ctypes.addressof(dil), ctypes.addressof(ctr) if ctr is not None else None,

@@ -50,6 +50,7 @@ class TorchHashTable:
         self._table = None        # uint8 buffer of wcn_hash_table_bytes(capacity)
         self._vector_keys = None  # [N, 4] int32 as inserted
         self._key_dim = -1
+        self._standby = False  # True: built only if a brick table was unusable (decided on the device)
 
     # -- properties
     @property
@@ -75,7 +76,12 @@ class TorchHashTable:
         return self._vector_keys
 
     # -- build
-    def insert(self, vec_keys: Tensor, threads_per_block: int = 256):
+    def insert(self, vec_keys: Tensor, threads_per_block: int = 256, standby_for=None):
+        """``standby_for`` (an addition to the reference signature): a :class:`BrickTable` of the same
+        keys, built earlier on this stream.  The insert kernels then return at once when that table is
+        usable, and this table is filled for real the first time something probes it directly
+        (:meth:`search`, a dilated or custom-centred kernel map); a kernel map through the brick
+        table needs it only when the brick table is unusable, which is exactly when it was filled."""
         if not isinstance(vec_keys, Tensor):
             raise TypeError(f"Input vec_keys must be a PyTorch Tensor, got {type(vec_keys)}")
         if not vec_keys.is_cuda:
@@ -95,13 +101,25 @@ class TorchHashTable:
         self._vector_keys = vec_keys
         nbytes = query_bytes("wcn_hash_table_bytes", self._capacity)
         self._table = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+        self._standby = standby_for is not None  # (no reference to the brick table: it refers to this one)
+        skip_if = lib().wcn_brick_usable_flag(ptr(standby_for._table)) if standby_for is not None else None
         check(lib().wcn_hash_build(ptr(vec_keys), num_keys, None, ptr(self._table), self._capacity,
-                                   self._hash_method_enum.value, ptr(device_status(dev)), stream_ptr(dev)),
+                                   self._hash_method_enum.value, skip_if, ptr(device_status(dev)), stream_ptr(dev)),
               "wcn_hash_build")
+
+    def ensure_built(self):
+        """Fill a table whose build was left to the device's decision (``standby_for``).  Enqueues the
+        unconditional build once; no host synchronisation."""
+        if self._standby:
+            self._standby = False
+            dev = self._table.device
+            check(lib().wcn_hash_build(ptr(self._vector_keys), len(self._vector_keys), None, ptr(self._table),
+                                       self._capacity, self._hash_method_enum.value, None, ptr(device_status(dev)),
+                                       stream_ptr(dev)), "wcn_hash_build")
 
     @classmethod
     def from_keys(cls, vec_keys: Tensor, hash_method: HashMethod = HashMethod.CITY,
-                  device: Union[str, torch.device, None] = None):
+                  device: Union[str, torch.device, None] = None, standby_for=None):
         if not isinstance(vec_keys, Tensor):
             vec_keys = torch.as_tensor(vec_keys)
         if device is not None and vec_keys.device != torch.device(device):
@@ -110,7 +128,7 @@ class TorchHashTable:
             raise ValueError(f"Input vec_keys for from_keys must be 2D, got {vec_keys.ndim} dimensions")
         # capacity rule of the reference (torch_hashmap.py:218-219)
         obj = cls(capacity=max(16, int(len(vec_keys) * 2)), hash_method=hash_method, device=vec_keys.device)
-        obj.insert(vec_keys)
+        obj.insert(vec_keys, standby_for=standby_for)
         return obj
 
     # -- query
@@ -131,6 +149,7 @@ class TorchHashTable:
             raise ValueError(f"Search keys dimension ({search_keys.shape[1]}) must match "
                              f"inserted keys dimension ({self._key_dim})")
         search_keys = _as_int32_keys(search_keys, "search_keys")
+        self.ensure_built()
         results = torch.empty(len(search_keys), dtype=torch.int32, device=dev)
         check(lib().wcn_hash_search(ptr(self._table), self._capacity, self._hash_method_enum.value,
                                     ptr(search_keys), len(search_keys), ptr(results), stream_ptr(dev)),
