@@ -214,7 +214,7 @@ class ConvProfile:
     launching stream without host-induced gaps."""
 
     def __init__(self):
-        self.calls = []    # (callable, nbr tensor, c_in, c_out, kind) of the step being recorded
+        self.calls = []    # (callable, nbr tensor or (pairs, M, K), c_in, c_out, kind) of the step being recorded
         self.records = []  # (ms, pairs, M, K, c_in, c_out, kind) of replayed launches
         self._pairs = {}
 
@@ -230,6 +230,10 @@ class ConvProfile:
             evs.append((s, e))
         torch.cuda.synchronize()
         for (s, e), (fn, nbr, c_in, c_out, kind) in zip(evs, self.calls):
+            if isinstance(nbr, tuple):  # a layer run from the input side: one pair per output row
+                pairs, M, K = nbr
+                self.records.append((s.elapsed_time(e), pairs, M, K, c_in, c_out, kind))
+                continue
             key = nbr.data_ptr()
             if key not in self._pairs:
                 self._pairs[key] = int((nbr >= 0).sum().item())
@@ -277,12 +281,19 @@ class ConvProfile:
 
 
 def install_conv_profiler(profile):
-    """Wrap the two fused-convolution entries (the functional one and the launch record the network
+    """Wrap the fused-convolution entries (the functional one and the two launch records the network
     plan uses) so that each call of a step is recorded for replay."""
     import warpconvnet_b200.nn.functional.sparse_conv as F
     from warpconvnet_b200._native import query_bytes, dtype_code
     orig = F.sparse_conv_fused
     orig_launch = F.FusedConvLaunch.__call__
+    orig_rows = F.FusedRowsLaunch.__call__
+
+    def rows_launch(self, feats, dst_rows, num_out, residual=None, out=None):
+        res = orig_rows(self, feats, dst_rows, num_out, residual, out)
+        profile.calls.append((lambda: orig_rows(self, feats, dst_rows, num_out, residual, res),
+                              (num_out, num_out, self.K), self.c_in, self.c_out, "tcgen05"))
+        return res
 
     def wrapped(in_features, weight, kernel_map, num_out_coords, *rest, **kw):
         out = orig(in_features, weight, kernel_map, num_out_coords, *rest, **kw)
@@ -301,10 +312,12 @@ def install_conv_profiler(profile):
 
     F.sparse_conv_fused = wrapped
     F.FusedConvLaunch.__call__ = launch
+    F.FusedRowsLaunch.__call__ = rows_launch
 
     def restore():
         F.sparse_conv_fused = orig
         F.FusedConvLaunch.__call__ = orig_launch
+        F.FusedRowsLaunch.__call__ = orig_rows
     return restore
 
 
@@ -584,7 +597,7 @@ def run_gpu_arm(args):
             "traffic": (NCU_DRAM_BYTES_C96_500K * dominant["rows"] / 500000.0
                         if dominant and (dominant["c_in"], dominant["c_out"], dominant["offsets"]) == (96, 96, 27) else None),
             "traffic_of": "dominant shape, per launch", "peak_source": peak_src,
-            "kernel": "conv_tcgen05_kernel (all tensor-core convolution launches of a step)",
+            "kernel": "conv_tcgen05_kernel + conv_rows_tcgen05_kernel (all tensor-core convolution launches of a step)",
             "useful_flop_per_step": prof["tc_flop"] / prof_steps, "launches_per_step": prof["tc_launches"] / prof_steps,
             "avg_launch_ms": prof["tc_ms"] / max(prof["tc_launches"], 1),
             "conv_share_of_step": (prof["ms"] / prof_steps) / (ms / args.steps),

@@ -377,6 +377,26 @@ int wcn_conv_fwd(int algo, const void* feats, int64_t num_in, int64_t feats_ld, 
 int wcn_row_reduce(const void* feats, int64_t num_in, const int32_t* nbr, int64_t num_out, int32_t num_offsets,
                    int32_t channels, int dtype, int op, void* out, int32_t* dev_status, void* stream);
 
+/* Convolution in which every output row has exactly one (input row, kernel offset) pair, run from the
+ * INPUT side on the tensor cores: a 1x1x1 convolution (optionally writing through a row permutation)
+ * and a transposed convolution whose window equals its stride (2x2x2, stride 2).  For input row j and
+ * offset k, out[dst_rows[k * num_in + j], :] = epilogue(feats[j, :] @ weight[k]); entries < 0 name no
+ * output row.  dst_rows == NULL (num_offsets must be 1) means dst = j.  The caller guarantees that no
+ * output row is named twice (it would be written twice, last writer wins) — for the stride-2 case
+ * dst_rows is the [8, num_coarse] neighbour table of the matching strided convolution.
+ * Feature rows arrive through TMA tiles (16-byte aligned base and pitch), weights (packed by
+ * wcn_conv_pack_weight at width c_out_packed, a multiple of 16 >= c_out whose extra columns are zero)
+ * stay in shared memory; fp16 / bf16 features, c_in % 32 == 0, c_out_packed <= 256.
+ * The reference runs these layers through the same gather-GEMM-scatter as every other convolution
+ * (warpconvnet/nn/functional/sparse_conv.py:358-415 with the swapped kernel map of :1916-1945). */
+int wcn_conv_rows_supported(int32_t num_offsets, int32_t c_in, int32_t c_out_packed, int dtype, int out_dtype,
+                            int32_t* supported);
+int wcn_conv_rows_fwd(const void* feats, int64_t num_in, int64_t feats_ld, const void* packed_weight,
+                      const int32_t* dst_rows, int64_t num_out, int32_t num_offsets, int32_t c_in,
+                      int32_t c_out_packed, int32_t c_out, int dtype, const float* scale, const float* shift,
+                      const void* residual, int64_t residual_ld, int relu, void* out, int64_t out_ld,
+                      int out_dtype, int32_t* dev_status, void* stream);
+
 /* Weight gradient of the convolution above, accumulated into grad_weight[K, c_in, c_out] (fp32; the
  * caller zeroes it):
  *   grad_weight[k] += feats[nbr[k*M + m], :]^T (outer) grad_out[m, :]   over rows m with nbr >= 0

@@ -58,6 +58,9 @@ SIGNATURES = {
     "wcn_conv_fwd": [_c_i32, _c_vp, _c_i64, _c_i64, _c_vp, _c_vp, _c_vp, _c_vp, _c_i64, _c_i32, _c_i32, _c_i32, _c_i32,
                      _c_vp, _c_vp, _c_vp, _c_i64, _c_i32, _c_vp, _c_i64, _c_i32, _c_i32, _c_vp, _c_i64, _c_vp, _c_vp],
     "wcn_selftest_bounded_wait": [_c_i64, _c_vp, _c_vp, _c_vp],
+    "wcn_conv_rows_supported": [_c_i32, _c_i32, _c_i32, _c_i32, _c_i32, _c_vp],
+    "wcn_conv_rows_fwd": [_c_vp, _c_i64, _c_i64, _c_vp, _c_vp, _c_i64, _c_i32, _c_i32, _c_i32, _c_i32, _c_i32, _c_vp, _c_vp,
+                          _c_vp, _c_i64, _c_i32, _c_vp, _c_i64, _c_i32, _c_vp, _c_vp],
 }
 
 _lib = None
@@ -70,6 +73,7 @@ KERNELS_PER_CALL = {
     "wcn_kmap_tile_order": 3, "wcn_conv_wgrad": 1, "wcn_kmap_tile_masks": 1, "wcn_row_reduce": 1, "wcn_kmap_search_self": 1, "wcn_kmap_search_dilated": 1, "wcn_kmap_count": 1,
     "wcn_gather_rows": 1, "wcn_scatter_add_rows": 1, "wcn_conv_pack_weight": 1, "wcn_conv_fwd": 1,
     "wcn_selftest_bounded_wait": 1, "wcn_brick_build": 3, "wcn_kmap_search_bricks": 1,
+    "wcn_conv_rows_fwd": 1,
 }
 LAUNCH_COUNTS: Counter = Counter()
 

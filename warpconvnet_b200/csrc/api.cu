@@ -129,6 +129,36 @@ extern "C" int wcn_conv_fwd(int algo, const void* feats, int64_t num_in, int64_t
                            scale, shift, residual, residual_ld, relu, out, out_ld, out_dtype, dev_status, st);
 }
 
+bool wcn_conv_rows_shape_supported(int K, int c_in, int c_out_packed, int dtype, int out_dtype);
+int wcn_conv_rows_tcgen05_fwd(const void* feats, int64_t num_in, int64_t feats_ld, const void* packed,
+                              const int32_t* dst_rows, int64_t num_out, int K, int c_in, int c_out_packed, int c_out,
+                              int dtype, const float* scale, const float* shift, const void* residual,
+                              int64_t residual_ld, int relu, void* out, int64_t out_ld, int out_dtype,
+                              int32_t* dev_status, cudaStream_t st);
+
+extern "C" int wcn_conv_rows_supported(int32_t num_offsets, int32_t c_in, int32_t c_out_packed, int dtype, int out_dtype,
+                                       int32_t* supported) {
+  if (!supported) return WCN_ERR_INVALID_PARAMETERS;
+  *supported = wcn_conv_rows_shape_supported(num_offsets, c_in, c_out_packed, dtype, out_dtype) ? 1 : 0;
+  return WCN_OK;
+}
+
+extern "C" int wcn_conv_rows_fwd(const void* feats, int64_t num_in, int64_t feats_ld, const void* packed_weight,
+                                 const int32_t* dst_rows, int64_t num_out, int32_t num_offsets, int32_t c_in,
+                                 int32_t c_out_packed, int32_t c_out, int dtype, const float* scale, const float* shift,
+                                 const void* residual, int64_t residual_ld, int relu, void* out, int64_t out_ld,
+                                 int out_dtype, int32_t* dev_status, void* stream) {
+  if (num_in < 0 || num_out < 0 || num_offsets <= 0 || c_in <= 0 || c_out <= 0) return WCN_ERR_INVALID_PARAMETERS;
+  if (feats_ld == 0) feats_ld = c_in;
+  if (out_ld == 0) out_ld = c_out;
+  if (residual_ld == 0) residual_ld = c_out;
+  if (feats_ld < c_in || out_ld < c_out || residual_ld < c_out) return WCN_ERR_INVALID_PARAMETERS;
+  if (num_in == 0 || num_out == 0) return WCN_OK;
+  return wcn_conv_rows_tcgen05_fwd(feats, num_in, feats_ld, packed_weight, dst_rows, num_out, num_offsets, c_in,
+                                   c_out_packed, c_out, dtype, scale, shift, residual, residual_ld, relu, out, out_ld,
+                                   out_dtype, dev_status, wcn_stream(stream));
+}
+
 extern "C" int wcn_conv_wgrad(const void* feats, int64_t num_in, const void* grad_out, const int32_t* nbr,
                               const int32_t* out_rows, const uint32_t* tile_masks, int64_t num_out, int32_t num_offsets, int32_t c_in, int32_t c_out, int dtype,
                               float* grad_weight, int32_t* dev_status, void* stream) {

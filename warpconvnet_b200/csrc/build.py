@@ -8,7 +8,7 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 SOURCES = ["api.cu", "hash_kmap.cu", "brick_kmap.cu", "conv_explicit.cu", "conv_simt.cu", "conv_tcgen05.cu",
-           "conv_wgrad_tcgen05.cu"]
+           "conv_wgrad_tcgen05.cu", "conv_rows_tcgen05.cu"]
 HEADERS = ["wcn_common.cuh", "tcgen05_common.cuh", os.path.join("..", "..", "include", "wcn_b200.h")]
 LIB = os.path.join(HERE, "libwcn_b200.so")
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

@@ -18,7 +18,7 @@ from ..geometry.types.voxels import Voxels
 from ..geometry.coords.search.cache import IntSearchCache
 from ..geometry.coords.search.search_results import IntSearchResult
 from ..nn.functional.sparse_conv import (STRIDED_CONV_MODE, TILE_ORDER_MIN_OFFSETS, TILE_ORDER_MIN_ROWS, ConvEpilogue,
-                                         FusedConvLaunch, _identity_map, _implicit_gemm_forward_logic, _merge_bias,
+                                         FusedConvLaunch, FusedRowsLaunch, _identity_map, _implicit_gemm_forward_logic, _merge_bias,
                                          generate_output_coords_and_kernel_map, prefetch_strided_coordinates)
 from ..nn.functional.transforms import cat
 from ..nn.modules.activations import ReLU
@@ -227,22 +227,28 @@ class _LaunchPlan:
         self._versions = [t._version for t in self._tensors]
         self._ptrs = [t.data_ptr() for t in self._tensors]
 
-        def conv_block(seq) -> FusedConvLaunch:
+        def conv_block(seq, rows_too: bool = False):
             conv, bn = seq[0], seq[1]
             scale, shift = fold_batchnorm(bn)
             ep = _merge_bias(ConvEpilogue(scale=scale, shift=shift), conv.bias)
-            return FusedConvLaunch(conv.weight, dtype, ep.scale, ep.shift, relu=isinstance(seq[2], (nn.ReLU, ReLU)))
+            relu = isinstance(seq[2], (nn.ReLU, ReLU))
+            rec = FusedConvLaunch(conv.weight, dtype, ep.scale, ep.shift, relu=relu)
+            if rows_too:  # a 1x1x1 projection: also its input-side record
+                return rec, FusedRowsLaunch(conv.weight, dtype, ep.scale, ep.shift, relu=relu)
+            return rec
 
         def basic_block(blk: BasicBlock):
             last = conv_block(blk.conv2)
             last.relu = 1  # relu(conv2 + identity)
-            return conv_block(blk.conv1), last, conv_block(blk.downsample) if blk.downsample is not None else None
+            return (conv_block(blk.conv1), last,
+                    conv_block(blk.downsample, rows_too=True) if blk.downsample is not None else None)
 
-        def tr_block(blk: ConvTrBlock) -> FusedConvLaunch:
+        def tr_block(blk: ConvTrBlock):
             scale, shift = fold_batchnorm(blk.norm_act[0])
             ep = _merge_bias(ConvEpilogue(scale=scale, shift=shift), blk.conv_tr.bias)
-            return FusedConvLaunch(blk.conv_tr.weight, dtype, ep.scale, ep.shift,
-                                   relu=isinstance(blk.norm_act[1], (nn.ReLU, ReLU)))
+            relu = isinstance(blk.norm_act[1], (nn.ReLU, ReLU))
+            return (FusedConvLaunch(blk.conv_tr.weight, dtype, ep.scale, ep.shift, relu=relu),
+                    FusedRowsLaunch(blk.conv_tr.weight, dtype, ep.scale, ep.shift, relu=relu))
 
         assert tuple(model.conv0[0].kernel_size) == (1, 1, 1), "the stem is a 1x1x1 convolution in this plan"
         self.stem = conv_block(model.conv0)
@@ -251,7 +257,9 @@ class _LaunchPlan:
         self.up = [tr_block(m) for m in (model.convtr4, model.convtr5, model.convtr6, model.convtr7)]
         self.dec = [[basic_block(b) for b in st] for st in (model.block5, model.block6, model.block7, model.block8)]
         head = model.final
-        self.head = FusedConvLaunch(head.weight, dtype, None, head.bias.detach().float() if head.bias is not None else None)
+        head_shift = head.bias.detach().float() if head.bias is not None else None
+        self.head = FusedConvLaunch(head.weight, dtype, None, head_shift)
+        self.head_rows = FusedRowsLaunch(head.weight, dtype, None, head_shift)
 
     def current(self, dtype, device) -> bool:
         if dtype != self.dtype or device != self.device:
@@ -265,7 +273,12 @@ class _LaunchPlan:
     def _blocks(stage, x: torch.Tensor, nbr, rows, n: int, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         last = len(stage) - 1
         for i, (c1, c2, proj) in enumerate(stage):
-            identity = x if proj is None else proj(x, _identity_map(n, x.device).neighbor_table(n), None, n)
+            if proj is None:
+                identity = x
+            elif proj[1].takes(x):   # 1x1x1 projection of the block input: rows streamed once, from the input side
+                identity = proj[1](x, None, n)
+            else:
+                identity = proj[0](x, _identity_map(n, x.device).neighbor_table(n), None, n)
             x = c2(c1(x, nbr, rows, n), nbr, rows, n, residual=identity, out=out if i == last else None)
         return x
 
@@ -307,15 +320,23 @@ class _LaunchPlan:
                 joined(n[3], P[4], P[2])]
         cur = self.stem(feats, _identity_map(n[0], dev).neighbor_table(n[0]), None, n[0], out=bufs[0][2])
         tables = [None] * 5
+        children = [None] * 4   # [8, n[level + 1]]: the fine row of every (coarse row, offset), -1 where there is none
         for level in range(4):
-            cur = self.down[level](cur, down_table(level), None, n[level + 1])
+            children[level] = down_table(level)
+            cur = self.down[level](cur, children[level], None, n[level + 1])
             tables[level + 1] = conv3_table(level + 1)
             nbr, rows = tables[level + 1]
             cur = self._blocks(self.enc[level], cur, nbr, rows, n[level + 1], out=bufs[level + 1][2] if level < 3 else None)
         # decoder: the transposed convolution fills the left-hand block, the stage reads the whole buffer
         for i, level in enumerate((3, 2, 1, 0)):
             buf, left, _ = bufs[level]
-            self.up[i](cur, up_table(level), None, n[level], out=left)
+            up, up_rows = self.up[i]
+            if up_rows.takes(cur):
+                # every fine voxel has one parent (the coarse set is the strided fine set): the parents'
+                # rows are streamed once and each offset's block written at its child
+                up_rows(cur, children[level], n[level], out=left)
+            else:
+                up(cur, up_table(level), None, n[level], out=left)
             if tables[level] is None:
                 tables[level] = conv3_table(level)
             nbr, rows = tables[level]
@@ -326,9 +347,15 @@ class _LaunchPlan:
             # sorted = original[perm], so original row r sits at sorted row inverse[r]: the head reads its
             # input row THROUGH the inverse permutation (whole rows from scattered places) and writes the
             # logits in order, instead of scattering 40-byte rows
+            if self.head_rows.takes(cur):
+                # sorted row j is original row perm[j]: stream the rows in order, write each at its original place
+                dst = perm.to(torch.int32).view(1, n[0]) if perm.dtype != torch.int32 else perm.view(1, n[0])
+                return self.head_rows(cur, dst.contiguous(), n[0])
             inverse = torch.empty(n[0], dtype=torch.int32, device=dev)
             inverse[perm] = torch.arange(n[0], dtype=torch.int32, device=dev)
             return self.head(cur, inverse.view(1, n[0]), None, n[0])
+        if self.head_rows.takes(cur):
+            return x._derive(self.head_rows(cur, None, n[0]))
         return x._derive(self.head(cur, _identity_map(n[0], dev).neighbor_table(n[0]), None, n[0]))
 
 

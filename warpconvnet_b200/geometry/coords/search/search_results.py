@@ -57,14 +57,14 @@ class IntSearchResult:
     def _compact(self):
         if self._offsets is not None:
             return
-        nbr, K, M = self._nbr, self._num_offsets, self._num_out
-        dev = nbr.device
-        ws = self._workspace
-        if ws is None and self._forward is not None:
+        if self._workspace is None and self._forward is not None:
             # transposed view: the compact form is the forward map's with in/out exchanged
             fwd = self._forward
             self._in_maps, self._out_maps, self._offsets = fwd.out_maps, fwd.in_maps, fwd.offsets
             return
+        nbr, K, M = self._nbr, self._num_offsets, self._num_out
+        dev = nbr.device
+        ws = self._workspace
         if ws is None:  # searched without hit counts: count now
             ws = torch.empty(query_bytes("wcn_kmap_workspace_bytes", M, K), dtype=torch.uint8, device=dev)
             check(lib().wcn_kmap_count(ptr(nbr), M, K, ptr(ws), stream_ptr(dev)), "wcn_kmap_count")
@@ -102,6 +102,15 @@ class IntSearchResult:
         if self._nbr is not None:
             assert self._num_out == num_out, f"kernel map was built for {self._num_out} outputs, got {num_out}"
             return self._nbr
+        if self._in_maps is None:  # a transposed view whose table has not been asked for yet
+            fwd = self._forward
+            assert self._num_out == num_out, f"kernel map was built for {self._num_out} outputs, got {num_out}"
+            dev = fwd._nbr.device
+            nbr_t = torch.empty((self._num_offsets, num_out), dtype=torch.int32, device=dev)
+            check(lib().wcn_nbr_transpose(ptr(fwd._nbr), fwd._num_offsets, fwd._num_out, num_out, ptr(nbr_t),
+                                          stream_ptr(dev)), "wcn_nbr_transpose")
+            self._nbr = nbr_t
+            return nbr_t
         dev = self._in_maps.device
         K = self._num_offsets
         nbr = torch.empty((K, num_out), dtype=torch.int32, device=dev)
@@ -145,14 +154,22 @@ class IntSearchResult:
     def swapped(self, num_in: Optional[int] = None) -> "IntSearchResult":
         """The map with inputs and outputs exchanged (transposed convolution,
         warpconvnet/nn/functional/sparse_conv.py:1934-1938)."""
+        if self._forward is not None and self._in_maps is None and (num_in is None or int(num_in) == self._forward._num_out):
+            return self._forward  # exchanging a transposed view back gives the map it came from
         if self._offsets is None and self._nbr is not None and (num_in or self._num_in) is not None:
-            n_in = int(num_in if num_in is not None else self._num_in)
-            dev = self._nbr.device
-            nbr_t = torch.empty((self._num_offsets, n_in), dtype=torch.int32, device=dev)
-            check(lib().wcn_nbr_transpose(ptr(self._nbr), self._num_offsets, self._num_out, n_in, ptr(nbr_t),
-                                          stream_ptr(dev)), "wcn_nbr_transpose")
-            out = IntSearchResult.from_neighbor_table(nbr_t, self._num_out, None, None)
-            out._forward = self  # compact form, if ever asked for, comes from the forward map
+            # Both forms of the view come from this map when first asked for: the compact one by exchanging
+            # in and out, the dense one by transposing the table (a layer that runs from the input side,
+            # sparse_conv_rows_fused, needs neither: it reads this map's own table).
+            out = IntSearchResult.__new__(IntSearchResult)
+            out._in_maps = out._out_maps = out._offsets = None
+            out.identity_map_index = None
+            out._nbr = None
+            out._num_offsets = self._num_offsets
+            out._num_out = int(num_in if num_in is not None else self._num_in)
+            out._num_in = self._num_out
+            out._workspace = None
+            out._forward = self
+            out._tiled = None
             return out
         return IntSearchResult(self.out_maps, self.in_maps, self.offsets)
 
@@ -204,4 +221,6 @@ class IntSearchResult:
 
     @property
     def device(self):
-        return self._nbr.device if self._nbr is not None else self._in_maps.device
+        if self._nbr is not None:
+            return self._nbr.device
+        return self._in_maps.device if self._in_maps is not None else self._forward.device

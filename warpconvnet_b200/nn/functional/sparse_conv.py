@@ -18,6 +18,7 @@ There is no auto-tuner and no CPU path.
 """
 from __future__ import annotations
 
+import ctypes
 import enum
 from dataclasses import dataclass
 from typing import List, Optional, Tuple, Union
@@ -219,6 +220,22 @@ def sparse_conv_fused(in_features: Tensor, weight: Tensor, kernel_map: IntSearch
     residual and ``epilogue.out`` may be column blocks of wider matrices."""
     require_cuda(in_features, "in_features")
     x = _row_view(in_features)
+    if algo == CONV_AUTO and split_k == 0 and not tile_order and num_out_coords > 0:
+        # one (input row, offset) pair per output row: the input-side kernel, when it takes the call
+        ep0 = epilogue or ConvEpilogue()
+        done = None
+        if getattr(kernel_map, "_identity", False) and x.shape[0] == num_out_coords:
+            dst = None
+            if ep0.out_rows is not None and ep0.residual is None and (ep0.out is None or ep0.out.shape[0] == num_out_coords):
+                dst = ep0.out_rows.to(device=x.device, dtype=torch.int32).view(1, -1).contiguous()
+                ep0 = ConvEpilogue(ep0.scale, ep0.shift, None, ep0.relu, None, ep0.out)
+            if ep0.out_rows is None:
+                done = sparse_conv_rows_fused(x, weight, dst, num_out_coords, ep0, out_dtype)
+        elif getattr(kernel_map, "_one_pair", False) and ep0.out_rows is None and kernel_map._forward is not None:
+            done = sparse_conv_rows_fused(x, weight, kernel_map._forward.neighbor_table(x.shape[0]), num_out_coords,
+                                          ep0, out_dtype)
+        if done is not None:
+            return done
     w, packed = _prepared_weight(weight, x.dtype, algo)
     K, c_in, c_out = w.shape
     assert x.shape[1] == c_in, f"features have {x.shape[1]} channels, weight expects {c_in}"
@@ -329,6 +346,136 @@ class FusedConvLaunch:
         return out
 
 
+def _prepared_rows_weight(weight: Tensor, dtype: torch.dtype):
+    """``(packed, c_out_packed)``: the weight re-tiled for the input-side kernel at a width padded to a
+    multiple of 16 columns (extra columns zero), or ``(None, 0)`` when that kernel does not take the
+    shape.  Cached on the weight tensor like :func:`_prepared_weight`."""
+    store = weight.__dict__.setdefault("_wcn_prepared", {})
+    hit = store.get((dtype, "rows"))
+    if hit is not None and hit[0] == weight._version and hit[3] == weight.device:
+        return hit[1], hit[2]
+    packed, c_pack = None, 0
+    if weight.is_cuda and dtype in (torch.float16, torch.bfloat16):
+        K, c_in, c_out = (int(v) for v in weight.shape)
+        width = -(-c_out // 16) * 16
+        dc = dtype_code(dtype)
+        yes = ctypes.c_int32(0)
+        check(lib().wcn_conv_rows_supported(K, c_in, width, dc, dc, ctypes.byref(yes)), "wcn_conv_rows_supported")
+        if yes.value:
+            w = weight.detach().to(dtype=dtype)
+            if width != c_out:
+                w = torch.nn.functional.pad(w, (0, width - c_out))
+            w = w.contiguous()
+            nbytes = query_bytes("wcn_conv_packed_weight_bytes", CONV_AUTO, K, c_in, width, dc)
+            if nbytes > 0:
+                packed, c_pack = torch.empty(nbytes, dtype=torch.uint8, device=w.device), width
+                check(lib().wcn_conv_pack_weight(CONV_AUTO, ptr(w), K, c_in, width, dc, ptr(packed), stream_ptr(w.device)),
+                      "wcn_conv_pack_weight")
+    store[(dtype, "rows")] = (weight._version, packed, c_pack, weight.device)
+    return packed, c_pack
+
+
+def _tma_rows_ok(x: Tensor) -> bool:
+    """Rows a tensor map can describe: 16-byte aligned base and row pitch, contiguous rows, at least
+    one full 128-row tile."""
+    return (x.dim() == 2 and x.shape[0] >= 128 and x.stride(1) == 1 and x.data_ptr() % 16 == 0
+            and (x.stride(0) * x.element_size()) % 16 == 0)
+
+
+def sparse_conv_rows_fused(in_features: Tensor, weight: Tensor, dst_rows: Optional[Tensor], num_out_coords: int,
+                           epilogue: Optional[ConvEpilogue] = None,
+                           out_dtype: Optional[torch.dtype] = None) -> Optional[Tensor]:
+    """A convolution in which every output row has exactly one (input row, offset) pair, run from
+    the input side (``wcn_conv_rows_fwd``): ``out[dst_rows[k, j]] = epilogue(in_features[j] @ weight[k])``.
+    ``dst_rows`` is int32 ``[K, N_in]`` (entries < 0: no such pair) — for a 2x2x2 stride-2 transposed
+    convolution the neighbour table of the matching strided convolution — or None for a 1x1x1
+    convolution (``K == 1``, output row = input row).  Returns None when the kernel does not take the
+    call (dtype, shape or alignment), so the caller can use the output-side kernels.  Output rows
+    that no pair names are left as they were (in a fresh result: uninitialised)."""
+    require_cuda(in_features, "in_features")
+    x = _row_view(in_features)
+    ep = epilogue or ConvEpilogue()
+    if x.dtype not in (torch.float16, torch.bfloat16) or not _tma_rows_ok(x) or ep.out_rows is not None:
+        return None
+    packed, c_pack = _prepared_rows_weight(weight, x.dtype)
+    if packed is None:
+        return None
+    K, c_in, c_out = (int(v) for v in weight.shape)
+    assert x.shape[1] == c_in, f"features have {x.shape[1]} channels, weight expects {c_in}"
+    dev = x.device
+    out_dtype = out_dtype or (ep.out.dtype if ep.out is not None else x.dtype)
+    if out_dtype not in (x.dtype, torch.float32):
+        return None
+    if ep.out is not None:
+        out = ep.out
+        assert out.dtype == out_dtype and out.device == dev and out.dim() == 2 and out.shape[1] == c_out \
+            and out.shape[0] >= num_out_coords and (out.stride(1) == 1 or num_out_coords == 0)
+    else:
+        out = torch.empty((num_out_coords, c_out), dtype=out_dtype, device=dev)
+    if num_out_coords == 0 or x.shape[0] == 0:
+        return out
+    if dst_rows is not None:
+        assert dst_rows.dtype == torch.int32 and tuple(dst_rows.shape) == (K, x.shape[0]) and dst_rows.is_contiguous()
+    else:
+        assert K == 1 and x.shape[0] == num_out_coords
+    residual = None
+    if ep.residual is not None:
+        residual = ep.residual if ep.residual.dtype == out_dtype else ep.residual.to(dtype=out_dtype)
+        residual = _row_view(residual)
+        assert tuple(residual.shape) == (num_out_coords, c_out)
+    scale, shift = _as_f32_on(ep.scale, dev), _as_f32_on(ep.shift, dev)
+    check(lib().wcn_conv_rows_fwd(ptr(x), x.shape[0], x.stride(0), ptr(packed), ptr(dst_rows), num_out_coords, K,
+                                  c_in, c_pack, c_out, dtype_code(x.dtype), ptr(scale), ptr(shift), ptr(residual),
+                                  residual.stride(0) if residual is not None else 0, int(ep.relu), ptr(out),
+                                  out.stride(0), dtype_code(out_dtype), ptr(device_status(dev)), stream_ptr(dev)),
+          "wcn_conv_rows_fwd")
+    return out
+
+
+class FusedRowsLaunch:
+    """The launch record of a one-pair-per-output-row convolution (:func:`sparse_conv_rows_fused`) with
+    everything constant resolved once, as :class:`FusedConvLaunch` is for the output-side kernels.
+    ``usable`` is False when the input-side kernel does not take the layer's shape."""
+
+    __slots__ = ("packed", "scale", "shift", "relu", "K", "c_in", "c_out", "c_pack", "dtype", "device", "_dc",
+                 "_packed_ptr", "_scale_ptr", "_shift_ptr", "_status_ptr", "_dev_index", "_fn", "usable")
+
+    def __init__(self, weight: Tensor, dtype: torch.dtype, scale: Optional[Tensor] = None,
+                 shift: Optional[Tensor] = None, relu: bool = False):
+        self.packed, self.c_pack = _prepared_rows_weight(weight, dtype)
+        self.usable = self.packed is not None
+        dev = weight.device
+        self.scale, self.shift = _as_f32_on(scale, dev), _as_f32_on(shift, dev)
+        self.relu = int(bool(relu))
+        self.K, self.c_in, self.c_out = (int(v) for v in weight.shape)
+        self.dtype, self.device = dtype, dev
+        self._dc = dtype_code(dtype) if self.usable else 0
+        self._packed_ptr = ptr(self.packed)
+        self._scale_ptr, self._shift_ptr = ptr(self.scale), ptr(self.shift)
+        self._status_ptr = ptr(device_status(dev)) if self.usable else None
+        self._dev_index = dev.index if dev.index is not None else (torch.cuda.current_device() if self.usable else 0)
+        self._fn = lib().wcn_conv_rows_fwd
+
+    def takes(self, feats: Tensor) -> bool:
+        return self.usable and _tma_rows_ok(feats)
+
+    def __call__(self, feats: Tensor, dst_rows: Optional[Tensor], num_out: int, residual: Optional[Tensor] = None,
+                 out: Optional[Tensor] = None) -> Tensor:
+        if out is None:
+            out = torch.empty((num_out, self.c_out), dtype=self.dtype, device=self.device)
+        if num_out == 0 or feats.shape[0] == 0:
+            return out
+        rc = self._fn(feats.data_ptr(), feats.shape[0], feats.stride(0), self._packed_ptr,
+                      dst_rows.data_ptr() if dst_rows is not None else None, num_out, self.K, self.c_in, self.c_pack,
+                      self.c_out, self._dc, self._scale_ptr, self._shift_ptr,
+                      residual.data_ptr() if residual is not None else None,
+                      residual.stride(0) if residual is not None else 0, self.relu, out.data_ptr(), out.stride(0),
+                      self._dc, self._status_ptr, torch._C._cuda_getCurrentRawStream(self._dev_index))
+        if rc != 0:
+            check(rc, "wcn_conv_rows_fwd")
+        return out
+
+
 def _implicit_gemm_forward_logic(in_features: Tensor, weight: Tensor, kernel_map: IntSearchResult,
                                  num_out_coords: int, compute_dtype: Optional[torch.dtype],
                                  fwd_block_size: Optional[int] = None,
@@ -433,6 +580,13 @@ def generate_output_coords_and_kernel_map(input_sparse_tensor: Voxels, kernel_si
                                           hashtable=_cached_table(output_spatially_sparse_tensor, out_coords),
                                           bricks=_cached_bricks(output_spatially_sparse_tensor, out_coords))
         kernel_map = fwd.swapped(num_in=out_coords.shape[0])
+        # Window = stride without dilation, and the inputs are exactly the strided outputs: every output
+        # voxel then has one parent and one offset, which the input-side kernel exploits.
+        fine = output_spatially_sparse_tensor.batched_coordinates if output_spatially_sparse_tensor is not None else None
+        parent = fine._shared.get(("strided", tuple(int(s) for s in stride))) if fine is not None else None
+        kernel_map._one_pair = (tuple(kernel_size) == tuple(stride) and all(int(d) == 1 for d in kernel_dilation)
+                                and parent is not None
+                                and parent._shared is input_sparse_tensor.batched_coordinates._shared)
     else:
         kernel_map = _generate_kernel_map_nd(in_coords, out_coords, stride, kernel_size, kernel_dilation,
                                              hashtable=_cached_table(input_sparse_tensor, in_coords),
@@ -824,6 +978,7 @@ def _identity_map(n: int, device: torch.device) -> IntSearchResult:
     if hit is None:
         nbr = torch.arange(n, dtype=torch.int32, device=device).unsqueeze(0).contiguous()
         hit = IntSearchResult.from_neighbor_table(nbr, n, None, 0)
+        hit._identity = True
         if len(_identity_maps) > 64:
             _identity_maps.clear()
         _identity_maps[key] = hit
