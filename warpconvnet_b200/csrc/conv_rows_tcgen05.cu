@@ -53,7 +53,7 @@ struct RowsParams {
   int relu;
   void* out;
   int64_t out_ld;
-  int vec;                   // bytes every output / residual row start is aligned to: 16, 8 or 0
+  int vec;                   // bytes every output / residual row start is aligned to: 32, 16, 8 or 0
   int32_t* dev_status;
 };
 
@@ -81,15 +81,27 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
       : "memory");
 }
 
+// 32 bytes in one request: a whole sector per lane, so that rows scattered over the output cost the
+// L2 one full-sector write each instead of two half-sector ones.
+__device__ __forceinline__ void st_global_32B(void* p, const uint32_t* v) {
+  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "r"(v[0]), "r"(v[1]), "r"(v[2]),
+               "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7])
+               : "memory");
+}
+
 // One 16-column piece of a row: convert and store columns [c0, c0 + 16) that exist (< c_store).
 template <typename TO>
 __device__ __forceinline__ void store_piece(TO* orow, int c0, const float (&y)[16], int c_store, int vec) {
   constexpr int PER16 = 16 / (int)sizeof(TO), PER8 = 8 / (int)sizeof(TO);
-  __align__(16) TO tmp[16];
+  __align__(32) TO tmp[16];
 #pragma unroll
   for (int i = 0; i < 16; ++i) tmp[i] = wcn_from_float<TO>(y[i]);
   const int valid = min(16, c_store - c0);
-  if (vec == 16 && valid == 16) {
+  if (vec == 32 && valid == 16) {
+#pragma unroll
+    for (int i = 0; i < (int)sizeof(TO) / 2; ++i)   // 16 columns are 32 (fp16 / bf16) or 64 bytes (fp32)
+      st_global_32B(reinterpret_cast<char*>(orow + c0) + 32 * i, reinterpret_cast<const uint32_t*>(tmp) + 8 * i);
+  } else if (vec >= 16 && valid == 16) {
 #pragma unroll
     for (int i = 0; i < 16 / PER16; ++i) reinterpret_cast<uint4*>(orow + c0)[i] = reinterpret_cast<const uint4*>(tmp)[i];
   } else if (vec >= 8) {
@@ -114,7 +126,7 @@ template <typename TO>
 __device__ __forceinline__ void add_residual(const TO* rrow, int c0, float (&y)[16], int c_store, int vec) {
   constexpr int PER16 = 16 / (int)sizeof(TO);
   const int valid = min(16, c_store - c0);
-  if (vec == 16 && valid == 16) {
+  if (vec >= 16 && valid == 16) {
     __align__(16) TO tmp[16];
 #pragma unroll
     for (int i = 0; i < 16 / PER16; ++i) reinterpret_cast<uint4*>(tmp)[i] = __ldg(reinterpret_cast<const uint4*>(rrow + c0) + i);
@@ -466,7 +478,7 @@ int wcn_conv_rows_tcgen05_fwd(const void* feats, int64_t num_in, int64_t feats_l
     return (reinterpret_cast<uintptr_t>(out) % a) == 0 && (out_ld * osz) % a == 0 &&
            (!residual || ((reinterpret_cast<uintptr_t>(residual) % a) == 0 && (residual_ld * osz) % a == 0));
   };
-  const int vec = aligned(16) ? 16 : aligned(8) ? 8 : 0;
+  const int vec = aligned(32) ? 32 : aligned(16) ? 16 : aligned(8) ? 8 : 0;
   RowsParams p = {};
   size_t smem = 0;
   if (!plan_rows(K, c_in, c_out_packed, &p, &smem)) return WCN_ERR_UNSUPPORTED_CONFIG;

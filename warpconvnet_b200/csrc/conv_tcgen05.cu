@@ -50,6 +50,7 @@ constexpr int THREADS = 608;
 
 struct ConvTcParams {
   const char* feats;
+  bool wide_out, wide_partial;   // rows of `out` / of the slice workspace start on 32-byte boundaries
   const char* wpacked;
   const int32_t* nbr;
   const int32_t* out_rows;  // slot -> output row, or null for the identity
@@ -83,9 +84,24 @@ __device__ __forceinline__ uint32_t slice_mask(int s, int S, int K) {
   return upto_hi & ~((1u << lo) - 1u);
 }
 
+// 32 bytes in one request: a whole sector per lane.  Every thread of the epilogue writes its own row,
+// so a store instruction touches 32 different lines; with 16-byte pieces the L2 gets two half-sector
+// writes per sector, with 32-byte ones a single full-sector write.
+__device__ __forceinline__ void st_global_32B(void* p, const uint32_t* v) {
+  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "r"(v[0]), "r"(v[1]), "r"(v[2]),
+               "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7])
+               : "memory");
+}
+
+// `wide`: the destination is 32-byte aligned (rows start on 32-byte boundaries).
 template <typename TO> struct OutVec;
 template <> struct OutVec<float> {
-  static __device__ __forceinline__ void store(float* p, const float (&y)[16]) {
+  static __device__ __forceinline__ void store(float* p, const float (&y)[16], bool wide) {
+    if (wide) {
+      st_global_32B(p, reinterpret_cast<const uint32_t*>(y));
+      st_global_32B(p + 8, reinterpret_cast<const uint32_t*>(y) + 8);
+      return;
+    }
 #pragma unroll
     for (int i = 0; i < 4; ++i) reinterpret_cast<float4*>(p)[i] = make_float4(y[4 * i], y[4 * i + 1], y[4 * i + 2], y[4 * i + 3]);
   }
@@ -98,10 +114,14 @@ template <> struct OutVec<float> {
   }
 };
 template <typename T16> struct OutVec16 {
-  static __device__ __forceinline__ void store(T16* p, const float (&y)[16]) {
-    __align__(16) T16 tmp[16];
+  static __device__ __forceinline__ void store(T16* p, const float (&y)[16], bool wide) {
+    __align__(32) T16 tmp[16];
 #pragma unroll
     for (int i = 0; i < 16; ++i) tmp[i] = wcn_from_float<T16>(y[i]);
+    if (wide) {
+      st_global_32B(p, reinterpret_cast<const uint32_t*>(tmp));
+      return;
+    }
     reinterpret_cast<uint4*>(p)[0] = reinterpret_cast<uint4*>(tmp)[0];
     reinterpret_cast<uint4*>(p)[1] = reinterpret_cast<uint4*>(tmp)[1];
   }
@@ -547,7 +567,7 @@ conv_tcgen05_kernel(const ConvTcParams p) {
 #pragma unroll
         for (int i = 0; i < 16; ++i) y[i] = fmaxf(y[i], 0.f);
       }
-      OutVec<TO>::store(orow + c0, y);
+      OutVec<TO>::store(orow + c0, y, p.wide_out);
     };
     const bool sliced = p.S > 1;  // leave raw fp32 sums for the reduction kernel instead of finishing rows
     for (int64_t wu = blockIdx.x; wu < p.units; wu += gridDim.x) {
@@ -591,8 +611,8 @@ conv_tcgen05_kernel(const ConvTcParams p) {
             for (int i = 0; i < 16; ++i) y0[i] = y1[i] = 0.f;
           }
           if (live && sliced) {
-            OutVec<float>::store(prow + c0, y0);
-            OutVec<float>::store(prow + c0 + 16, y1);
+            OutVec<float>::store(prow + c0, y0, p.wide_partial);
+            OutVec<float>::store(prow + c0 + 16, y1, p.wide_partial);
           } else if (live) {
             finish16(y0, c0, orow, rrow);
             finish16(y1, c0 + 16, orow, rrow);
@@ -610,7 +630,7 @@ conv_tcgen05_kernel(const ConvTcParams p) {
 #pragma unroll
             for (int i = 0; i < 16; ++i) y0[i] = 0.f;
           }
-          if (live && sliced) OutVec<float>::store(prow + c0, y0);
+          if (live && sliced) OutVec<float>::store(prow + c0, y0, p.wide_partial);
           else if (live) finish16(y0, c0, orow, rrow);
         }
       }
@@ -897,6 +917,8 @@ int wcn_conv_tcgen05_fwd(const void* feats, int64_t num_in, int64_t feats_ld, co
   p.in_ld_bytes = feats_ld * 2; p.out_ld = out_ld; p.res_ld = residual_ld;
   p.scale = scale; p.shift = shift; p.residual = residual; p.relu = relu; p.out = out;
   p.dev_status = dev_status;
+  p.wide_out = (reinterpret_cast<uintptr_t>(out) & 31) == 0 && (out_ld * osz) % 32 == 0;
+  p.wide_partial = (reinterpret_cast<uintptr_t>(workspace) & 31) == 0;   // its rows are c_out fp32 values: 64-byte multiples
   const int bk = pick_bk(c_in);
   const bool bf = dtype == WCN_BF16;
 #define WCN_TC_CASE(BKV, BFV, TO) \
