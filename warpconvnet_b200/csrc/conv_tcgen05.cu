@@ -181,7 +181,7 @@ struct Control {
 
 // ------------------------------------------------------------------ kernel
 
-template <int BK, int KBC, bool BF16, typename TO>
+template <int BK, int KBC, bool SPAN, bool BF16, typename TO>
 __global__ void __launch_bounds__(THREADS, 1)
 conv_tcgen05_kernel(const ConvTcParams p) {
   constexpr int RB = BK * 2;         // bytes per tile row
@@ -316,7 +316,7 @@ conv_tcgen05_kernel(const ConvTcParams p) {
         // One channel slice per offset (KB == 1) and KBC > 1: a ring slot spans KBC consecutive
         // ACTIVE OFFSETS instead of KBC channel slices of one offset, so narrow layers get the same
         // fat slots as wide ones.  All roles take the offsets off the mask in the same groups.
-        while (KBC > 1 && KB == 1 && rest && ok) {
+        while (SPAN && rest && ok) {
           int ku[KBC];
           const int nu = pop_offsets<KBC>(rest, ku);
           if (!mbar_wait(bar(&ctl->b_empty[rb.slot]), rb.phase ^ 1, p.dev_status)) { ok = false; break; }
@@ -329,7 +329,7 @@ conv_tcgen05_kernel(const ConvTcParams p) {
                             p.wpacked + ((int64_t)ku[u] * p.c_out + n0) * RB, (uint32_t)B_BYTES, fullb);
           rb.advance();
         }
-        while (rest && ok) {
+        while (!SPAN && rest && ok) {
           const int k = __ffs(rest) - 1;
           rest &= rest - 1;
           const char* bsrc_k = p.wpacked + ((int64_t)k * KB * p.c_out + n0) * RB;
@@ -365,7 +365,7 @@ conv_tcgen05_kernel(const ConvTcParams p) {
       const uint32_t mk2 = ctl->info_mask[ib][2], mk3 = ctl->info_mask[ib][3];
       const int32_t* tab = rows_idx + ib * IDX_INTS + gwarp * ROWS_PER_WARP + sub_row;
       uint32_t rest = mk0 | mk1 | mk2 | mk3;
-      while (KBC > 1 && KB == 1 && rest && ok) {  // slots that span offsets (see the weight loader)
+      while (SPAN && rest && ok) {  // slots that span offsets (see the weight loader)
         int ku[KBC];
         pop_offsets<KBC>(rest, ku);
         uint32_t gbu[KBC], gany = 0;
@@ -398,7 +398,7 @@ conv_tcgen05_kernel(const ConvTcParams p) {
           ra.advance();
         }
       }
-      while (rest && ok) {
+      while (!SPAN && rest && ok) {
         const int k = __ffs(rest) - 1;
         rest &= rest - 1;
         const uint32_t gbits = subtiles_at(mk0, mk1, mk2, mk3, k);
@@ -453,7 +453,7 @@ conv_tcgen05_kernel(const ConvTcParams p) {
         tc_fence_after();
         uint32_t started = 0;
         uint32_t rest = uni;
-        while (KBC > 1 && KB == 1 && rest && ok) {  // slots that span offsets (see the weight loader)
+        while (SPAN && rest && ok) {  // slots that span offsets (see the weight loader)
           int ku[KBC];
           pop_offsets<KBC>(rest, ku);
           uint32_t gbu[KBC], gany = 0;
@@ -495,7 +495,7 @@ conv_tcgen05_kernel(const ConvTcParams p) {
           umma_commit(bar(&ctl->b_empty[rb.slot]));
           rb.advance();
         }
-        while (rest && ok) {
+        while (!SPAN && rest && ok) {
           const int k = __ffs(rest) - 1;
           rest &= rest - 1;
           const uint32_t gbits = subtiles_at(mk0, mk1, mk2, mk3, k);
@@ -573,9 +573,8 @@ conv_tcgen05_kernel(const ConvTcParams p) {
     for (int64_t wu = blockIdx.x; wu < p.units; wu += gridDim.x) {
       const int64_t st = sliced ? wu / p.S : wu;
       if (ok) ok = mbar_wait(bar(&ctl->info_full[ib]), iphase, p.dev_status);
-      uint32_t gm[MAX_G];
-#pragma unroll
-      for (int g = 0; g < MAX_G; ++g) gm[g] = ok ? ctl->info_mask[ib][g] : 0u;
+      const uint32_t gm0 = ok ? ctl->info_mask[ib][0] : 0u, gm1 = ok ? ctl->info_mask[ib][1] : 0u;
+      const uint32_t gm2 = ok ? ctl->info_mask[ib][2] : 0u, gm3 = ok ? ctl->info_mask[ib][3] : 0u;
       mbar_arrive(bar(&ctl->info_empty[ib]));  // only the masks were needed
       if (++ib == 2) { ib = 0; iphase ^= 1; }
       if (ok) ok = mbar_wait(bar(&ctl->acc_full[ab]), aphase, p.dev_status);
@@ -583,10 +582,12 @@ conv_tcgen05_kernel(const ConvTcParams p) {
       if (!__all_sync(0xFFFFFFFFu, ok)) { ok = false; break; }
       tc_fence_after();
       const int64_t m0 = st * G * BLOCK_M;
-#pragma unroll
-      for (int g = 0; g < MAX_G; ++g) {
-        if (g >= G || m0 + (int64_t)g * BLOCK_M >= p.M) break;
-        const uint32_t gmask = gm[g];
+      // (neither loop is unrolled: the epilogue's code is shared by all sub-tiles and column pieces, which
+      // keeps the kernel's instruction footprint — five roles run side by side on a multiprocessor — small)
+#pragma unroll 1
+      for (int g = 0; g < G; ++g) {
+        if (m0 + (int64_t)g * BLOCK_M >= p.M) break;
+        const uint32_t gmask = g == 0 ? gm0 : g == 1 ? gm1 : g == 2 ? gm2 : gm3;
         const int64_t slot = m0 + (int64_t)g * BLOCK_M + tid;
         // rows past the end keep m >= M and are never stored
         const int64_t m = (p.out_rows && slot < p.M) ? (int64_t)__ldg(&p.out_rows[slot]) : slot;
@@ -596,42 +597,28 @@ conv_tcgen05_kernel(const ConvTcParams p) {
         const TO* rrow = p.residual ? reinterpret_cast<const TO*>(p.residual) + m * p.res_ld + n0 : nullptr;
         // slice wu % S of this row block: [S][M][c_out] fp32, rows in table order (a slice owns all columns)
         float* prow = sliced ? p.partial + (((wu - st * p.S) * p.M + slot) * p.c_out) : nullptr;
-        int c0 = 0;
-        for (; c0 + 32 <= BN; c0 += 32) {  // two TMEM loads in flight per wait
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 32) {  // two TMEM loads in flight per wait (BN is a multiple of 16)
+          const bool two = c0 + 16 < BN;
           float y0[16], y1[16];
           if (gmask) {
             uint32_t r0[16], r1[16];
             tmem_ld16(trow + (uint32_t)c0, r0);  // executed by all lanes of the warp
-            tmem_ld16(trow + (uint32_t)c0 + 16u, r1);
+            if (two) tmem_ld16(trow + (uint32_t)c0 + 16u, r1);
             tmem_ld_wait();
 #pragma unroll
-            for (int i = 0; i < 16; ++i) { y0[i] = __uint_as_float(r0[i]); y1[i] = __uint_as_float(r1[i]); }
+            for (int i = 0; i < 16; ++i) { y0[i] = __uint_as_float(r0[i]); y1[i] = two ? __uint_as_float(r1[i]) : 0.f; }
           } else {
 #pragma unroll
             for (int i = 0; i < 16; ++i) y0[i] = y1[i] = 0.f;
           }
           if (live && sliced) {
             OutVec<float>::store(prow + c0, y0, p.wide_partial);
-            OutVec<float>::store(prow + c0 + 16, y1, p.wide_partial);
+            if (two) OutVec<float>::store(prow + c0 + 16, y1, p.wide_partial);
           } else if (live) {
             finish16(y0, c0, orow, rrow);
-            finish16(y1, c0 + 16, orow, rrow);
+            if (two) finish16(y1, c0 + 16, orow, rrow);
           }
-        }
-        if (c0 < BN) {  // BN is a multiple of 16
-          float y0[16];
-          if (gmask) {
-            uint32_t r0[16];
-            tmem_ld16(trow + (uint32_t)c0, r0);
-            tmem_ld_wait();
-#pragma unroll
-            for (int i = 0; i < 16; ++i) y0[i] = __uint_as_float(r0[i]);
-          } else {
-#pragma unroll
-            for (int i = 0; i < 16; ++i) y0[i] = 0.f;
-          }
-          if (live && sliced) OutVec<float>::store(prow + c0, y0, p.wide_partial);
-          else if (live) finish16(y0, c0, orow, rrow);
         }
       }
       tc_fence_before();
@@ -804,9 +791,9 @@ bool plan_launch(ConvTcParams& p, int bk, int split_k, size_t* smem, dim3* grid)
   return true;
 }
 
-template <int BK, int KBC, bool BF16, typename TO>
+template <int BK, int KBC, bool SPAN, bool BF16, typename TO>
 int launch_kbc(const ConvTcParams& p, size_t smem, dim3 grid, cudaStream_t st) {
-  auto kern = conv_tcgen05_kernel<BK, KBC, BF16, TO>;
+  auto kern = conv_tcgen05_kernel<BK, KBC, SPAN, BF16, TO>;
   static bool configured[64] = {};  // per template instance and device: opt in to large shared memory once
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return WCN_ERR_INITIALIZATION;
@@ -840,11 +827,22 @@ int launch_tc(ConvTcParams& p, int split_k, void* workspace, int64_t workspace_b
       return WCN_ERR_INVALID_PARAMETERS;
     p.partial = reinterpret_cast<float*>(workspace);
   }
+  // SPAN: the whole C_in is one slice and a ring slot holds KBC consecutive active offsets; otherwise a
+  // slot holds KBC channel slices of one offset.  A compile-time choice, so that every role's loop
+  // carries only the form it runs.
+  if (p.kbc > 1 && p.c_in == BK) {
+    switch (p.kbc) {
+      case 2: return launch_kbc<BK, 2, true, BF16, TO>(p, smem, grid, st);
+      case 3: return launch_kbc<BK, 3, true, BF16, TO>(p, smem, grid, st);
+      case 4: return launch_kbc<BK, 4, true, BF16, TO>(p, smem, grid, st);
+      default: return WCN_ERR_UNSUPPORTED_CONFIG;
+    }
+  }
   switch (p.kbc) {
-    case 1: return launch_kbc<BK, 1, BF16, TO>(p, smem, grid, st);
-    case 2: return launch_kbc<BK, 2, BF16, TO>(p, smem, grid, st);
-    case 3: return launch_kbc<BK, 3, BF16, TO>(p, smem, grid, st);
-    case 4: return launch_kbc<BK, 4, BF16, TO>(p, smem, grid, st);
+    case 1: return launch_kbc<BK, 1, false, BF16, TO>(p, smem, grid, st);
+    case 2: return launch_kbc<BK, 2, false, BF16, TO>(p, smem, grid, st);
+    case 3: return launch_kbc<BK, 3, false, BF16, TO>(p, smem, grid, st);
+    case 4: return launch_kbc<BK, 4, false, BF16, TO>(p, smem, grid, st);
     default: return WCN_ERR_UNSUPPORTED_CONFIG;
   }
 }

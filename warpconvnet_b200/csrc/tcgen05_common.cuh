@@ -40,11 +40,10 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // out.  The status word lives in global memory and is looked at about once per millisecond of
 // waiting.  An expired wait overrides whatever the word held (a skipped out-of-range index is
 // reported with a compare-and-swap that never overrides anything, see wcn_report_bounds).
-template <bool CUSTOM_LIMIT>
-__device__ __forceinline__ bool mbar_wait_impl(uint32_t bar, uint32_t parity, int32_t* dev_status, long long limit_cycles) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const long long limit = CUSTOM_LIMIT ? limit_cycles : kWaitCycles;
-  const long long poll = (CUSTOM_LIMIT && limit_cycles < kStatusPollCycles) ? limit_cycles : kStatusPollCycles;
+// The slow path is a function of its own (not inlined): the waits sit in the hot loops of single-thread
+// roles, whose instruction footprint should stay small.
+__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, int32_t* dev_status, long long limit) {
+  const long long poll = limit < kStatusPollCycles ? limit : kStatusPollCycles;
   const long long t0 = clock64();
   long long next_check = t0 + poll;
   for (;;) {
@@ -62,13 +61,15 @@ __device__ __forceinline__ bool mbar_wait_impl(uint32_t bar, uint32_t parity, in
     }
   }
 }
-// The wait every kernel role uses: the limit is a compile-time constant (about two seconds).
+// The wait every kernel role uses: the limit is about two seconds.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int32_t* dev_status) {
-  return mbar_wait_impl<false>(bar, parity, dev_status, 0);
+  if (mbar_try_wait(bar, parity)) return true;
+  return mbar_wait_slow(bar, parity, dev_status, kWaitCycles);
 }
 // The same wait with a caller-chosen limit (the self test of the expiry path).
 __device__ __forceinline__ bool mbar_wait_limit(uint32_t bar, uint32_t parity, int32_t* dev_status, long long limit_cycles) {
-  return mbar_wait_impl<true>(bar, parity, dev_status, limit_cycles);
+  if (mbar_try_wait(bar, parity)) return true;
+  return mbar_wait_slow(bar, parity, dev_status, limit_cycles);
 }
 
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {

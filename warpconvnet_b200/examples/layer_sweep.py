@@ -69,6 +69,9 @@ def measure(voxels: int = 500000, voxel_size: float = 0.01, mode: str = "raster_
         "down2": (generate_kernel_map(fine, coarse, (2, 2, 2), (2, 2, 2)), n, len(coarse)),
     }
     maps["up2"] = (maps["down2"][0].swapped(num_in=n), len(coarse), n)
+    # the coarse set is the strided fine set: every fine voxel has one parent and one offset, which is what
+    # generate_output_coords_and_kernel_map records on such a map (under `auto` the layer then runs from the input side)
+    maps["up2"][0]._one_pair = True
     if flush is None:
         flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     g = torch.Generator(device="cpu").manual_seed(0)
