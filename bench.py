@@ -322,8 +322,8 @@ def install_conv_profiler(profile):
 
 
 # DRAM bytes (read + write) of one 3x3x3 C = 96 fp16 launch over 500 000 rows, from the ncu capture
-# summarised under profiles/ (153 MB read + 57 MB written; the algorithmic bytes are 248 MB).
-NCU_DRAM_BYTES_C96_500K = 210e6
+# summarised under profiles/ (153 MB read + 63 MB written; the algorithmic bytes are 248 MB).
+NCU_DRAM_BYTES_C96_500K = 216e6
 
 
 def measure_strong(args, rank, world, dev, model, forward_of, timed, flush, weak_ms_per_step, weak_voxels, lanes, lane,

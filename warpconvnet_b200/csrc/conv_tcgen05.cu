@@ -50,7 +50,7 @@ constexpr int THREADS = 608;
 
 struct ConvTcParams {
   const char* feats;
-  bool wide_out, wide_partial;   // rows of `out` / of the slice workspace start on 32-byte boundaries
+  bool wide_out, wide_partial, wide_res;   // rows of `out` / the slice workspace / `residual` start on 32-byte boundaries
   const char* wpacked;
   const int32_t* nbr;
   const int32_t* out_rows;  // slot -> output row, or null for the identity
@@ -93,6 +93,12 @@ __device__ __forceinline__ void st_global_32B(void* p, const uint32_t* v) {
                : "memory");
 }
 
+__device__ __forceinline__ void ld_global_32B(const void* p, uint32_t* v) {
+  asm volatile("ld.global.nc.v8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
+               : "l"(p));
+}
+
 // `wide`: the destination is 32-byte aligned (rows start on 32-byte boundaries).
 template <typename TO> struct OutVec;
 template <> struct OutVec<float> {
@@ -105,7 +111,12 @@ template <> struct OutVec<float> {
 #pragma unroll
     for (int i = 0; i < 4; ++i) reinterpret_cast<float4*>(p)[i] = make_float4(y[4 * i], y[4 * i + 1], y[4 * i + 2], y[4 * i + 3]);
   }
-  static __device__ __forceinline__ void load(const float* p, float (&y)[16]) {
+  static __device__ __forceinline__ void load(const float* p, float (&y)[16], bool wide) {
+    if (wide) {
+      ld_global_32B(p, reinterpret_cast<uint32_t*>(y));
+      ld_global_32B(p + 8, reinterpret_cast<uint32_t*>(y) + 8);
+      return;
+    }
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       float4 v = __ldg(reinterpret_cast<const float4*>(p) + i);
@@ -125,10 +136,14 @@ template <typename T16> struct OutVec16 {
     reinterpret_cast<uint4*>(p)[0] = reinterpret_cast<uint4*>(tmp)[0];
     reinterpret_cast<uint4*>(p)[1] = reinterpret_cast<uint4*>(tmp)[1];
   }
-  static __device__ __forceinline__ void load(const T16* p, float (&y)[16]) {
-    __align__(16) T16 tmp[16];
-    reinterpret_cast<uint4*>(tmp)[0] = __ldg(reinterpret_cast<const uint4*>(p));
-    reinterpret_cast<uint4*>(tmp)[1] = __ldg(reinterpret_cast<const uint4*>(p) + 1);
+  static __device__ __forceinline__ void load(const T16* p, float (&y)[16], bool wide) {
+    __align__(32) T16 tmp[16];
+    if (wide) {
+      ld_global_32B(p, reinterpret_cast<uint32_t*>(tmp));
+    } else {
+      reinterpret_cast<uint4*>(tmp)[0] = __ldg(reinterpret_cast<const uint4*>(p));
+      reinterpret_cast<uint4*>(tmp)[1] = __ldg(reinterpret_cast<const uint4*>(p) + 1);
+    }
 #pragma unroll
     for (int i = 0; i < 16; ++i) y[i] = wcn_to_float<T16>(tmp[i]);
   }
@@ -559,7 +574,7 @@ conv_tcgen05_kernel(const ConvTcParams p) {
       }
       if (rrow) {
         float res[16];
-        OutVec<TO>::load(rrow + c0, res);
+        OutVec<TO>::load(rrow + c0, res, p.wide_res);
 #pragma unroll
         for (int i = 0; i < 16; ++i) y[i] += res[i];
       }
@@ -916,6 +931,7 @@ int wcn_conv_tcgen05_fwd(const void* feats, int64_t num_in, int64_t feats_ld, co
   p.scale = scale; p.shift = shift; p.residual = residual; p.relu = relu; p.out = out;
   p.dev_status = dev_status;
   p.wide_out = (reinterpret_cast<uintptr_t>(out) & 31) == 0 && (out_ld * osz) % 32 == 0;
+  p.wide_res = residual && (reinterpret_cast<uintptr_t>(residual) & 31) == 0 && (residual_ld * osz) % 32 == 0;
   p.wide_partial = (reinterpret_cast<uintptr_t>(workspace) & 31) == 0;   // its rows are c_out fp32 values: 64-byte multiples
   const int bk = pick_bk(c_in);
   const bool bf = dtype == WCN_BF16;
