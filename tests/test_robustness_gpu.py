@@ -142,6 +142,48 @@ def test_bounded_wait_gives_up_and_later_launches_are_loud():
     assert lib().wcn_selftest_bounded_wait(10, ptr(device_status(DEV)), None, stream_ptr(DEV)) != 0  # limit too small
 
 
+def test_input_side_kernel_reports_bad_destinations_and_is_loud_after_an_expired_wait():
+    """wcn_conv_rows_fwd: a destination past the output is skipped and reported (every other row is
+    right, the rows nobody names keep what they held); while the status word holds an expired wait
+    the kernel computes nothing and marks the rows it would have written with NaN."""
+    from warpconvnet_b200.nn.functional.sparse_conv import sparse_conv_rows_fused
+    check_device_status(DEV)
+    g = torch.Generator().manual_seed(4)
+    n_in, n_out, c_in, c_out = 3000, 5000, 64, 48
+    x = torch.randn(n_in, c_in, generator=g).half().to(DEV)
+    w = (torch.randn(1, c_in, c_out, generator=g) * 0.1).half().to(DEV)
+    dst = torch.randperm(n_out, generator=g)[:n_in].to(torch.int32).view(1, -1).contiguous()
+    bad = dst.clone()
+    bad[0, 17] = n_out + 99
+    bad[0, 18] = -1            # a pair that names no row: not an error
+    out = torch.full((n_out, c_out), -3.0, dtype=torch.float16, device=DEV)
+    got = sparse_conv_rows_fused(x, w, bad.to(DEV), n_out, ConvEpilogue(out=out))
+    assert got is not None
+    torch.cuda.synchronize()
+    with pytest.raises(RuntimeError, match=BOUNDS):
+        check_device_status(DEV)
+    want = (x.float() @ w[0].float()).half()
+    rows = dst[0].long()
+    keep = torch.ones(n_in, dtype=torch.bool)
+    keep[17] = keep[18] = False
+    assert rel_l2(out[rows[keep]].float().cpu().numpy(), want[keep].float().cpu().numpy()) < 2e-3
+    untouched = torch.ones(n_out, dtype=torch.bool)
+    untouched[rows[keep]] = False
+    assert bool((out[untouched.to(DEV)] == -3.0).all())
+    # an expired wait on the status word: nothing is computed, the named rows turn NaN
+    assert lib().wcn_selftest_bounded_wait(200_000, ptr(device_status(DEV)), None, stream_ptr(DEV)) == 0
+    loud = sparse_conv_rows_fused(x, w, dst.to(DEV), n_out, ConvEpilogue(out=torch.zeros_like(out)))
+    torch.cuda.synchronize()
+    unnamed = torch.ones(n_out, dtype=torch.bool)
+    unnamed[rows] = False
+    assert bool(torch.isnan(loud[rows]).all()) and bool((loud[unnamed.to(DEV)] == 0).all())
+    with pytest.raises(RuntimeError, match=EXPIRED):
+        check_device_status(DEV)
+    again = sparse_conv_rows_fused(x, w, dst.to(DEV), n_out)
+    check_device_status(DEV)
+    assert rel_l2(again[rows].float().cpu().numpy(), want.float().cpu().numpy()) < 2e-3
+
+
 def test_status_word_is_read_where_the_host_waits_anyway():
     """A failure recorded by an earlier kernel surfaces at the next point where the package
     synchronises with the host: sizing strided coordinates, compacting a kernel map."""

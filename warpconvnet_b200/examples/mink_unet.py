@@ -9,6 +9,7 @@ one fused kernel.
 """
 from __future__ import annotations
 
+import operator
 from typing import Optional, Union
 
 import torch
@@ -210,6 +211,9 @@ class MinkUNetBase(nn.Module):
         return self.block8(out_p1._derive(buf8))
 
 
+_tensor_version = operator.attrgetter("_version")
+
+
 class _LaunchPlan:
     """Inference forward of a :class:`MinkUNetBase` as a fixed sequence of
     :class:`FusedConvLaunch` records over per-level neighbour tables.
@@ -262,12 +266,12 @@ class _LaunchPlan:
         self.head_rows = FusedRowsLaunch(head.weight, dtype, None, head_shift)
 
     def current(self, dtype, device) -> bool:
+        """True while no parameter or buffer has been written or re-allocated since the plan was made
+        (version counters and data pointers compared in C loops: this runs on every forward)."""
         if dtype != self.dtype or device != self.device:
             return False
-        for t, v, p in zip(self._tensors, self._versions, self._ptrs):
-            if t._version != v or t.data_ptr() != p:
-                return False
-        return True
+        return (list(map(_tensor_version, self._tensors)) == self._versions
+                and list(map(torch.Tensor.data_ptr, self._tensors)) == self._ptrs)
 
     @staticmethod
     def _blocks(stage, x: torch.Tensor, nbr, rows, n: int, out: Optional[torch.Tensor] = None) -> torch.Tensor:
