@@ -36,7 +36,7 @@
 namespace {
 
 constexpr int BLOCK_M = 128;
-constexpr int MAX_G = 4;              // sub-tiles per supertile
+constexpr int MAX_G = 2;              // sub-tiles per supertile (one per MMA issuer)
 constexpr int MAX_RING = 12;          // slots per ring
 constexpr int MAX_OFFSETS = 27;
 constexpr int EPI_THREADS = 128;      // warps 0..3: TMEM lane quarter = warp index
@@ -287,23 +287,33 @@ conv_tcgen05_kernel(const ConvTcParams p) {
       const int64_t m0 = st * G * BLOCK_M;
       if (!mbar_wait(bar(&ctl->info_empty[ib]), iphase ^ 1, p.dev_status)) { ok = false; break; }
       int32_t* dst = rows_idx + ib * IDX_INTS;
-      for (int g = 0; g < G; ++g) {
-        const int64_t m = m0 + (int64_t)g * BLOCK_M + itid;
-        uint32_t mine = 0;
-        int r[MAX_OFFSETS];  // all loads are issued before the first one is consumed
+      // The rows of both sub-tiles are requested before either is consumed: a thread's loads are what this
+      // role waits for, so twice as many in flight halve the time a table takes.
+      const int64_t ma = m0 + itid, mb = m0 + BLOCK_M + itid;
+      const bool two = G > 1;
+      int ra[MAX_OFFSETS], rb[MAX_OFFSETS];
 #pragma unroll
-        for (int k = 0; k < MAX_OFFSETS; ++k)
-          r[k] = (k < K && ((kmask >> k) & 1u) && m < p.M) ? __ldg(&p.nbr[(int64_t)k * p.M + m]) : -1;
+      for (int k = 0; k < MAX_OFFSETS; ++k) {
+        const bool want = k < K && ((kmask >> k) & 1u);
+        ra[k] = (want && ma < p.M) ? __ldg(&p.nbr[(int64_t)k * p.M + ma]) : -1;
+        rb[k] = (want && two && mb < p.M) ? __ldg(&p.nbr[(int64_t)k * p.M + mb]) : -1;
+      }
+      uint32_t mine_a = 0, mine_b = 0;
 #pragma unroll
-        for (int k = 0; k < MAX_OFFSETS; ++k) {
-          if (k < K) {
-            if (r[k] >= num_in) { r[k] = -1; bad = true; }
-            dst[(g * K + k) * BLOCK_M + itid] = r[k];
-            if (__any_sync(0xFFFFFFFFu, r[k] >= 0)) mine |= 1u << k;
+      for (int k = 0; k < MAX_OFFSETS; ++k) {
+        if (k < K) {
+          if (ra[k] >= num_in) { ra[k] = -1; bad = true; }
+          dst[k * BLOCK_M + itid] = ra[k];
+          if (__any_sync(0xFFFFFFFFu, ra[k] >= 0)) mine_a |= 1u << k;
+          if (two) {
+            if (rb[k] >= num_in) { rb[k] = -1; bad = true; }
+            dst[(K + k) * BLOCK_M + itid] = rb[k];
+            if (__any_sync(0xFFFFFFFFu, rb[k] >= 0)) mine_b |= 1u << k;
           }
         }
-        if (lane == 0 && mine) atomicOr(&ctl->mask_acc[ib][g], mine);
       }
+      if (lane == 0 && mine_a) atomicOr(&ctl->mask_acc[ib][0], mine_a);
+      if (lane == 0 && mine_b) atomicOr(&ctl->mask_acc[ib][1], mine_b);
       // all index threads meet (bounded: a thread that gave up does not arrive, the others time out)
       mbar_arrive(bar(&ctl->idx_sync));
       if (!mbar_wait(bar(&ctl->idx_sync), sphase, p.dev_status)) { ok = false; break; }
@@ -325,7 +335,7 @@ conv_tcgen05_kernel(const ConvTcParams p) {
       int ib = 0, iphase = 0;
       for (int64_t wu = blockIdx.x; wu < p.units && ok; wu += gridDim.x) {
         if (!mbar_wait(bar(&ctl->info_full[ib]), iphase, p.dev_status)) { ok = false; break; }
-        uint32_t rest = ctl->info_mask[ib][0] | ctl->info_mask[ib][1] | ctl->info_mask[ib][2] | ctl->info_mask[ib][3];
+        uint32_t rest = ctl->info_mask[ib][0] | ctl->info_mask[ib][1];
         mbar_arrive(bar(&ctl->info_empty[ib]));  // only the masks were needed
         if (++ib == 2) { ib = 0; iphase ^= 1; }
         // One channel slice per offset (KB == 1) and KBC > 1: a ring slot spans KBC consecutive
@@ -377,7 +387,7 @@ conv_tcgen05_kernel(const ConvTcParams p) {
     for (int64_t wu = blockIdx.x; wu < p.units && ok; wu += gridDim.x) {
       if (!mbar_wait(bar(&ctl->info_full[ib]), iphase, p.dev_status)) { ok = false; break; }
       const uint32_t mk0 = ctl->info_mask[ib][0], mk1 = ctl->info_mask[ib][1];
-      const uint32_t mk2 = ctl->info_mask[ib][2], mk3 = ctl->info_mask[ib][3];
+      constexpr uint32_t mk2 = 0u, mk3 = 0u;
       const int32_t* tab = rows_idx + ib * IDX_INTS + gwarp * ROWS_PER_WARP + sub_row;
       uint32_t rest = mk0 | mk1 | mk2 | mk3;
       while (SPAN && rest && ok) {  // slots that span offsets (see the weight loader)
@@ -459,7 +469,7 @@ conv_tcgen05_kernel(const ConvTcParams p) {
       for (int64_t wu = blockIdx.x; wu < p.units && ok; wu += gridDim.x) {
         if (!mbar_wait(bar(&ctl->info_full[ib]), iphase, p.dev_status)) { ok = false; break; }
         const uint32_t mk0 = ctl->info_mask[ib][0], mk1 = ctl->info_mask[ib][1];
-        const uint32_t mk2 = ctl->info_mask[ib][2], mk3 = ctl->info_mask[ib][3];
+        constexpr uint32_t mk2 = 0u, mk3 = 0u;
         const uint32_t uni = mk0 | mk1 | mk2 | mk3;
         mbar_arrive(bar(&ctl->info_empty[ib]));  // only the masks were needed
         if (++ib == 2) { ib = 0; iphase ^= 1; }
@@ -589,7 +599,6 @@ conv_tcgen05_kernel(const ConvTcParams p) {
       const int64_t st = sliced ? wu / p.S : wu;
       if (ok) ok = mbar_wait(bar(&ctl->info_full[ib]), iphase, p.dev_status);
       const uint32_t gm0 = ok ? ctl->info_mask[ib][0] : 0u, gm1 = ok ? ctl->info_mask[ib][1] : 0u;
-      const uint32_t gm2 = ok ? ctl->info_mask[ib][2] : 0u, gm3 = ok ? ctl->info_mask[ib][3] : 0u;
       mbar_arrive(bar(&ctl->info_empty[ib]));  // only the masks were needed
       if (++ib == 2) { ib = 0; iphase ^= 1; }
       if (ok) ok = mbar_wait(bar(&ctl->acc_full[ab]), aphase, p.dev_status);
@@ -602,7 +611,7 @@ conv_tcgen05_kernel(const ConvTcParams p) {
 #pragma unroll 1
       for (int g = 0; g < G; ++g) {
         if (m0 + (int64_t)g * BLOCK_M >= p.M) break;
-        const uint32_t gmask = g == 0 ? gm0 : g == 1 ? gm1 : g == 2 ? gm2 : gm3;
+        const uint32_t gmask = g == 0 ? gm0 : gm1;
         const int64_t slot = m0 + (int64_t)g * BLOCK_M + tid;
         // rows past the end keep m >= M and are never stored
         const int64_t m = (p.out_rows && slot < p.M) ? (int64_t)__ldg(&p.out_rows[slot]) : slot;
@@ -757,7 +766,10 @@ bool plan_launch(ConvTcParams& p, int bk, int split_k, size_t* smem, dim3* grid)
   int cols = 32;
   while (cols < p.block_n) cols <<= 1;
   p.cols = cols;
-  int g = cols >= 128 ? 2 : 4;
+  // Two sub-tiles per supertile (one per issuer).  Four were used for narrow outputs once, to share a weight
+  // slice among more rows; narrow layers have tiny weights, and the two extra staged tables (55 KB) are worth
+  // more as row slots: 3x3x3 C = 32 / 64 layers measured 11 % faster with two.
+  int g = 2;
   while (g > 1 && ((tiles + g - 1) / g) * split * S < 2 * (int64_t)sms) g /= 2;
   const size_t a_unit = (size_t)BLOCK_M * bk * 2, b_unit = (size_t)p.block_n * bk * 2;
   const size_t limit = 226 * 1024;  // the kernels opt in to this much dynamic shared memory
