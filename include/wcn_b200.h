@@ -262,10 +262,12 @@ int wcn_kmap_search_bricks(const void* brick_table, const void* table, int64_t c
 int wcn_kmap_count(const int32_t* nbr, int64_t num_queries, int32_t num_offsets, void* workspace,
                    void* stream);
 
-/* Tile order of a neighbour table: within each window of 4096 consecutive output rows the
- * rows are sorted by their neighbour-presence mask (bit k set when nbr[k][m] >= 0; ties by
- * row), so that rows with the same present offsets share a 128-row tile and the convolution
- * skips the (tile, offset) pairs that have no neighbour at all.
+/* Tile order of a neighbour table: within each window of consecutive output rows (4096 rows for
+ * tables of at most 4096 rows, else 16384) the rows are sorted by their neighbour-presence key (a
+ * bit per offset, set when nbr[k][m] >= 0; for 27 offsets the centre of the 3x3x3 window is bit 0,
+ * then the face, edge and corner offsets, so the rarest ones are the most significant; otherwise bit
+ * k; ties by row), so that rows with the same present offsets share a 128-row tile and the
+ * convolution skips the (tile, offset) pairs that have no neighbour at all.
  *   out_rows[s]        the output row that slot s of the tiled table stands for (a permutation
  *                      of 0..num_out-1 that moves no row out of its window)
  *   nbr_tiled[k][s]    = nbr[k][out_rows[s]]

@@ -288,20 +288,41 @@ def canonical_kernel_map(in_maps, out_maps, offsets, in_coords=None, out_coords=
 
 
 
-def tile_order(found: np.ndarray, window: int = 4096) -> Tuple[np.ndarray, np.ndarray]:
-    """Row order used by the product's tiled neighbour table (its own layout, no reference
-    counterpart): inside each window of ``window`` consecutive output rows, rows sorted by
-    the presence mask ``sum_k (found[k, m] >= 0) << k``, ties by row.  Returns
-    ``(out_rows[M], found[:, out_rows])``."""
+def tile_order_window(num_rows: int) -> int:
+    """Window of the product's tile order: 4096 rows for tables of at most 4096 rows, else 16384."""
+    return 4096 if num_rows <= 4096 else 16384
+
+
+def tile_order_key(found: np.ndarray) -> np.ndarray:
+    """Sort key of the product's tile order: the presence mask ``sum_k (found[k, m] >= 0) << pos(k)``.
+    For a 3x3x3 window (27 offsets) ``pos`` puts the centre offset in bit 0, then the 6 face, the 12 edge
+    and the 8 corner offsets, each class in offset order; otherwise ``pos(k) = k``."""
     found = np.asarray(found)
     K, M = found.shape
-    mask = np.zeros(M, dtype=np.uint64)
+    if K == 27:
+        cls = [(k // 9 != 1) + ((k // 3) % 3 != 1) + (k % 3 != 1) for k in range(27)]
+        order = sorted(range(27), key=lambda k: (cls[k], k))
+        pos = {k: i for i, k in enumerate(order)}
+    else:
+        pos = {k: k for k in range(K)}
+    key = np.zeros(M, dtype=np.uint64)
     for k in range(K):
-        mask |= (found[k] >= 0).astype(np.uint64) << np.uint64(k)
+        key |= (found[k] >= 0).astype(np.uint64) << np.uint64(pos[k])
+    return key
+
+
+def tile_order(found: np.ndarray, window: int = 0) -> Tuple[np.ndarray, np.ndarray]:
+    """Row order used by the product's tiled neighbour table (its own layout, no reference
+    counterpart): inside each window of consecutive output rows (``tile_order_window``), rows sorted by
+    ``tile_order_key``, ties by row.  Returns ``(out_rows[M], found[:, out_rows])``."""
+    found = np.asarray(found)
+    K, M = found.shape
+    window = window or tile_order_window(M)
+    key = tile_order_key(found)
     rows = np.arange(M, dtype=np.int64)
     for s in range(0, M, window):
         e = min(M, s + window)
-        rows[s:e] = s + np.argsort(mask[s:e], kind="stable")
+        rows[s:e] = s + np.argsort(key[s:e], kind="stable")
     return rows.astype(np.int32), found[:, rows]
 
 

@@ -211,10 +211,12 @@ def test_kernel_map_full_size_properties(mode, n_per_scene):
 
 
 @pytest.mark.parametrize("n,ksize,stride", [(30000, (3, 3, 3), (1, 1, 1)), (4096, (3, 3, 3), (1, 1, 1)),
-                                             (5000, (2, 2, 2), (2, 2, 2)), (37, (3, 3, 3), (1, 1, 1))])
+                                             (5000, (2, 2, 2), (2, 2, 2)), (37, (3, 3, 3), (1, 1, 1)),
+                                             (70000, (3, 3, 3), (1, 1, 1)), (20000, (3, 1, 3), (1, 1, 1))])
 def test_tile_order_matches_oracle(n, ksize, stride):
-    """Tiled neighbour table: rows of each 4096-row window sorted by presence mask, ties by row;
-    bit-exact against the oracle's restatement, for a forward and a transposed (one-hot) map."""
+    """Tiled neighbour table: rows of each window (4096 rows for small tables, 16384 otherwise) sorted by
+    the presence key (3x3x3: rare offsets in the high bits), ties by row; bit-exact against the oracle's
+    restatement, for a forward and a transposed (one-hot) map, several windows and a ragged last one."""
     coords = synthetic.room_scene(n, 0.02, 41, "raster_crop")
     coords = np.concatenate([np.zeros((len(coords), 1), np.int32), coords], axis=1).astype(np.int32)
     coords = np.ascontiguousarray(coords[np.argsort(km.morton_code(coords[:, 1:]), kind="stable")])
@@ -233,7 +235,8 @@ def test_tile_order_matches_oracle(n, ksize, stride):
         assert np.array_equal(rows.cpu().numpy(), want_rows)
         assert np.array_equal(tiled.cpu().numpy(), want_tiled)
         assert np.array_equal(np.sort(want_rows), np.arange(m))
-        assert np.array_equal(want_rows // 4096, np.arange(m) // 4096)  # no row leaves its window
+        w = km.tile_order_window(m)
+        assert np.array_equal(want_rows // w, np.arange(m) // w)  # no row leaves its window
     check_device_status(DEV)
 
 

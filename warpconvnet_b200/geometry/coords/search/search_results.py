@@ -123,7 +123,7 @@ class IntSearchResult:
 
     def tiled_neighbor_table(self, num_out: int) -> Tuple[Tensor, Tensor]:
         """``(nbr_tiled[K, num_out], out_rows[num_out])``: the neighbour table with the output
-        rows of every 4096-row window grouped by which offsets have a neighbour, and the output
+        rows of every 16384-row window grouped by which offsets have a neighbour, and the output
         row each slot stands for.  A 128-row tile of it has far fewer offsets with any
         neighbour than a tile of consecutive rows (12 instead of 18.5 of 27 on a 2 cm room
         scan), and the convolution kernels skip the empty ones.  Built once per map, so every
