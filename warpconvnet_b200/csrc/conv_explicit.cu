@@ -112,11 +112,12 @@ __global__ void row_reduce_kernel(const T* __restrict__ feats, int num_in, const
   const int c0 = (int)(t - m * vpr) * VEC;
   float acc[VEC];
   int count = 0;
+  bool bad = false;
   for (int k = 0; k < K; ++k) {
     const int src = __ldg(&nbr[(int64_t)k * M + m]);
     if (src < 0) continue;
-    if (src >= num_in) {  // not a feature row: counts as absent and is reported
-      wcn_report_bounds(dev_status);
+    if (src >= num_in) {  // not a feature row: counts as absent, reported once when the thread is done
+      bad = true;
       continue;
     }
     __align__(16) T v[VEC];
@@ -154,6 +155,7 @@ __global__ void row_reduce_kernel(const T* __restrict__ feats, int num_in, const
   } else {
     out[m * channels + c0] = o[0];
   }
+  if (bad) wcn_report_bounds(dev_status);
 }
 
 template <typename T>

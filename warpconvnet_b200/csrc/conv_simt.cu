@@ -36,15 +36,16 @@ conv_simt_kernel(const T* __restrict__ feats, const T* __restrict__ weight, cons
   const int tx = threadIdx.x & 15;  // column group
   const int ty = threadIdx.x >> 4;  // row group
   float acc[4][4] = {};
+  bool bad = false;
 
   for (int k = 0; k < K; ++k) {
     int r = -1;
     if (threadIdx.x < TM) {
       const int64_t m = m0 + threadIdx.x;
       r = m < M ? __ldg(&nbr[(int64_t)k * M + m]) : -1;
-      if (r >= lay.num_in) {  // not a feature row: treated as absent and reported
+      if (r >= lay.num_in) {  // not a feature row: treated as absent, reported once when the thread is done
         r = -1;
-        wcn_report_bounds(lay.dev_status);
+        bad = true;
       }
       rows[threadIdx.x] = r;
     }
@@ -101,6 +102,7 @@ conv_simt_kernel(const T* __restrict__ feats, const T* __restrict__ weight, cons
       out[m * lay.out_ld + n] = wcn_from_float<TO>(y);
     }
   }
+  if (bad) wcn_report_bounds(lay.dev_status);
 }
 
 template <typename T, typename TO>
@@ -140,11 +142,12 @@ conv_narrow_kernel(const T* __restrict__ feats, const T* __restrict__ weight, co
   const int n0 = (int)(t - slot * groups) * 8;
   if (slot >= M) return;
   float acc[8] = {};
+  bool bad = false;
   for (int k = 0; k < K; ++k) {
     const int src = __ldg(&nbr[(int64_t)k * M + slot]);
     if (src < 0) continue;
     if (src >= lay.num_in) {
-      wcn_report_bounds(lay.dev_status);
+      bad = true;
       continue;
     }
     const T* x = feats + (int64_t)src * lay.in_ld;
@@ -176,6 +179,7 @@ conv_narrow_kernel(const T* __restrict__ feats, const T* __restrict__ weight, co
   }
 #pragma unroll
   for (int v = 0; v < VEC; ++v) reinterpret_cast<uint4*>(out + m * lay.out_ld + n0)[v] = reinterpret_cast<uint4*>(tmp)[v];
+  if (bad) wcn_report_bounds(lay.dev_status);
 }
 
 template <typename T, typename TO>
@@ -214,6 +218,7 @@ conv_narrow_out_kernel(const T* __restrict__ feats, const T* __restrict__ weight
   if (slot0 >= M) return;
   constexpr int EPV = 16 / (int)sizeof(T);  // input elements per 16-byte load
   float acc[ROWS][NP];
+  bool bad = false;
 #pragma unroll
   for (int r = 0; r < ROWS; ++r)
 #pragma unroll
@@ -225,7 +230,7 @@ conv_narrow_out_kernel(const T* __restrict__ feats, const T* __restrict__ weight
     for (int r = 0; r < ROWS; ++r) {
       int src = slot0 + r < M ? __ldg(&nbr[(int64_t)k * M + slot0 + r]) : -1;
       if (src >= lay.num_in) {
-        wcn_report_bounds(lay.dev_status);
+        bad = true;
         src = -1;
       }
       x[r] = src >= 0 ? reinterpret_cast<const uint4*>(feats + (int64_t)src * lay.in_ld) : nullptr;
@@ -292,6 +297,7 @@ conv_narrow_out_kernel(const T* __restrict__ feats, const T* __restrict__ weight
       }
     }
   }
+  if (bad) wcn_report_bounds(lay.dev_status);
 }
 
 template <typename T, typename TO>

@@ -117,6 +117,7 @@ conv_wgrad_tcgen05_kernel(const WgradParams p) {
     const int PR = p.c_out * 2 / 16;              // 16-byte pieces of a dY row
     const int b_iters = WG_ROWS * PR / WG_PROD_THREADS;
     int slot = 0, phase = 0;
+    bool bad = false;
     for (int64_t st = step0; st < step1 && ok; ++st) {
       if (p.tile_masks && !(__ldg(&p.tile_masks[st]) & gmask)) continue;
       const int64_t m0 = st * WG_ROWS;
@@ -129,15 +130,14 @@ conv_wgrad_tcgen05_kernel(const WgradParams p) {
 #pragma unroll
         for (int j = 0; j < NJ; ++j) {
           const int64_t m = m0 + pwarp * 16 + j * RPI + sub_row;
+          // (the loads of a step are independent and all in flight together: nothing with a side effect sits
+          // between them — an index that names no feature row only raises a flag here and is reported once)
           int r = (unit < total_units && m < p.M) ? __ldg(&p.nbr[(int64_t)k * p.M + m]) : -1;
-          if (r >= (int)p.num_in) {  // not a feature row: counts as absent and is reported
-            r = -1;
-            wcn_report_bounds(p.dev_status);
-          }
+          if (r >= (int)p.num_in) { r = -1; bad = true; }  // counts as absent
           src[u][j] = r;
         }
       }
-      if (!mbar_wait(bar(&ctl->empty[slot]), phase ^ 1, p.dev_status)) { ok = false; break; }
+      if (!mbar_wait_inline(bar(&ctl->empty[slot]), phase ^ 1, p.dev_status)) { ok = false; break; }
       const uint32_t a_dst = base + slot * STAGE;
       const uint32_t b_dst = a_dst + A_STAGE;
 #pragma unroll
@@ -165,6 +165,7 @@ conv_wgrad_tcgen05_kernel(const WgradParams p) {
       if (++slot == p.stages) { slot = 0; phase ^= 1; }
     }
     cp_async_drain();
+    if (bad) wcn_report_bounds(p.dev_status);
   } else if (warp == WG_MMA_WARP) {
     // ================================================================ MMA issuer
     if (lane == 0) {
@@ -175,7 +176,7 @@ conv_wgrad_tcgen05_kernel(const WgradParams p) {
       bool any = false;
       for (int64_t st = step0; st < step1 && ok; ++st) {
         if (p.tile_masks && !(__ldg(&p.tile_masks[st]) & gmask)) continue;
-        if (!mbar_wait(bar(&ctl->full[slot]), phase, p.dev_status)) { ok = false; break; }
+        if (!mbar_wait_inline(bar(&ctl->full[slot]), phase, p.dev_status)) { ok = false; break; }
         tc_fence_after();
         const uint32_t a_slot = base + slot * STAGE;
         const uint32_t b_slot = a_slot + A_STAGE;
@@ -196,7 +197,7 @@ conv_wgrad_tcgen05_kernel(const WgradParams p) {
     __syncwarp();
   } else {
     // ================================================================ epilogue (warps 0..3)
-    ok = mbar_wait(bar(&ctl->acc_full), 0, p.dev_status);
+    ok = mbar_wait_inline(bar(&ctl->acc_full), 0, p.dev_status);
     if (__all_sync(0xFFFFFFFFu, ok) && ctl->any) {
       tc_fence_after();
       const int row = warp * 32 + lane;            // TMEM lane = position on the M side

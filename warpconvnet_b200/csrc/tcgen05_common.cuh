@@ -61,10 +61,32 @@ __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, int32
     }
   }
 }
-// The wait every kernel role uses: the limit is about two seconds.
+// The wait of the kernels whose roles are long single-thread or single-slot loops: the limit is about two
+// seconds, the slow path is a call.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int32_t* dev_status) {
   if (mbar_try_wait(bar, parity)) return true;
   return mbar_wait_slow(bar, parity, dev_status, kWaitCycles);
+}
+// The same wait entirely inline, for roles in which many threads block often while holding many live
+// registers (the weight-gradient kernel's producers): a call there spills around every blocked wait.
+__device__ __forceinline__ bool mbar_wait_inline(uint32_t bar, uint32_t parity, int32_t* dev_status) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  long long next_check = t0 + kStatusPollCycles;
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 16; ++i)
+      if (mbar_try_wait(bar, parity)) return true;
+    const long long now = clock64();
+    if (now > next_check) {
+      if (*(volatile int32_t*)dev_status == (int)WCN_ERR_WAIT_EXPIRED) return false;
+      if (now - t0 > kWaitCycles) {
+        atomicExch(dev_status, (int)WCN_ERR_WAIT_EXPIRED);
+        return false;
+      }
+      next_check = now + kStatusPollCycles;
+    }
+  }
 }
 // The same wait with a caller-chosen limit (the self test of the expiry path).
 __device__ __forceinline__ bool mbar_wait_limit(uint32_t bar, uint32_t parity, int32_t* dev_status, long long limit_cycles) {
