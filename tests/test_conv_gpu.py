@@ -165,6 +165,35 @@ def test_tile_order_is_bit_identical(dtype, algo, c_in, c_out):
         assert torch.equal(a, b)
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("c_in,c_out", [(32, 16), (64, 48), (32, 80), (96, 112), (64, 144), (128, 256)])
+def test_residual_rows_of_every_width(dtype, c_in, c_out):
+    """The tensor-core kernel reads the residual of 16-bit outputs through shared memory, 64 columns at a
+    time with a narrower last piece: widths that end in a 16-, 32- and 48-column piece, rows in tile order
+    and in table order, the residual a column block of a wider matrix and a last sub-tile that is not full.
+    Against the FP32-pipe kernel (both round the same fp32 value once)."""
+    n = 33333
+    coords, x, w = _layer_case(n, c_in, c_out, 31 + c_out, "raster_crop")
+    coords = np.ascontiguousarray(coords[np.argsort(km.morton_code(coords[:, 1:]), kind="stable")])
+    c = torch.from_numpy(coords).to(DEV)
+    kmap = generate_kernel_map(c, c, (1, 1, 1), (3, 3, 3))
+    g = torch.Generator().manual_seed(c_out)
+    wide = torch.randn(n, c_out + 32, generator=g).to(dtype).to(DEV)
+    xd, wd = x.to(dtype).to(DEV), w.to(dtype).to(DEV)
+    for residual in (wide[:, 16:16 + c_out], wide[:, :c_out].contiguous()):
+        ep = ConvEpilogue(scale=(torch.rand(c_out, generator=g) + 0.5).to(DEV), shift=torch.randn(c_out, generator=g).to(DEV),
+                          residual=residual, relu=True)
+        ref = sparse_conv_fused(xd, wd, kmap, n, epilogue=ep, algo=CONV_SIMT)
+        for tile_order in (False, True):
+            got = sparse_conv_fused(xd, wd, kmap, n, epilogue=ep, algo=CONV_TCGEN05, tile_order=tile_order, split_k=1)
+            check_device_status(DEV)
+            assert rel_l2(got.float().cpu().numpy(), ref.float().cpu().numpy()) < 2e-3
+            assert float((got.float() - ref.float()).abs().max()) < 0.25
+        plain = sparse_conv_fused(xd, wd, kmap, n, algo=CONV_TCGEN05, split_k=1).float()
+        want = torch.relu(plain * ep.scale + ep.shift + residual.float())
+        assert float((got.float() - want).abs().max()) < 0.1   # `plain` is rounded once more than `got`
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
 @pytest.mark.parametrize("K,c_in,c_out", [(27, 3, 32), (1, 3, 32), (27, 4, 64), (8, 6, 16),
                                           (1, 96, 20), (1, 64, 8), (8, 32, 24), (1, 128, 31)])

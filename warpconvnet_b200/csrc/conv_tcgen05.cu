@@ -595,8 +595,26 @@ conv_tcgen05_kernel(const ConvTcParams p) {
       OutVec<TO>::store(orow + c0, y, p.wide_out);
     };
     const bool sliced = p.S > 1;  // leave raw fp32 sums for the reduction kernel instead of finishing rows
+    // This thread's output rows in the two sub-tiles of a unit.  With rows in tile order they come from
+    // `out_rows`, and a load issued when its value is needed costs the epilogue a full memory latency per
+    // sub-tile (the gather keeps the memory system busy): the rows of the next unit are read while this one
+    // is finished.
+    auto unit_rows = [&](int64_t wu, int32_t (&rows)[MAX_G]) {
+      const int64_t first = (sliced ? wu / p.S : wu) * G * BLOCK_M + tid;
+#pragma unroll
+      for (int g = 0; g < MAX_G; ++g) {
+        const int64_t slot = first + (int64_t)g * BLOCK_M;
+        rows[g] = (g < G && slot < p.M) ? (p.out_rows ? __ldg(&p.out_rows[slot]) : (int32_t)slot) : -1;
+      }
+    };
+    int32_t next_rows[MAX_G];
+    if ((int64_t)blockIdx.x < p.units) unit_rows(blockIdx.x, next_rows);
     for (int64_t wu = blockIdx.x; wu < p.units; wu += gridDim.x) {
       const int64_t st = sliced ? wu / p.S : wu;
+      int32_t rows[MAX_G];
+#pragma unroll
+      for (int g = 0; g < MAX_G; ++g) rows[g] = next_rows[g];
+      if (wu + gridDim.x < p.units) unit_rows(wu + gridDim.x, next_rows);
       if (ok) ok = mbar_wait(bar(&ctl->info_full[ib]), iphase, p.dev_status);
       const uint32_t gm0 = ok ? ctl->info_mask[ib][0] : 0u, gm1 = ok ? ctl->info_mask[ib][1] : 0u;
       mbar_arrive(bar(&ctl->info_empty[ib]));  // only the masks were needed
@@ -613,8 +631,7 @@ conv_tcgen05_kernel(const ConvTcParams p) {
         if (m0 + (int64_t)g * BLOCK_M >= p.M) break;
         const uint32_t gmask = g == 0 ? gm0 : gm1;
         const int64_t slot = m0 + (int64_t)g * BLOCK_M + tid;
-        // rows past the end keep m >= M and are never stored
-        const int64_t m = (p.out_rows && slot < p.M) ? (int64_t)__ldg(&p.out_rows[slot]) : slot;
+        const int64_t m = g == 0 ? rows[0] : rows[1];   // -1 past the end: never stored
         const bool live = slot < p.M;
         const uint32_t trow = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)((ab * G + g) * p.cols);
         TO* orow = reinterpret_cast<TO*>(p.out) + m * p.out_ld + n0;
@@ -929,7 +946,7 @@ int wcn_conv_tcgen05_fwd(const void* feats, int64_t num_in, int64_t feats_ld, co
                          void* out, int64_t out_ld, int out_dtype, int split_k, void* workspace,
                          int64_t workspace_bytes, int32_t* dev_status, cudaStream_t st) {
   if (!wcn_conv_tcgen05_supported(K, c_in, c_out, dtype, out_dtype)) return WCN_ERR_UNSUPPORTED_CONFIG;
-  if (!dev_status || !packed || num_in <= 0 || num_in >= 0x7FFFFFFFll) return WCN_ERR_INVALID_PARAMETERS;
+  if (!dev_status || !packed || num_in <= 0 || num_in >= 0x7FFFFFFFll || M >= 0x7FFFFFFFll) return WCN_ERR_INVALID_PARAMETERS;
   const int64_t osz = out_dtype == WCN_F32 ? 4 : 2;
   if ((reinterpret_cast<uintptr_t>(feats) & 15) || (reinterpret_cast<uintptr_t>(packed) & 15) ||
       (reinterpret_cast<uintptr_t>(out) & 15) || (reinterpret_cast<uintptr_t>(residual) & 15) ||

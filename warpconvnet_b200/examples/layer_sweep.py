@@ -20,7 +20,7 @@ import torch
 from .. import POINT_ORDERING, Voxels, generate_kernel_map, stride_coords
 from .._native import CONV_AUTO, CONV_SIMT, CONV_TCGEN05, check_device_status
 from ..datasets import synthetic
-from ..nn.functional.sparse_conv import sparse_conv_fused, sparse_conv_wgrad
+from ..nn.functional.sparse_conv import ConvEpilogue, sparse_conv_fused, sparse_conv_wgrad
 
 DT = {"fp16": torch.float16, "bf16": torch.bfloat16, "fp32": torch.float32}
 ALGOS = {"auto": CONV_AUTO, "simt": CONV_SIMT, "tcgen05": CONV_TCGEN05}
@@ -53,7 +53,7 @@ def time_ms(fn, iters, flush):
 
 def measure(voxels: int = 500000, voxel_size: float = 0.01, mode: str = "raster_crop", channels=(32, 64, 128, 256),
             dtypes=("fp16", "bf16"), kinds=("conv3", "down2", "up2"), algo: str = "auto", iters: int = 10,
-            sort: bool = True, dev=None, flush=None):
+            sort: bool = True, dev=None, flush=None, residual: bool = False):
     """One dict per (kind, width, dtype) case of the single-layer sweep."""
     dev = dev or torch.device("cuda", 0)
     hbm, tflops, src = peaks()
@@ -95,16 +95,20 @@ def measure(voxels: int = 500000, voxel_size: float = 0.01, mode: str = "raster_
                     gy = torch.randn(n_out, c, generator=g).to(dev, dt)
                     wt, kt = w.transpose(1, 2).contiguous(), kmap.swapped(num_in=n_in)
                     fn = lambda: sparse_conv_fused(gy, wt, kt, n_in, algo=ALGOS[algo])
+                elif residual:  # the second convolution of a residual block: folded BatchNorm, + identity, ReLU
+                    ep = ConvEpilogue(scale=torch.rand(c, generator=g).to(dev) + 0.5, shift=torch.randn(c, generator=g).to(dev),
+                                      residual=torch.randn(n_out, c, generator=g).to(dev, dt), relu=True)
+                    fn = lambda: sparse_conv_fused(x, w, kmap, n_out, epilogue=ep, algo=ALGOS[algo])
                 else:
                     fn = lambda: sparse_conv_fused(x, w, kmap, n_out, algo=ALGOS[algo])
                 ms = time_ms(fn, iters, flush)
                 check_device_status(dev)
                 es = 4 if dt == torch.float32 else 2
                 flop = 2.0 * pairs * c * c
-                byts = es * (n_in * c + n_out * c + K * c * c) + 4.0 * n_out * K
+                byts = es * (n_in * c + n_out * c * (2 if residual and not which else 1) + K * c * c) + 4.0 * n_out * K
                 t_tc, t_hbm = flop / (tflops * 1e12), byts / (hbm * 1e9)
                 lines.append({
-                    "kind": kind_arg, "c": c, "dtype": dname, "voxels_in": n_in, "voxels_out": n_out, "pairs": pairs,
+                    "kind": kind_arg + ("+residual" if residual and not which else ""), "c": c, "dtype": dname, "voxels_in": n_in, "voxels_out": n_out, "pairs": pairs,
                     "pairs_per_out": pairs / n_out, "ms": ms, "useful_tflops": flop / ms / 1e9,
                     "alg_gbs": byts / ms / 1e6, "bound": "tensor" if t_tc > t_hbm else "hbm",
                     "roofline_frac": max(t_tc, t_hbm) / (ms * 1e-3), "peaks": src,
@@ -124,9 +128,12 @@ def main():
     ap.add_argument("--algo", default="auto", choices=list(ALGOS))
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--no-sort", action="store_true", help="keep the generator's random row order")
+    ap.add_argument("--residual", action="store_true",
+                    help="forward layers carry the tail of a residual block: scale/shift, + residual rows, ReLU")
     args = ap.parse_args()
     lines = measure(args.voxels, args.voxel_size, args.mode, [int(v) for v in args.channels.split(",")],
-                    args.dtypes.split(","), args.kinds.split(","), args.algo, args.iters, not args.no_sort)
+                    args.dtypes.split(","), args.kinds.split(","), args.algo, args.iters, not args.no_sort,
+                    residual=args.residual)
     for line in lines:
         print(json.dumps(line), flush=True)
 
