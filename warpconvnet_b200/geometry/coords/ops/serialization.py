@@ -97,8 +97,9 @@ def encode(grid_coord: Tensor, batch_offsets: Optional[Tensor] = None,
     if batch_offsets is not None and len(batch_offsets) > 2:
         # sort by code inside each batch segment: stable sort by code, then stable sort by batch
         from .batch_index import batch_index_on
-        # (a 16-bit batch key: the radix sort behind argsort runs one pass per key byte)
-        seg_dtype = torch.int16 if len(batch_offsets) - 1 < 2 ** 15 else torch.int64
+        # (the narrowest batch key: the radix sort behind argsort runs one pass per key byte)
+        nb = len(batch_offsets) - 1
+        seg_dtype = torch.uint8 if nb <= 256 else torch.int16 if nb < 2 ** 15 else torch.int64
         seg = batch_index_on(batch_offsets, codes.shape[0], codes.device, seg_dtype)
         by_code = torch.argsort(codes, stable=True)
         perm = by_code[torch.argsort(seg[by_code], stable=True)]
