@@ -343,6 +343,7 @@ int wcn_conv_workspace_bytes(int algo, int64_t num_out, int32_t num_offsets, int
  * matrices in elements (0 = dense: c_in / c_out), so a matrix may be a column block of a wider
  * one (a skip connection's half of a concatenated buffer); rows must start on 16-byte boundaries
  * for the tensor-core kernel.  nbr entries >= num_in count as absent and raise WCN_ERR_BOUNDS.
+ * num_in and M are below 2^31 (row numbers are 32-bit); larger values return WCN_ERR_INVALID_PARAMETERS.
  * algo WCN_CONV_TCGEN05 needs dtype f16/bf16, c_in % 32 == 0, c_out % 16 == 0, 16 <= c_out <= 256
  * and `packed_weight` from wcn_conv_pack_weight; WCN_CONV_AUTO picks it when those hold and
  * packed_weight is not NULL, else the SIMT kernel.

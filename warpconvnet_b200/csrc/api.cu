@@ -93,6 +93,7 @@ extern "C" int wcn_conv_fwd(int algo, const void* feats, int64_t num_in, int64_t
                             int relu, void* out, int64_t out_ld, int out_dtype, int32_t split_k, void* workspace,
                             int64_t workspace_bytes, int32_t* dev_status, void* stream) {
   if (num_in < 0 || num_out < 0 || num_offsets <= 0 || c_in <= 0 || c_out <= 0) return WCN_ERR_INVALID_PARAMETERS;
+  if (num_in >= 0x7FFFFFFFll || num_out >= 0x7FFFFFFFll) return WCN_ERR_INVALID_PARAMETERS;  // row numbers are 32-bit
   if (dtype < WCN_F32 || dtype > WCN_BF16 || out_dtype < WCN_F32 || out_dtype > WCN_BF16)
     return WCN_ERR_INVALID_PARAMETERS;
   if (feats_ld == 0) feats_ld = c_in;  // 0: rows are dense
